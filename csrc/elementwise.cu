@@ -1,0 +1,377 @@
+// Memory-bound kernels of the TaH layer stack: RMSNorm, per-head QK-norm + RoPE + KV-cache write,
+// embedding gather, rank-r LoRA-A products for the few "hard" rows of a decode tick, SwiGLU,
+// and the logit post-processing of a tick (cumulative logits, argmax).
+//
+// Rounding follows what a bf16 PyTorch module stack produces (norm output rounded before the
+// weight multiply, RoPE products rounded before the add), so that greedy token streams agree
+// with an eager bf16 run of the same model.
+#include "common.cuh"
+
+namespace tahb {
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm: y = w * bf16(x * rsqrt(mean(x^2) + eps)).  One CTA (128 threads) per row, row kept in
+// registers (H <= 128 * 8 * VPT elements).
+// ---------------------------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(128) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                      const __nv_bfloat16* __restrict__ w,
+                                                      __nv_bfloat16* __restrict__ y, int H, long long ldx,
+                                                      long long ldy, float eps) {
+  const int row = blockIdx.x;
+  const int nvec = H / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+  uint4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    if (idx < nvec) {
+      v[i] = xr[idx];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+  __shared__ float red[4];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float tot = red[0] + red[1] + red[2] + red[3];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    if (idx < nvec) {
+      uint4 wv = wr[idx];
+      uint4 o;
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        float2 g = __bfloat1622float2(wh[j]);
+        oh[j] = __floats2bfloat162_rn(g.x * bf16_round(f.x * rstd), g.y * bf16_round(f.y * rstd));
+      }
+      yr[idx] = o;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-head QK RMSNorm + rotate-half RoPE + KV write.  One warp per (token, head).
+//   qkv      [M, (nq + 2 nkv) * HD]
+//   q_out    [M, nq * HD]
+//   k_dense / v_dense (optional) [M, nkv * HD] : packed K/V of this pass (prefill / training)
+//   cache (optional): paged cache of ONE layer; entry (page, kv, head, off) at
+//        ((page * 2 + kv) * nkv + head) * page_size + off) * HD ; slot[t] = page * page_size + off,
+//        negative slot = do not write.  With n_caches > 1, cache_sel[t] picks the depth cache.
+// ---------------------------------------------------------------------------------------------
+struct QkvRopeParams {
+  const __nv_bfloat16* qkv;
+  const __nv_bfloat16* q_w;
+  const __nv_bfloat16* k_w;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_dense;
+  __nv_bfloat16* v_dense;
+  __nv_bfloat16* cache[4];
+  const int* cache_sel;
+  const int* slot;
+  const int* pos;
+  int M, nq, nkv, page_size;
+  long long ld_qkv;
+  float eps, log2_theta;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(const QkvRopeParams p) {
+  constexpr int EPL = HD / 32;  // elements per lane
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int heads = p.nq + 2 * p.nkv;
+  if (warp_global >= p.M * heads) return;
+  const int t = warp_global / heads;
+  const int h = warp_global % heads;
+  const __nv_bfloat16* src = p.qkv + (size_t)t * p.ld_qkv + (size_t)h * HD + lane * EPL;
+  float x[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) x[i] = __bfloat162float(src[i]);
+  const bool is_q = h < p.nq;
+  const bool is_k = !is_q && h < p.nq + p.nkv;
+  float y[EPL];
+  if (is_q || is_k) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)HD + p.eps);
+    const __nv_bfloat16* w = (is_q ? p.q_w : p.k_w) + lane * EPL;
+    float n[EPL], partner[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) n[i] = bf16_round(__bfloat162float(w[i]) * bf16_round(x[i] * rstd));
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, n[i], 16);
+    const float posf = (float)p.pos[t];
+    const bool upper = lane >= 16;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int d = lane * EPL + i;
+      const int j = upper ? d - HD / 2 : d;                    // frequency index
+      const float inv = exp2f(-(2.0f * (float)j / (float)HD) * p.log2_theta);
+      const float ang = posf * inv;
+      const float c = bf16_round(cosf(ang)), s = bf16_round(sinf(ang));
+      const float rot = upper ? partner[i] : -partner[i];
+      y[i] = bf16_round(bf16_round(n[i] * c) + bf16_round(rot * s));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) y[i] = x[i];
+  }
+  __nv_bfloat16 o[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) o[i] = __float2bfloat16_rn(y[i]);
+  if (is_q) {
+    __nv_bfloat16* dst = p.q_out + ((size_t)t * p.nq + h) * HD + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dst[i] = o[i];
+    return;
+  }
+  const int kvh = is_k ? h - p.nq : h - p.nq - p.nkv;
+  const int which = is_k ? 0 : 1;
+  __nv_bfloat16* dense = is_k ? p.k_dense : p.v_dense;
+  if (dense != nullptr) {
+    __nv_bfloat16* dst = dense + ((size_t)t * p.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dst[i] = o[i];
+  }
+  if (p.slot != nullptr) {
+    const int sl = p.slot[t];
+    if (sl >= 0) {
+      const int sel = p.cache_sel ? p.cache_sel[t] : 0;
+      __nv_bfloat16* cache = p.cache[sel];
+      const int page = sl / p.page_size, off = sl % p.page_size;
+      __nv_bfloat16* dst =
+          cache + ((((size_t)page * 2 + which) * p.nkv + kvh) * p.page_size + off) * HD + lane * EPL;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) dst[i] = o[i];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Embedding gather: out[r] = E[tok[r]]  (tok < 0 -> zeros)
+// ---------------------------------------------------------------------------------------------
+__global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ E, const int* __restrict__ tok,
+                                    __nv_bfloat16* __restrict__ out, int H, long long ld_out) {
+  const int r = blockIdx.x;
+  const int id = tok[r];
+  const uint4* src = reinterpret_cast<const uint4*>(E + (size_t)(id < 0 ? 0 : id) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * ld_out);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = id < 0 ? make_uint4(0, 0, 0, 0) : src[i];
+}
+
+// ---------------------------------------------------------------------------------------------
+// LoRA-A on gated rows:  T[r, :] = gate[r] ? x[r, :] A^T : 0        (A: [R, K], T: [M, ldt])
+// One CTA per row; rows whose gate is 0 only clear their output.  Meant for decode ticks where
+// a handful of rows are at depth >= 1; dense passes use the tensor-core GEMM instead.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ A,
+                                                          __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
+                                                          int K, int R, long long ldx, long long ldt) {
+  const int r = blockIdx.x;
+  __nv_bfloat16* out = T + (size_t)r * ldt;
+  if (gate != nullptr && gate[r] == 0) {
+    for (int i = threadIdx.x; i < R; i += blockDim.x) out[i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
+  for (int j = warp; j < R; j += 8) {
+    const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)j * K);
+    float acc = 0.f;
+    for (int i = lane; i < K / 8; i += 32) {
+      uint4 xv = xr[i], av = ar[i];
+      const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 a = __bfloat1622float2(xh[q]), b = __bfloat1622float2(ah[q]);
+        acc += a.x * b.x + a.y * b.y;
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[j] = __float2bfloat16_rn(acc);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU on a materialised [M, 2I] gate|up tensor (used where the GEMM epilogue fusion is off).
+// ---------------------------------------------------------------------------------------------
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int M, int I,
+                              long long ld_in, long long ld_out) {
+  const long long n = (long long)M * I;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / I), c = (int)(i % I);
+    const float g = __bfloat162float(gu[(size_t)r * ld_in + c]);
+    const float u = __bfloat162float(gu[(size_t)r * ld_in + I + c]);
+    out[(size_t)r * ld_out + c] = __float2bfloat16_rn(bf16_round(silu(g)) * u);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tick logit post-processing.  Per row r:
+//   cum[r] = depth[r] > 0 ? cum[r] + logits[r] : logits[r]      (bf16 add, like the model's
+//   additive logit update), and argmax over cum[r] -> best[r] (lowest index wins ties).
+// One CTA of 1024 threads per row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) logits_post_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                           __nv_bfloat16* __restrict__ cum,
+                                                           const int* __restrict__ depth, int* __restrict__ best,
+                                                           int V, long long ld_logits, long long ld_cum) {
+  const int r = blockIdx.x;
+  const bool add = depth != nullptr && depth[r] > 0;
+  const __nv_bfloat16* lr = logits + (size_t)r * ld_logits;
+  __nv_bfloat16* cr = cum + (size_t)r * ld_cum;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  const int nvec = V / 8;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    uint4 lv = reinterpret_cast<const uint4*>(lr)[i];
+    __nv_bfloat16* le = reinterpret_cast<__nv_bfloat16*>(&lv);
+    if (add) {
+      uint4 cv = reinterpret_cast<const uint4*>(cr)[i];
+      const __nv_bfloat16* ce = reinterpret_cast<const __nv_bfloat16*>(&cv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) le[j] = __float2bfloat16_rn(__bfloat162float(ce[j]) + __bfloat162float(le[j]));
+    }
+    reinterpret_cast<uint4*>(cr)[i] = lv;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = __bfloat162float(le[j]);
+      if (v > bv) { bv = v; bi = i * 8 + j; }
+    }
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    float v = __bfloat162float(lr[i]);
+    if (add) v = bf16_round(__bfloat162float(cr[i]) + v);
+    cr[i] = __float2bfloat16_rn(v);
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  // block argmax (value desc, index asc)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = sv[lane];
+    bi = si[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) best[r] = bi;
+  }
+}
+
+}  // namespace tahb
+
+using namespace tahb;
+
+extern "C" int tahb_rmsnorm(const void* x, const void* w, void* y, int M, int H, long long ldx, long long ldy,
+                            float eps, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H % 8) return -1;
+  const int nvec = H / 8;
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  if (nvec <= 128) rmsnorm_kernel<1><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
+  else if (nvec <= 256) rmsnorm_kernel<2><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
+  else if (nvec <= 512) rmsnorm_kernel<4><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
+  else if (nvec <= 1024) rmsnorm_kernel<8><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_qk_norm_rope_kv(const void* qkv, const void* q_w, const void* k_w, void* q_out, void* k_dense,
+                                    void* v_dense, void* const* caches, int n_caches, const int* cache_sel,
+                                    const int* slot, const int* pos, int M, int nq, int nkv, int hd, int page_size,
+                                    long long ld_qkv, float eps, float theta, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (n_caches > 4) return -1;
+  QkvRopeParams p;
+  p.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
+  p.q_w = reinterpret_cast<const __nv_bfloat16*>(q_w);
+  p.k_w = reinterpret_cast<const __nv_bfloat16*>(k_w);
+  p.q_out = reinterpret_cast<__nv_bfloat16*>(q_out);
+  p.k_dense = reinterpret_cast<__nv_bfloat16*>(k_dense);
+  p.v_dense = reinterpret_cast<__nv_bfloat16*>(v_dense);
+  for (int i = 0; i < 4; ++i) p.cache[i] = i < n_caches ? reinterpret_cast<__nv_bfloat16*>(caches[i]) : nullptr;
+  p.cache_sel = cache_sel;
+  p.slot = n_caches > 0 ? slot : nullptr;
+  p.pos = pos;
+  p.M = M; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
+  p.ld_qkv = ld_qkv;
+  p.eps = eps;
+  p.log2_theta = log2f(theta);
+  const long long warps = (long long)M * (nq + 2 * nkv);
+  const int blocks = (int)((warps + 3) / 4);
+  if (hd == 128) qk_norm_rope_kv_kernel<128><<<blocks, 128, 0, stream>>>(p);
+  else if (hd == 64) qk_norm_rope_kv_kernel<64><<<blocks, 128, 0, stream>>>(p);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_embed_gather(const void* E, const int* tok, void* out, int M, int H, long long ld_out,
+                                 cudaStream_t stream) {
+  if (M <= 0) return 0;
+  embed_gather_kernel<<<M, 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(E), tok,
+                                             reinterpret_cast<__nv_bfloat16*>(out), H, ld_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_lora_a_rows(const void* x, const void* A, void* T, const int* gate, int M, int K, int R,
+                                long long ldx, long long ldt, cudaStream_t stream) {
+  if (M <= 0 || R <= 0) return 0;
+  if (K % 8) return -1;
+  lora_a_rows_kernel<<<M, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                            reinterpret_cast<const __nv_bfloat16*>(A),
+                                            reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_swiglu(const void* gu, void* out, int M, int I, long long ld_in, long long ld_out,
+                           cudaStream_t stream) {
+  if (M <= 0) return 0;
+  const long long n = (long long)M * I;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  swiglu_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
+                                            reinterpret_cast<__nv_bfloat16*>(out), M, I, ld_in, ld_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_logits_post(const void* logits, void* cum, const int* depth, int* best, int M, int V,
+                                long long ld_logits, long long ld_cum, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if ((ld_logits % 8) || (ld_cum % 8)) return -1;
+  logits_post_kernel<<<M, 1024, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits),
+                                             reinterpret_cast<__nv_bfloat16*>(cum), depth, best, V, ld_logits, ld_cum);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,355 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory,
+// operands staged by TMA), with the fusions the TaH layers need.
+//
+// Orientation: "features on lanes".  The 128 TMEM lanes of a CTA hold 128 output features
+// (rows of the weight matrix W[F, K]); the TMEM columns hold BN tokens (rows of X[M, K]).
+//
+//     acc[f, t] = sum_k W[f, k] * X[t, k]  +  sum_r W2[f, r] * X2[t, r]
+//
+// The second sum is the K-extension used for LoRA: W2 = scaled LoRA-B (block-diagonal over the
+// fused projections), X2 = gated x*A^T, so the adapter is part of the same accumulation and of the
+// same epilogue ("fused LoRA-GEMM").  Putting the weights on the 128-row operand keeps the tensor
+// cores full in decode, where M is 16..256 tokens and the cost is streaming W once from HBM.
+//
+// Epilogues (all write out[t, f] in bf16):
+//   plain      out = acc
+//   residual   out = residual[t, f] + bf16(acc)
+//   DUAL       two accumulators per CTA, gate = rows f and up = rows up_off + f of W:
+//              out = bf16(silu(bf16(gate))) * bf16(up)             (SwiGLU)
+//
+// Split-K: a thread-block cluster of S CTAs along z splits the k-blocks; partial accumulators go
+// to each CTA's own shared memory and every CTA reduces a slice of the token columns from all
+// peers through distributed shared memory, in rank order (deterministic).  No global scratch.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31).
+#include <cuda.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace tahb {
+
+struct GemmParams {
+  __nv_bfloat16* out;
+  const __nv_bfloat16* residual;
+  int ld_out;
+  int ld_res;
+  int M;        // tokens
+  int F;        // output features (per half when DUAL)
+  int up_off;   // DUAL: row offset of the "up" half inside W
+  int kb_main;  // K / 64
+  int kb_ext;   // R / 64
+  int splits;   // cluster size along z (1 = no split-K)
+  int* status;
+};
+
+template <int BN, bool DUAL>
+struct GemmCfg {
+  static constexpr int W_TILE = 128 * 64 * 2;                 // 16 KiB
+  static constexpr int W_BYTES = W_TILE * (DUAL ? 2 : 1);
+  static constexpr int X_BYTES = BN * 64 * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int NS_RAW = (196 * 1024) / STAGE_BYTES;
+  static constexpr int NS = NS_RAW > 8 ? 8 : NS_RAW;
+  static constexpr int COLS = BN * (DUAL ? 2 : 1);
+  static constexpr int TMEM_COLS = COLS < 32 ? 32 : COLS;     // power of two >= 32 (BN is a power of two)
+  static constexpr int SMEM_BYTES = NS * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int CHUNK = BN >= 32 ? 32 : 16;
+};
+
+template <int CHUNK>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float* v) {
+  if constexpr (CHUNK == 32) tmem_ld32(taddr, v);
+  else tmem_ld16(taddr, v);
+}
+
+template <bool DUAL>
+__device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, float a, float u) {
+  float y;
+  if constexpr (DUAL) {
+    y = bf16_round(silu(bf16_round(a))) * bf16_round(u);
+  } else {
+    y = a;
+    if (p.residual != nullptr) y = bf16_round(a) + __bfloat162float(p.residual[(size_t)t * p.ld_res + f]);
+  }
+  p.out[(size_t)t * p.ld_out + f] = __float2bfloat16_rn(y);
+}
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(192, 1)
+gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+               const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_x2,
+               const GemmParams p) {
+  using C = GemmCfg<BN, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::NS * C::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + C::NS;
+  uint64_t* accum_bar = empty_bar + C::NS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * 128;
+  const int t0 = blockIdx.y * BN;
+  const int S = p.splits;
+  const int rank = blockIdx.z;                       // == cluster rank: cluster dims are (1, 1, S)
+  const int kb_total = p.kb_main + p.kb_ext;
+  const int kb_begin = (int)(((long long)kb_total * rank) / S);
+  const int kb_end = (int)(((long long)kb_total * (rank + 1)) / S);
+  const int n_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::NS; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tm_w);
+    prefetch_tensormap(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % C::NS;
+        const uint32_t ph = (i / C::NS) & 1;
+        mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_STAGE_EMPTY);
+        mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+        const int g = kb_begin + i;
+        const bool ext = g >= p.kb_main;
+        const int x = (ext ? g - p.kb_main : g) * 64;
+        const CUtensorMap* mw = ext ? &tm_w2 : &tm_w;
+        const CUtensorMap* mx = ext ? &tm_x2 : &tm_x;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        tma_load_2d(st, mw, x, f0, &full_bar[s]);
+        if constexpr (DUAL) tma_load_2d(st + C::W_TILE, mw, x, p.up_off + f0, &full_bar[s]);
+        tma_load_2d(st + C::W_BYTES, mx, x, t0, &full_bar[s]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, BN);
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % C::NS;
+        const uint32_t ph = (i / C::NS) & 1;
+        mbar_wait(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + C::W_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t db = umma_desc_sw128(b_addr + k * 32);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), db, idesc, acc);
+          if constexpr (DUAL) umma_bf16(tmem_base + BN, umma_desc_sw128(a_addr + C::W_TILE + k * 32), db, idesc, acc);
+        }
+        umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+      }
+      umma_commit(accum_bar);
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int f = f0 + row;
+    const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    mbar_wait(accum_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
+    tc_fence_after();
+    if (S == 1) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += C::CHUNK) {
+        float a[C::CHUNK];
+        float u[DUAL ? C::CHUNK : 1];
+        tmem_ld_chunk<C::CHUNK>(trow + c0, a);
+        if constexpr (DUAL) tmem_ld_chunk<C::CHUNK>(trow + BN + c0, u);
+        tmem_ld_wait();
+        if (f < p.F) {
+#pragma unroll
+          for (int j = 0; j < C::CHUNK; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < p.M) store_one<DUAL>(p, t, f, a[j], DUAL ? u[j] : 0.f);
+          }
+        }
+      }
+    } else {
+      // partial accumulator -> own shared memory, column-major [col][128 rows]
+      float* red = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+      for (int c0 = 0; c0 < C::COLS; c0 += C::CHUNK) {
+        float a[C::CHUNK];
+        tmem_ld_chunk<C::CHUNK>(trow + c0, a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < C::CHUNK; ++j) red[(c0 + j) * 128 + row] = a[j];
+      }
+    }
+    tc_fence_before();
+  }
+
+  if (S > 1) {
+    // every thread of every CTA in the cluster takes part in both barriers
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int q = warp & 3;
+      const int row = q * 32 + lane;
+      const int f = f0 + row;
+      const int per = BN / S;
+      const uint32_t red_addr = smem_u32(smem);
+      for (int c = rank * per; c < (rank + 1) * per; ++c) {
+        float a = 0.f, u = 0.f;
+        for (int r = 0; r < S; ++r) {
+          a += ld_dsmem_f32(red_addr + (c * 128 + row) * 4, r);
+          if constexpr (DUAL) u += ld_dsmem_f32(red_addr + ((BN + c) * 128 + row) * 4, r);
+        }
+        const int t = t0 + c;
+        if (f < p.F && t < p.M) store_one<DUAL>(p, t, f, a, u);
+      }
+    }
+    cluster_sync_all();
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2D bf16 row-major [rows, cols] with leading dimension ld (elements); box = {64, box_rows}, 128B swizzle.
+static int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <int BN, bool DUAL>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mw2, const CUtensorMap& mx2,
+                  const GemmParams& p, cudaStream_t stream) {
+  using C = GemmCfg<BN, DUAL>;
+  static bool configured = false;
+  auto kern = gemm_fl_kernel<BN, DUAL>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -10;
+    configured = true;
+  }
+  if (p.splits > 1 && (size_t)C::COLS * 512 > (size_t)C::NS * C::STAGE_BYTES) return -11;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.F + 127) / 128, (p.M + BN - 1) / BN, p.splits);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, mw2, mx2, p);
+  return e == cudaSuccess ? 0 : -12;
+}
+
+}  // namespace tahb
+
+using namespace tahb;
+
+// out[M, F] = X[M, K] W[F, K]^T (+ X2[M, R] W2[F, R]^T) (+ residual) ; dual != 0 => SwiGLU over W rows
+// [0, F) (gate) and [up_off, up_off + F) (up).  All matrices bf16 row-major; K and R multiples of 64.
+// bn = token-tile width (16/32/64/128/256, 0 = choose from M); splits = split-K cluster size (1,2,4,8).
+// Returns 0 on success, a negative code on a host-side error.  *status (device int) is set non-zero
+// by the kernel if a bounded wait ran out.
+extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* residual, const void* W2,
+                         const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
+                         long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
+                         int* status, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (K % 64 || R % 64 || K <= 0) return -20;
+  if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (dual && bn > 128) bn = 128;   // two accumulators: 2*BN tensor-memory columns, keep <= 256
+  if (splits < 1) splits = 1;
+  const int kb = K / 64 + R / 64;
+  while (splits > 1 && (splits > kb || bn % splits)) splits >>= 1;
+  const long long w_rows = dual ? (long long)up_off + F : F;
+  CUtensorMap mw, mx, mw2, mx2;
+  int rc;
+  if ((rc = make_map(&mw, W, w_rows, K, ldw, 128))) return rc;
+  if ((rc = make_map(&mx, X, M, K, ldx, bn))) return rc;
+  if (R > 0) {
+    if ((rc = make_map(&mw2, W2, w_rows, R, ldw2, 128))) return rc;
+    if ((rc = make_map(&mx2, X2, M, R, ldx2, bn))) return rc;
+  } else {
+    mw2 = mw;
+    mx2 = mx;
+  }
+  GemmParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ld_out = (int)ldo;
+  p.ld_res = (int)ldr;
+  p.M = M;
+  p.F = F;
+  p.up_off = up_off;
+  p.kb_main = K / 64;
+  p.kb_ext = R / 64;
+  p.splits = splits;
+  p.status = status;
+#define TAHB_LAUNCH(BN_)                                                              \
+  case BN_:                                                                           \
+    return dual ? launch<BN_, true>(mw, mx, mw2, mx2, p, stream) : launch<BN_, false>(mw, mx, mw2, mx2, p, stream);
+  switch (bn) {
+    TAHB_LAUNCH(16)
+    TAHB_LAUNCH(32)
+    TAHB_LAUNCH(64)
+    TAHB_LAUNCH(128)
+    case 256:
+      return dual ? -21 : launch<256, false>(mw, mx, mw2, mx2, p, stream);
+    default:
+      return -22;
+  }
+#undef TAHB_LAUNCH
+}

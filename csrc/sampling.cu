@@ -1,0 +1,412 @@
+// Per-tick control kernels of the decode engine: sorted top-k over the vocabulary, the soft
+// embedding mix for rows that iterate again, the top-k/top-p/min-p sampler, the continue/stop
+// decision, and the two scheduler kernels that advance every row's (token, depth, position)
+// state and allocate KV pages on the device.  None of them synchronises with the host, so a
+// whole decode tick is one CUDA graph.
+#include "common.cuh"
+
+namespace tahb {
+
+// ---------------------------------------------------------------------------------------------
+// Sorted top-k (k <= 128) of one bf16 row of V values per CTA, for rows whose flag is set.
+// Radix select on the 16-bit order-preserving key (two 256-bin histogram passes), then an
+// index-ordered gather (ties at the threshold are taken lowest index first, so the result is
+// deterministic), then a 128-wide bitonic sort by (value desc, index asc).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t order_key(__nv_bfloat16 v) {
+  const uint16_t u = __bfloat16_as_ushort(v);
+  return (u & 0x8000) ? (uint16_t)~u : (uint16_t)(u | 0x8000);
+}
+
+constexpr int TOPK_THREADS = 1024;
+
+__device__ __forceinline__ int find_bin(const int* hist, int want, int* above) {
+  // largest b with sum_{j > b} hist[j] < want <= sum_{j >= b} hist[j]
+  int acc = 0;
+  for (int b = 255; b >= 0; --b) {
+    if (acc + hist[b] >= want) { *above = acc; return b; }
+    acc += hist[b];
+  }
+  *above = acc;
+  return 0;
+}
+
+__global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const int* __restrict__ flag,
+                                                                 float* __restrict__ out_val,
+                                                                 int* __restrict__ out_idx, int V, int K,
+                                                                 long long ldx) {
+  const int r = blockIdx.x;
+  if (flag != nullptr && flag[r] == 0) return;
+  const __nv_bfloat16* xr = x + (size_t)r * ldx;
+  __shared__ int hist[256];
+  __shared__ int s_bin, s_above;
+  __shared__ int warp_cnt[2][32];
+  __shared__ uint32_t sel_key[128];
+  __shared__ int sel_idx[128];
+  __shared__ int s_ngt, s_neq;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // pass 1: high byte
+  if (tid < 256) hist[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < V; i += TOPK_THREADS) atomicAdd(&hist[order_key(xr[i]) >> 8], 1);
+  __syncthreads();
+  if (tid == 0) { int ab; s_bin = find_bin(hist, K, &ab); s_above = ab; }
+  __syncthreads();
+  const int b1 = s_bin;
+  const int above1 = s_above;
+  __syncthreads();
+  // pass 2: low byte among keys whose high byte is b1
+  if (tid < 256) hist[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < V; i += TOPK_THREADS) {
+    const uint32_t k = order_key(xr[i]);
+    if ((int)(k >> 8) == b1) atomicAdd(&hist[k & 255], 1);
+  }
+  __syncthreads();
+  if (tid == 0) { int ab; s_bin = find_bin(hist, K - above1, &ab); s_above = ab; s_ngt = 0; s_neq = 0; }
+  __syncthreads();
+  const uint32_t thr = ((uint32_t)b1 << 8) | (uint32_t)s_bin;
+  const int n_gt_total = above1 + s_above;     // keys strictly above the threshold (< K)
+  const int need_eq = K - n_gt_total;          // how many threshold ties to take (>= 1)
+  if (tid < 128) { sel_key[tid] = 0; sel_idx[tid] = 0x7fffffff; }
+  __syncthreads();
+
+  // pass 3: index-ordered gather
+  for (int base = 0; base < V; base += TOPK_THREADS) {
+    const int i = base + tid;
+    uint32_t k = 0;
+    bool gt = false, eq = false;
+    if (i < V) { k = order_key(xr[i]); gt = k > thr; eq = k == thr; }
+    const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) { warp_cnt[0][warp] = __popc(mg); warp_cnt[1][warp] = __popc(me); }
+    __syncthreads();
+    int og = s_ngt, oe = s_neq;
+    for (int w = 0; w < warp; ++w) { og += warp_cnt[0][w]; oe += warp_cnt[1][w]; }
+    og += __popc(mg & ((1u << lane) - 1));
+    oe += __popc(me & ((1u << lane) - 1));
+    if (gt && og < 128) { sel_key[og] = k; sel_idx[og] = i; }
+    if (eq && oe < need_eq) { const int slot = n_gt_total + oe; if (slot < 128) { sel_key[slot] = k; sel_idx[slot] = i; } }
+    __syncthreads();
+    if (tid == 0) {
+      int tg = 0, te = 0;
+      for (int w = 0; w < TOPK_THREADS / 32; ++w) { tg += warp_cnt[0][w]; te += warp_cnt[1][w]; }
+      s_ngt += tg; s_neq += te;
+    }
+    __syncthreads();
+  }
+  // bitonic sort of 128 (key desc, idx asc); empty slots have key 0 / idx max and sink to the end
+  for (int size = 2; size <= 128; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (tid < 128) {
+        const int partner = tid ^ stride;
+        if (partner > tid) {
+          const bool desc = (tid & size) == 0;
+          const uint32_t ka = sel_key[tid], kb = sel_key[partner];
+          const int ia = sel_idx[tid], ib = sel_idx[partner];
+          const bool a_first = (ka > kb) || (ka == kb && ia < ib);   // a should precede b in final order
+          if (desc ? !a_first : a_first) {
+            sel_key[tid] = kb; sel_key[partner] = ka; sel_idx[tid] = ib; sel_idx[partner] = ia;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (tid < K) {
+    const uint32_t k = sel_key[tid];
+    const uint16_t u = (k & 0x8000) ? (uint16_t)(k & 0x7fff) : (uint16_t)~k;
+    out_val[(size_t)r * K + tid] = __bfloat162float(__ushort_as_bfloat16(u));
+    out_idx[(size_t)r * K + tid] = sel_idx[tid];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Soft embedding: out[r] = bf16( sum_k bf16( bf16(softmax(val[r])_k) * E[idx[r,k]] ) ) for flagged rows.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) soft_embed_rows_kernel(const float* __restrict__ val,
+                                                              const int* __restrict__ idx,
+                                                              const int* __restrict__ flag,
+                                                              const __nv_bfloat16* __restrict__ E,
+                                                              __nv_bfloat16* __restrict__ out, int K, int H,
+                                                              long long ld_out) {
+  const int r = blockIdx.x;
+  if (flag != nullptr && flag[r] == 0) return;
+  __shared__ float prob[128];
+  __shared__ int id[128];
+  if (threadIdx.x < 32) {
+    float mx = -INFINITY;
+    for (int k = threadIdx.x; k < K; k += 32) mx = fmaxf(mx, val[(size_t)r * K + k]);
+    mx = warp_max(mx);
+    float s = 0.f;
+    for (int k = threadIdx.x; k < K; k += 32) s += __expf(val[(size_t)r * K + k] - mx);
+    s = warp_sum(s);
+    for (int k = threadIdx.x; k < K; k += 32) {
+      prob[k] = bf16_round(__expf(val[(size_t)r * K + k] - mx) / s);
+      id[k] = idx[(size_t)r * K + k];
+    }
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < K; ++k) {
+      const uint4 e = reinterpret_cast<const uint4*>(E + (size_t)id[k] * H)[v];
+      const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&e);
+      const float pk = prob[k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(eh[j]);
+        acc[2 * j] += bf16_round(pk * f.x);
+        acc[2 * j + 1] += bf16_round(pk * f.y);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(out + (size_t)r * ld_out)[v] = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sampler over a sorted top-k set (k <= 128): temperature -> softmax -> min_p -> (top_k is the set)
+// -> top_p -> draw.  Only ratios of probabilities matter after each renormalisation, so working
+// inside the top-k set is exact whenever top_k > 0.  One warp per row, lane 0 draws.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+__global__ void sample_topk_kernel(const float* __restrict__ val, const int* __restrict__ idx, int* __restrict__ out,
+                                   int rows, int K, float temperature, float top_p, float min_p,
+                                   unsigned long long seed, const int* __restrict__ step) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const float* v = val + (size_t)r * K;
+  const float inv_t = 1.0f / temperature;
+  float w[128];
+  float tot = 0.f;
+  int n = 0;
+  for (int k = 0; k < K; ++k) {
+    const float e = __expf((v[k] - v[0]) * inv_t);
+    if (min_p > 0.f && e < min_p) break;     // sorted: everything after is smaller too
+    w[k] = e;
+    tot += e;
+    n = k + 1;
+  }
+  if (top_p < 1.0f) {
+    float c = 0.f;
+    int keep = n;
+    for (int k = 0; k < n; ++k) {
+      c += w[k] / tot;
+      if (c > top_p) { keep = k + 1; break; }  // the token that crosses top_p is kept
+    }
+    n = keep;
+    tot = 0.f;
+    for (int k = 0; k < n; ++k) tot += w[k];
+  }
+  const uint64_t h = splitmix64(seed ^ splitmix64(((uint64_t)(step ? step[r] : 0) << 32) | (uint32_t)r));
+  const float u = (float)((h >> 40) + 0.5) * (1.0f / 16777216.0f) * tot;
+  float c = 0.f;
+  int pick = n - 1;
+  for (int k = 0; k < n; ++k) {
+    c += w[k];
+    if (u < c) { pick = k; break; }
+  }
+  out[r] = idx[(size_t)r * K + pick];
+}
+
+// ---------------------------------------------------------------------------------------------
+// Scheduler state of the iteration-level decode engine (one entry per batch row).
+// ---------------------------------------------------------------------------------------------
+struct TickState {
+  int* tok;        // token to feed at depth 0
+  int* depth;      // depth of the pass this tick runs for the row
+  int* pos;        // position id of the token being processed
+  int* finished;   // row has produced EOS
+  int* n_out;      // tokens emitted so far
+  int* out_tokens; // [rows, max_new]
+  int* iter_sum;   // passes spent on emitted tokens (for avg iteration count)
+  int* cur_iters;  // passes spent on the token in flight
+  int* slot;       // KV slot (page * page_size + off) of this tick's entry, in cache `depth`
+  int* gate;       // depth > 0 (LoRA on)
+  int* len[4];     // per-cache lengths
+  int* page_table[4];
+  int* free_stack[4];
+  int* free_count[4];
+  int max_pages[4];
+  int n_caches, page_size, rows, max_new, eos, max_iter;
+  int* status;
+  unsigned long long* tokens_done;   // global counter of emitted tokens
+};
+
+// Start of a tick: allocate this tick's KV slot in cache `depth` and build the input embedding
+// (embedding row of `tok` at depth 0, the soft embedding at depth >= 1).
+__global__ void __launch_bounds__(128) tick_begin_kernel(const TickState s, const __nv_bfloat16* __restrict__ E,
+                                                         const __nv_bfloat16* __restrict__ soft,
+                                                         __nv_bfloat16* __restrict__ x_in, int H) {
+  const int r = blockIdx.x;
+  const int d = s.depth[r];
+  if (threadIdx.x == 0) {
+    const int L = s.len[d][r];
+    int page;
+    if (L % s.page_size == 0) {
+      const int pi = L / s.page_size;
+      const int top = atomicSub(s.free_count[d], 1) - 1;
+      if (top < 0 || pi >= s.max_pages[d]) {
+        atomicAdd(s.free_count[d], 1);
+        atomicCAS(s.status, 0, STATUS_BAD_INDEX);
+        page = -1;
+      } else {
+        page = s.free_stack[d][top];
+        s.page_table[d][(size_t)r * s.max_pages[d] + pi] = page;
+      }
+    } else {
+      page = s.page_table[d][(size_t)r * s.max_pages[d] + L / s.page_size];
+    }
+    if (page >= 0) {
+      s.slot[r] = page * s.page_size + L % s.page_size;
+      s.len[d][r] = L + 1;
+    } else {
+      s.slot[r] = -1;
+    }
+    s.gate[r] = d > 0;
+  }
+  const uint4* src = (d == 0) ? reinterpret_cast<const uint4*>(E + (size_t)s.tok[r] * H)
+                              : reinterpret_cast<const uint4*>(soft + (size_t)r * H);
+  uint4* dst = reinterpret_cast<uint4*>(x_in + (size_t)r * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// Continue/stop decision.  override != nullptr: hard iff override[r, pos] > depth (scripted or
+// seeded-Bernoulli hard-token mask); else hard iff sigmoid(z) > threshold.  need_soft marks rows
+// that run another pass (they need top-k + soft embedding).
+__global__ void decide_kernel(const float* __restrict__ z, float threshold, const signed char* __restrict__ override_,
+                              int override_ld, const int* __restrict__ pos, const int* __restrict__ depth,
+                              int max_iter, int* __restrict__ need_soft, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int d = depth[r];
+  bool hard;
+  if (override_ != nullptr) {
+    const int p = min(pos[r], override_ld - 1);
+    hard = (int)override_[(size_t)r * override_ld + p] > d;
+  } else {
+    hard = z != nullptr && (1.0f / (1.0f + __expf(-z[r]))) > threshold;
+  }
+  need_soft[r] = (hard && d + 1 < max_iter) ? 1 : 0;
+}
+
+// End of a tick: rows that iterate again go one level deeper; the others emit `next_tok`
+// (never the EOS itself), return to depth 0 and advance their position.
+__global__ void tick_end_kernel(const TickState s, const int* __restrict__ need_soft, const int* __restrict__ next_tok) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= s.rows) return;
+  s.cur_iters[r] += 1;
+  if (need_soft[r]) {
+    s.depth[r] += 1;
+    return;
+  }
+  const int t = next_tok[r];
+  if (!s.finished[r]) {
+    if (t == s.eos) {
+      s.finished[r] = 1;
+    } else if (s.n_out[r] < s.max_new) {
+      s.out_tokens[(size_t)r * s.max_new + s.n_out[r]] = t;
+      s.n_out[r] += 1;
+      s.iter_sum[r] += s.cur_iters[r];
+      atomicAdd(s.tokens_done, 1ull);
+    }
+  }
+  s.cur_iters[r] = 0;
+  s.tok[r] = t;
+  s.depth[r] = 0;
+  s.pos[r] += 1;
+}
+
+}  // namespace tahb
+
+using namespace tahb;
+
+extern "C" int tahb_topk_rows(const void* x, const int* flag, float* out_val, int* out_idx, int rows, int V, int K,
+                              long long ldx, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (K < 1 || K > 128 || K > V) return -1;
+  topk_rows_kernel<<<rows, TOPK_THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), flag, out_val,
+                                                      out_idx, V, K, ldx);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_soft_embed_rows(const float* val, const int* idx, const int* flag, const void* E, void* out,
+                                    int rows, int K, int H, long long ld_out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (K > 128 || H % 8) return -1;
+  soft_embed_rows_kernel<<<rows, 256, 0, stream>>>(val, idx, flag, reinterpret_cast<const __nv_bfloat16*>(E),
+                                                   reinterpret_cast<__nv_bfloat16*>(out), K, H, ld_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_sample_topk(const float* val, const int* idx, int* out, int rows, int K, float temperature,
+                                float top_p, float min_p, unsigned long long seed, const int* step,
+                                cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (K > 128 || temperature <= 0.f) return -1;
+  sample_topk_kernel<<<(rows + 63) / 64, 64, 0, stream>>>(val, idx, out, rows, K, temperature, top_p, min_p, seed, step);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// The scheduler entry points take the state as an array of device pointers + ints, packed by the
+// Python engine in the order of the TickState fields.
+extern "C" int tahb_tick_begin(void* const* ptrs, const int* ints, const void* E, const void* soft, void* x_in, int H,
+                               cudaStream_t stream);
+extern "C" int tahb_tick_end(void* const* ptrs, const int* ints, const int* need_soft, const int* next_tok,
+                             cudaStream_t stream);
+
+static TickState unpack_state(void* const* p, const int* n) {
+  TickState s;
+  s.tok = (int*)p[0]; s.depth = (int*)p[1]; s.pos = (int*)p[2]; s.finished = (int*)p[3]; s.n_out = (int*)p[4];
+  s.out_tokens = (int*)p[5]; s.iter_sum = (int*)p[6]; s.cur_iters = (int*)p[7]; s.slot = (int*)p[8];
+  s.gate = (int*)p[9];
+  for (int c = 0; c < 4; ++c) {
+    s.len[c] = (int*)p[10 + c];
+    s.page_table[c] = (int*)p[14 + c];
+    s.free_stack[c] = (int*)p[18 + c];
+    s.free_count[c] = (int*)p[22 + c];
+    s.max_pages[c] = n[c];
+  }
+  s.status = (int*)p[26];
+  s.tokens_done = (unsigned long long*)p[27];
+  s.n_caches = n[4]; s.page_size = n[5]; s.rows = n[6]; s.max_new = n[7]; s.eos = n[8]; s.max_iter = n[9];
+  return s;
+}
+
+extern "C" int tahb_tick_begin(void* const* ptrs, const int* ints, const void* E, const void* soft, void* x_in, int H,
+                               cudaStream_t stream) {
+  TickState s = unpack_state(ptrs, ints);
+  if (s.rows <= 0) return 0;
+  tick_begin_kernel<<<s.rows, 128, 0, stream>>>(s, reinterpret_cast<const __nv_bfloat16*>(E),
+                                                reinterpret_cast<const __nv_bfloat16*>(soft),
+                                                reinterpret_cast<__nv_bfloat16*>(x_in), H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_decide(const float* z, float threshold, const signed char* override_, int override_ld,
+                           const int* pos, const int* depth, int max_iter, int* need_soft, int rows,
+                           cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  decide_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(z, threshold, override_, override_ld, pos, depth, max_iter,
+                                                        need_soft, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_tick_end(void* const* ptrs, const int* ints, const int* need_soft, const int* next_tok,
+                             cudaStream_t stream) {
+  TickState s = unpack_state(ptrs, ints);
+  if (s.rows <= 0) return 0;
+  tick_end_kernel<<<(s.rows + 127) / 128, 128, 0, stream>>>(s, need_soft, next_tok);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,304 @@
+"""ctypes bindings for the hand-written sm_100a kernels in ``csrc/`` (``libtahb200.so``).
+
+Every wrapper takes torch CUDA tensors, launches on the current torch stream and
+returns torch tensors.  The library is built in-tree by :mod:`tah_b200.ops.build`; if it
+is missing on a machine with a CUDA device, loading raises (no silent fallback).
+
+Kernels that wait on hardware barriers give up after a bounded time and set a status
+word; :func:`check_status` reads it (a host sync) and raises :class:`KernelTimeout`.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional, Sequence
+
+import torch
+
+_LIB = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libtahb200.so")
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+class KernelTimeout(RuntimeError):
+    pass
+
+
+STATUS_NAMES = {1: "timeout waiting for a TMA load", 2: "timeout waiting for a free pipeline stage",
+                3: "timeout waiting for the accumulator", 4: "timeout waiting for a peer flag",
+                5: "index out of range / KV pages exhausted"}
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(_LIB_PATH):
+            from tah_b200.ops.build import build
+            build()
+        _LIB = ctypes.CDLL(_LIB_PATH)
+        _LIB.tahb_decode_attn_ws_floats.restype = c_ll
+    return _LIB
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+_status = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    if dev.type != "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status[key]
+
+
+def check_status(device=None) -> None:
+    """Read the status word (synchronises) and raise if a kernel reported a failure."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise KernelTimeout(f"tah_b200 kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+def _rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed on the host side (code {rc})")
+
+
+def _check_bf16_2d(t: torch.Tensor, name: str):
+    if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
+        raise ValueError(f"{name}: need a 2-D bf16 CUDA tensor with unit inner stride, got {t.dtype} {tuple(t.shape)} {t.stride()}")
+
+
+# -------------------------------------------------------------------------------------------
+# GEMM
+# -------------------------------------------------------------------------------------------
+SM_COUNT = 148
+
+
+def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
+    """Split-K cluster size: fill the 148 SMs when the tile grid alone is too small (decode)."""
+    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+    if dual and bn > 128:
+        bn = 128
+    cols = bn * (2 if dual else 1)
+    stage = 16384 * (2 if dual else 1) + bn * 128
+    ns = min(8, (196 * 1024) // stage)
+    tiles = ((F + 127) // 128) * ((M + bn - 1) // bn)
+    kb = K // 64 + R // 64
+    s = 1
+    while s < 8 and tiles * s * 2 <= SM_COUNT and kb // (s * 2) >= 2 and bn % (s * 2) == 0 \
+            and cols * 512 <= ns * stage:
+        s *= 2
+    return s
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
+         w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
+         bn: int = 0) -> torch.Tensor:
+    """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
+    weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``."""
+    _check_bf16_2d(x, "x")
+    _check_bf16_2d(w, "w")
+    M, K = x.shape
+    F = w.shape[0] // 2 if swiglu else w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError(f"K mismatch: x {tuple(x.shape)} w {tuple(w.shape)}")
+    R = 0
+    if x2 is not None:
+        _check_bf16_2d(x2, "x2")
+        _check_bf16_2d(w2, "w2")
+        R = x2.shape[1]
+        if w2.shape[1] != R or w2.shape[0] != w.shape[0] or x2.shape[0] != M:
+            raise ValueError("K-extension operands do not match")
+    if out is None:
+        out = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
+    else:
+        _check_bf16_2d(out, "out")
+    if residual is not None:
+        _check_bf16_2d(residual, "residual")
+    if splits is None:
+        splits = pick_splits(M, F, K, R, swiglu)
+    rc = lib().tahb_gemm(_p(w), _p(x), _p(out), _p(residual), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R),
+                         c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
+                         c_ll(residual.stride(0) if residual is not None else 0),
+                         c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
+                         c_int(1 if swiglu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+                         _p(status_word(x.device)), _stream())
+    _rc(rc, "tahb_gemm")
+    return out
+
+
+# -------------------------------------------------------------------------------------------
+# elementwise / norm / rope
+# -------------------------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _check_bf16_2d(x, "x")
+    if out is None:
+        out = torch.empty_like(x)
+    _rc(lib().tahb_rmsnorm(_p(x), _p(w), _p(out), c_int(x.shape[0]), c_int(x.shape[1]), c_ll(x.stride(0)),
+                           c_ll(out.stride(0)), c_float(eps), _stream()), "tahb_rmsnorm")
+    return out
+
+
+def _ptr_array(tensors: Sequence[Optional[torch.Tensor]]):
+    arr = (c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = 0 if t is None else t.data_ptr()
+    return arr
+
+
+def qk_norm_rope_kv(qkv, q_w, k_w, pos, nq: int, nkv: int, hd: int, eps: float, theta: float, *,
+                    q_out=None, k_dense=None, v_dense=None, caches: Sequence[torch.Tensor] = (),
+                    cache_sel=None, slot=None, page_size: int = 16):
+    """Per-head QK RMSNorm + RoPE on a fused ``[M, (nq+2nkv)*hd]`` projection; writes normed/rotated
+    q to ``q_out``, K/V to ``k_dense``/``v_dense`` and/or into the paged cache(s) at ``slot``."""
+    _check_bf16_2d(qkv, "qkv")
+    M = qkv.shape[0]
+    if q_out is None:
+        q_out = torch.empty(M, nq * hd, dtype=torch.bfloat16, device=qkv.device)
+    arr = _ptr_array(list(caches)) if caches else (c_void_p * 1)()
+    _rc(lib().tahb_qk_norm_rope_kv(_p(qkv), _p(q_w), _p(k_w), _p(q_out), _p(k_dense), _p(v_dense), arr,
+                                   c_int(len(caches)), _p(cache_sel), _p(slot), _p(pos), c_int(M), c_int(nq),
+                                   c_int(nkv), c_int(hd), c_int(page_size), c_ll(qkv.stride(0)), c_float(eps),
+                                   c_float(theta), _stream()), "tahb_qk_norm_rope_kv")
+    return q_out
+
+
+def embed_gather(E, tok, out=None):
+    M, H = tok.shape[0], E.shape[1]
+    if out is None:
+        out = torch.empty(M, H, dtype=E.dtype, device=E.device)
+    _rc(lib().tahb_embed_gather(_p(E), _p(tok), _p(out), c_int(M), c_int(H), c_ll(out.stride(0)), _stream()),
+        "tahb_embed_gather")
+    return out
+
+
+def lora_a_rows(x, A, gate=None, out=None):
+    _check_bf16_2d(x, "x")
+    M, K = x.shape
+    R = A.shape[0]
+    if out is None:
+        out = torch.empty(M, R, dtype=torch.bfloat16, device=x.device)
+    _rc(lib().tahb_lora_a_rows(_p(x), _p(A), _p(out), _p(gate), c_int(M), c_int(K), c_int(R), c_ll(x.stride(0)),
+                               c_ll(out.stride(0)), _stream()), "tahb_lora_a_rows")
+    return out
+
+
+def swiglu(gate_up, out=None):
+    _check_bf16_2d(gate_up, "gate_up")
+    M, I2 = gate_up.shape
+    if out is None:
+        out = torch.empty(M, I2 // 2, dtype=torch.bfloat16, device=gate_up.device)
+    _rc(lib().tahb_swiglu(_p(gate_up), _p(out), c_int(M), c_int(I2 // 2), c_ll(gate_up.stride(0)),
+                          c_ll(out.stride(0)), _stream()), "tahb_swiglu")
+    return out
+
+
+def logits_post(logits, cum, depth, best):
+    _rc(lib().tahb_logits_post(_p(logits), _p(cum), _p(depth), _p(best), c_int(logits.shape[0]),
+                               c_int(logits.shape[1]), c_ll(logits.stride(0)), c_ll(cum.stride(0)), _stream()),
+        "tahb_logits_post")
+    return best
+
+
+# -------------------------------------------------------------------------------------------
+# attention
+# -------------------------------------------------------------------------------------------
+def decode_attn(q, caches: Sequence[torch.Tensor], page_tables: Sequence[torch.Tensor], lens: Sequence[torch.Tensor],
+                depth, nq: int, nkv: int, hd: int, page_size: int, scale: float, out=None, n_split: int = 1,
+                ws: Optional[torch.Tensor] = None):
+    rows = q.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    n = len(caches)
+    mp = (c_int * n)(*[pt.shape[1] for pt in page_tables])
+    if n_split > 1 and ws is None:
+        ws = torch.empty(int(lib().tahb_decode_attn_ws_floats(rows, nq, hd, n_split)), dtype=torch.float32, device=q.device)
+    _rc(lib().tahb_decode_attn(_p(q), _p(out), _ptr_array(caches), _ptr_array(page_tables), _ptr_array(lens), mp,
+                               c_int(n), _p(depth), c_int(rows), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
+                               c_float(scale), c_int(n_split), _p(ws), _stream()), "tahb_decode_attn")
+    return out
+
+
+def varlen_attn_naive(q, k0, v0, base0, count0, nq, nkv, hd, scale, k1=None, v1=None, base1=None, count1=None, out=None):
+    if out is None:
+        out = torch.empty_like(q)
+    _rc(lib().tahb_varlen_attn_naive(_p(q), _p(out), _p(k0), _p(v0), _p(k1), _p(v1), _p(base0), _p(count0), _p(base1),
+                                     _p(count1), c_int(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale),
+                                     _stream()), "tahb_varlen_attn_naive")
+    return out
+
+
+# -------------------------------------------------------------------------------------------
+# sampling / control
+# -------------------------------------------------------------------------------------------
+def topk_rows(x, k: int, flag=None, out_val=None, out_idx=None):
+    rows, V = x.shape
+    if out_val is None:
+        out_val = torch.zeros(rows, k, dtype=torch.float32, device=x.device)
+    if out_idx is None:
+        out_idx = torch.zeros(rows, k, dtype=torch.int32, device=x.device)
+    _rc(lib().tahb_topk_rows(_p(x), _p(flag), _p(out_val), _p(out_idx), c_int(rows), c_int(V), c_int(k),
+                             c_ll(x.stride(0)), _stream()), "tahb_topk_rows")
+    return out_val, out_idx
+
+
+def soft_embed_rows(val, idx, E, flag=None, out=None):
+    rows, K = val.shape
+    H = E.shape[1]
+    if out is None:
+        out = torch.zeros(rows, H, dtype=E.dtype, device=E.device)
+    _rc(lib().tahb_soft_embed_rows(_p(val), _p(idx), _p(flag), _p(E), _p(out), c_int(rows), c_int(K), c_int(H),
+                                   c_ll(out.stride(0)), _stream()), "tahb_soft_embed_rows")
+    return out
+
+
+def sample_topk(val, idx, temperature: float, top_p: float, min_p: float, seed: int, step=None, out=None):
+    rows, K = val.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=val.device)
+    _rc(lib().tahb_sample_topk(_p(val), _p(idx), _p(out), c_int(rows), c_int(K), c_float(temperature), c_float(top_p),
+                               c_float(min_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _p(step), _stream()),
+        "tahb_sample_topk")
+    return out
+
+
+def decide(z, threshold: float, override, pos, depth, max_iter: int, need_soft):
+    rows = need_soft.shape[0]
+    _rc(lib().tahb_decide(_p(z), c_float(threshold), _p(override), c_int(override.shape[1] if override is not None else 0),
+                          _p(pos), _p(depth), c_int(max_iter), _p(need_soft), c_int(rows), _stream()), "tahb_decide")
+    return need_soft
+
+
+class TickStateBinding:
+    """Packs the scheduler state tensors into the pointer/int arrays the tick kernels take."""
+
+    def __init__(self, tensors: List[Optional[torch.Tensor]], ints: List[int]):
+        assert len(tensors) == 28 and len(ints) == 10
+        self._keep = tensors
+        self.ptrs = _ptr_array(tensors)
+        self.ints = (c_int * len(ints))(*ints)
+
+    def tick_begin(self, E, soft, x_in):
+        _rc(lib().tahb_tick_begin(self.ptrs, self.ints, _p(E), _p(soft), _p(x_in), c_int(E.shape[1]), _stream()),
+            "tahb_tick_begin")
+
+    def tick_end(self, need_soft, next_tok):
+        _rc(lib().tahb_tick_end(self.ptrs, self.ints, _p(need_soft), _p(next_tok), _stream()), "tahb_tick_end")

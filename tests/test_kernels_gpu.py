@@ -1,0 +1,244 @@
+"""Numerics of the hand-written sm_100a kernels against plain PyTorch fp32 statements of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda():
+    from tah_b200.ops import cuda as K
+    return K
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(out, ref, atol, rtol):
+    torch.testing.assert_close(out.float(), ref.float(), atol=atol, rtol=rtol)
+
+
+GEMM_SHAPES = [(64, 256, 256), (16, 128, 64), (1, 128, 128), (100, 384, 512), (256, 4096, 2048), (300, 2048, 6144),
+               (64, 192, 2048), (130, 256, 320)]
+
+
+@pytest.mark.parametrize("M,F,K", GEMM_SHAPES)
+@pytest.mark.parametrize("splits", [1, None])
+def test_gemm_plain(M, F, K, splits):
+    Kc = _cuda()
+    x, w = _rand(M, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    out = Kc.gemm(x, w, splits=splits)
+    Kc.check_status()
+    _close(out, x.float() @ w.float().t(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,F,K,R", [(64, 256, 256, 64), (48, 4096, 2048, 192), (256, 2048, 6144, 64), (7, 128, 64, 128)])
+@pytest.mark.parametrize("splits", [1, None])
+def test_gemm_lora_extension_and_residual(M, F, K, R, splits):
+    Kc = _cuda()
+    x, w = _rand(M, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    t, b = _rand(M, R, seed=3), _rand(F, R, scale=R ** -0.5, seed=4)
+    res = _rand(M, F, seed=5)
+    out = Kc.gemm(x, w, x2=t, w2=b, residual=res, splits=splits)
+    Kc.check_status()
+    acc = x.float() @ w.float().t() + t.float() @ b.float().t()
+    ref = res.float() + acc.to(torch.bfloat16).float()
+    _close(out, ref, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(64, 768, 256), (16, 6144, 2048), (200, 1536, 512)])
+@pytest.mark.parametrize("splits", [1, None])
+def test_gemm_swiglu(M, I, K, splits):
+    Kc = _cuda()
+    x, w = _rand(M, K, seed=1), _rand(2 * I, K, scale=K ** -0.5, seed=2)
+    out = Kc.gemm(x, w, swiglu=True, splits=splits)
+    Kc.check_status()
+    gu = (x.float() @ w.float().t()).to(torch.bfloat16).float()
+    ref = torch.nn.functional.silu(gu[:, :I]).to(torch.bfloat16).float() * gu[:, I:]
+    _close(out, ref, atol=3e-2, rtol=3e-2)
+
+
+def test_gemm_strided_views():
+    Kc = _cuda()
+    big = _rand(64, 1024, seed=7)
+    x = big[:, 256:512]                     # row stride 1024, 512-byte offset (16-byte aligned)
+    w = _rand(256, 256, scale=1 / 16, seed=8)
+    out = Kc.gemm(x, w)
+    Kc.check_status()
+    _close(out, x.float() @ w.float().t(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,H", [(5, 256), (64, 2048), (33, 2560), (3, 6144)])
+def test_rmsnorm(M, H):
+    Kc = _cuda()
+    from tah_b200.ops import torch_ref
+    x, w = _rand(M, H, seed=1), (_rand(H, seed=2).float() * 0.1 + 1).to(torch.bfloat16)
+    _close(Kc.rms_norm(x, w, 1e-6), torch_ref.rms_norm(x, w, 1e-6), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("hd,nq,nkv", [(128, 16, 8), (64, 4, 2), (128, 32, 8)])
+def test_qk_norm_rope_and_paged_write(hd, nq, nkv):
+    Kc = _cuda()
+    from tah_b200.models.qwen3 import apply_rope, rope_cos_sin
+    from tah_b200.ops import torch_ref
+    M, page = 37, 16
+    qkv = _rand(M, (nq + 2 * nkv) * hd, seed=1)
+    qw, kw = (_rand(hd, seed=2).float() * 0.1 + 1).bfloat16(), (_rand(hd, seed=3).float() * 0.1 + 1).bfloat16()
+    pos = torch.randint(0, 5000, (M,), device="cuda", dtype=torch.int32)
+    n_pages = 8
+    cache = torch.zeros(n_pages, 2, nkv, page, hd, dtype=torch.bfloat16, device="cuda")
+    slot = torch.randperm(n_pages * page, device="cuda")[:M].to(torch.int32)
+    kd = torch.empty(M, nkv * hd, dtype=torch.bfloat16, device="cuda")
+    vd = torch.empty_like(kd)
+    q = Kc.qk_norm_rope_kv(qkv, qw, kw, pos, nq, nkv, hd, 1e-6, 1e6, k_dense=kd, v_dense=vd, caches=[cache],
+                           slot=slot, page_size=page)
+    qr, kr, vr = qkv.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
+    cos, sin = rope_cos_sin(pos[None].long(), hd, 1e6, torch.bfloat16)
+    q_ref = apply_rope(torch_ref.rms_norm(qr.view(1, M, nq, hd), qw, 1e-6), cos, sin)[0]
+    k_ref = apply_rope(torch_ref.rms_norm(kr.view(1, M, nkv, hd), kw, 1e-6), cos, sin)[0]
+    _close(q.view(M, nq, hd), q_ref, atol=3e-2, rtol=2e-2)
+    _close(kd.view(M, nkv, hd), k_ref, atol=3e-2, rtol=2e-2)
+    assert torch.equal(vd, vr.contiguous())
+    pg, off = (slot // page).long(), (slot % page).long()
+    assert torch.equal(cache[pg, 0, :, off], kd.view(M, nkv, hd))
+    assert torch.equal(cache[pg, 1, :, off], vd.view(M, nkv, hd))
+
+
+def _paged_setup(rows, lens, nkv, hd, page, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    max_pages = (max(lens) + page - 1) // page + 1
+    n_pages = rows * max_pages + 3
+    cache = (torch.randn(n_pages, 2, nkv, page, hd, generator=g, device="cuda")).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, device="cuda", generator=g)[: rows * max_pages].view(rows, max_pages).to(torch.int32)
+    return cache, perm, torch.tensor(lens, dtype=torch.int32, device="cuda")
+
+
+def _gather_paged(cache, pt, n, page):
+    ks, vs = [], []
+    for i in range(n):
+        pg = int(pt[i // page])
+        ks.append(cache[pg, 0, :, i % page])
+        vs.append(cache[pg, 1, :, i % page])
+    return torch.stack(ks), torch.stack(vs)     # [n, nkv, hd]
+
+
+@pytest.mark.parametrize("hd,nq,nkv", [(128, 16, 8), (64, 4, 2), (128, 32, 8)])
+@pytest.mark.parametrize("n_split", [1, 3])
+def test_decode_attention_two_caches(hd, nq, nkv, n_split):
+    Kc = _cuda()
+    rows, page = 5, 16
+    lens0, lens1 = [1, 17, 130, 64, 333], [0, 3, 0, 20, 1]
+    c0, pt0, l0 = _paged_setup(rows, lens0, nkv, hd, page, 1)
+    c1, pt1, l1 = _paged_setup(rows, lens1, nkv, hd, page, 2)
+    depth = torch.tensor([0, 1, 0, 1, 0], dtype=torch.int32, device="cuda")
+    q = _rand(rows, nq * hd, seed=3)
+    scale = hd ** -0.5
+    out = Kc.decode_attn(q, [c0, c1], [pt0, pt1], [l0, l1], depth, nq, nkv, hd, page, scale, n_split=n_split)
+    G = nq // nkv
+    for r in range(rows):
+        k, v = _gather_paged(c0, pt0[r], lens0[r], page)
+        if int(depth[r]) >= 1 and lens1[r] > 0:
+            k1, v1 = _gather_paged(c1, pt1[r], lens1[r], page)
+            k, v = torch.cat([k, k1]), torch.cat([v, v1])
+        qr = q[r].view(nq, hd).float()
+        kf = k.float().repeat_interleave(G, dim=1)
+        vf = v.float().repeat_interleave(G, dim=1)
+        s = torch.einsum("hd,nhd->hn", qr, kf) * scale
+        ref = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), vf)
+        _close(out[r].view(nq, hd), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_varlen_attention_duo_segments():
+    Kc = _cuda()
+    nq, nkv, hd = 4, 2, 64
+    seqlens = [9, 30, 1]
+    n0 = sum(seqlens)
+    starts = [0, 9, 39]
+    k0, v0 = _rand(n0, nkv * hd, seed=1), _rand(n0, nkv * hd, seed=2)
+    # depth-1 tokens: a subset of positions per sequence
+    hard = [[2, 7], [0, 5, 29], []]
+    q_list, b0, c0, b1, c1 = [], [], [], [], []
+    n1 = sum(len(h) for h in hard)
+    k1, v1 = _rand(n1, nkv * hd, seed=3), _rand(n1, nkv * hd, seed=4)
+    off1 = 0
+    for s, hs in enumerate(hard):
+        for j, p in enumerate(hs):
+            b0.append(starts[s]); c0.append(p + 1); b1.append(off1); c1.append(j + 1)
+        off1 += len(hs)
+    q = _rand(n1, nq * hd, seed=5)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    out = Kc.varlen_attn_naive(q, k0, v0, i32(b0), i32(c0), nq, nkv, hd, hd ** -0.5, k1=k1, v1=v1, base1=i32(b1), count1=i32(c1))
+    G = nq // nkv
+    for i in range(n1):
+        k = torch.cat([k0[b0[i]:b0[i] + c0[i]], k1[b1[i]:b1[i] + c1[i]]]).view(-1, nkv, hd).float().repeat_interleave(G, 1)
+        v = torch.cat([v0[b0[i]:b0[i] + c0[i]], v1[b1[i]:b1[i] + c1[i]]]).view(-1, nkv, hd).float().repeat_interleave(G, 1)
+        s = torch.einsum("hd,nhd->hn", q[i].view(nq, hd).float(), k) * hd ** -0.5
+        ref = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v)
+        _close(out[i].view(nq, hd), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("V,K", [(1024, 100), (151936, 100), (151936, 20), (5000, 1)])
+def test_topk_rows_sorted(V, K):
+    Kc = _cuda()
+    x = _rand(6, V, scale=3.0, seed=V)
+    flag = torch.tensor([1, 1, 0, 1, 1, 1], dtype=torch.int32, device="cuda")
+    val, idx = Kc.topk_rows(x, K, flag=flag)
+    ref_v, _ = torch.topk(x.float(), K, dim=-1)
+    keep = flag.bool()
+    assert torch.equal(val[keep], ref_v[keep])
+    assert torch.equal(torch.gather(x.float(), 1, idx.long())[keep], ref_v[keep])
+    assert (val[~keep] == 0).all()
+    # ties at equal value are ordered by index
+    same = val[keep][:, 1:] == val[keep][:, :-1]
+    assert (idx[keep][:, 1:][same] > idx[keep][:, :-1][same]).all()
+
+
+def test_soft_embed_and_logits_post():
+    Kc = _cuda()
+    from tah_b200.ops import torch_ref
+    V, H, K, rows = 4096, 512, 100, 4
+    E = _rand(V, H, seed=1)
+    logits = _rand(rows, V, scale=4.0, seed=2)
+    val, idx = Kc.topk_rows(logits, K)
+    out = Kc.soft_embed_rows(val, idx, E)
+    ref = torch_ref.topk_softmax_embed(logits, E, K)
+    _close(out, ref, atol=2e-2, rtol=2e-2)
+    cum = _rand(rows, V, seed=3)
+    cum0 = cum.clone()
+    depth = torch.tensor([0, 1, 0, 2], dtype=torch.int32, device="cuda")
+    best = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    Kc.logits_post(logits, cum, depth, best)
+    ref_cum = torch.where(depth[:, None] > 0, cum0 + logits, logits)
+    assert torch.equal(cum, ref_cum)
+    assert torch.equal(best.long(), ref_cum.float().argmax(-1))
+
+
+def test_lora_a_rows_and_swiglu():
+    Kc = _cuda()
+    x, A = _rand(9, 2048, seed=1), _rand(192, 2048, scale=2048 ** -0.5, seed=2)
+    gate = torch.tensor([0, 1, 0, 0, 1, 1, 0, 0, 1], dtype=torch.int32, device="cuda")
+    t = Kc.lora_a_rows(x, A, gate)
+    ref = (x.float() @ A.float().t()) * gate[:, None]
+    _close(t, ref, atol=2e-2, rtol=2e-2)
+    gu = _rand(11, 2 * 768, seed=3)
+    from tah_b200.ops import torch_ref
+    _close(Kc.swiglu(gu), torch_ref.swiglu(gu), atol=1e-2, rtol=1e-2)
+
+
+def test_sampler_topk_distribution():
+    Kc = _cuda()
+    rows, K = 4096, 8
+    val = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -2.0, -3.0, -9.0], device="cuda").repeat(rows, 1)
+    idx = torch.arange(K, dtype=torch.int32, device="cuda").repeat(rows, 1) + 10
+    step = torch.arange(rows, dtype=torch.int32, device="cuda")
+    out = Kc.sample_topk(val, idx, temperature=0.7, top_p=0.9, min_p=0.0, seed=123, step=step)
+    p = torch.softmax(val[0] / 0.7, -1)
+    c = p.cumsum(0)
+    n = int((c < 0.9).sum()) + 1
+    expect = p[:n] / p[:n].sum()
+    freq = torch.bincount(out.long() - 10, minlength=K).float() / rows
+    assert (freq[n:] == 0).all()
+    assert torch.allclose(freq[:n], expect, atol=0.03)
