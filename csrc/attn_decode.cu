@@ -68,7 +68,11 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const DecodeAttnParams
     for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
 
-  for (int base = begin + grp; base < end; base += 16 * U) {
+  // The trip count is the same for every lane of the CTA (groups past the end run masked
+  // iterations): the shuffles below name all 32 lanes, so no lane may leave the loop early.
+  const int n_steps = (end - begin + 16 * U - 1) / (16 * U);
+  for (int step = 0; step < n_steps; ++step) {
+    const int base = begin + grp + step * 16 * U;
     uint4 kreg[U][VEC], vreg[U][VEC];
     bool ok[U];
 #pragma unroll
@@ -198,7 +202,7 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, __nv_bflo
 
 // ---------------------------------------------------------------------------------------------
 // Plain varlen duo-causal attention over packed tokens (CUDA cores, one warp per (token, head)).
-// Query token i attends, in up to two segments s, KV rows  seg_base[s][i] + j  for
+// Query token i attends, in up to three segments s, KV rows  seg_base[s][i] + j  for
 // j < seg_count[s][i]  of the packed K/V tensors k[s]/v[s]  ([n, nkv, HD]).  Callers derive
 // (base, count) from the duo-causal rule: segment 0 = depth-0 K/V of the same sequence up to the
 // query's position, segment 1 = deeper K/V of the same sequence up to the query's own entry.
@@ -206,10 +210,10 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, __nv_bflo
 struct VarlenAttnParams {
   const __nv_bfloat16* q;
   __nv_bfloat16* out;
-  const __nv_bfloat16* k[2];
-  const __nv_bfloat16* v[2];
-  const int* seg_base[2];
-  const int* seg_count[2];
+  const __nv_bfloat16* k[3];
+  const __nv_bfloat16* v[3];
+  const int* seg_base[3];
+  const int* seg_count[3];
   int n_q, nq, nkv, n_seg;
   float scale_log2;
 };
@@ -299,18 +303,22 @@ extern "C" int tahb_decode_attn(const void* q, void* out, void* const* caches, c
   return -2;
 }
 
-extern "C" int tahb_varlen_attn_naive(const void* q, void* out, const void* k0, const void* v0, const void* k1,
-                                      const void* v1, const int* base0, const int* count0, const int* base1,
-                                      const int* count1, int n_q, int nq, int nkv, int hd, float scale,
-                                      cudaStream_t stream) {
+extern "C" int tahb_varlen_attn_naive(const void* q, void* out, void* const* ks, void* const* vs,
+                                      const int* const* bases, const int* const* counts, int n_seg, int n_q, int nq,
+                                      int nkv, int hd, float scale, cudaStream_t stream) {
   if (n_q <= 0) return 0;
+  if (n_seg < 1 || n_seg > 3) return -1;
   VarlenAttnParams p;
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  p.k[0] = reinterpret_cast<const __nv_bfloat16*>(k0); p.v[0] = reinterpret_cast<const __nv_bfloat16*>(v0);
-  p.k[1] = reinterpret_cast<const __nv_bfloat16*>(k1); p.v[1] = reinterpret_cast<const __nv_bfloat16*>(v1);
-  p.seg_base[0] = base0; p.seg_count[0] = count0; p.seg_base[1] = base1; p.seg_count[1] = count1;
-  p.n_q = n_q; p.nq = nq; p.nkv = nkv; p.n_seg = (k1 != nullptr) ? 2 : 1;
+  for (int s = 0; s < 3; ++s) {
+    const int ss = s < n_seg ? s : 0;
+    p.k[s] = reinterpret_cast<const __nv_bfloat16*>(ks[ss]);
+    p.v[s] = reinterpret_cast<const __nv_bfloat16*>(vs[ss]);
+    p.seg_base[s] = bases[ss];
+    p.seg_count[s] = counts[ss];
+  }
+  p.n_q = n_q; p.nq = nq; p.nkv = nkv; p.n_seg = n_seg;
   p.scale_log2 = scale * 1.4426950408889634f;
   const long long warps = (long long)n_q * nq;
   const int blocks = (int)((warps + 3) / 4);

@@ -1,0 +1,485 @@
+"""TaHEngine: KV-cached inference on the hand-written kernels.
+
+Two phases:
+
+* **prefill** - the prompts are packed (no padding) into one token stream; pass 0 runs the
+  backbone on all prompt tokens, the decider picks the hard ones, passes 1.. run on the packed
+  hard subset with the LoRA K-extension on, attending under the duo-causal rule over the dense
+  K/V of the earlier passes; every pass also writes its K/V into that depth's paged cache.
+* **decode** - *iteration-level continuous batching*: one "tick" processes exactly one token
+  per row, at whatever depth that row is at.  An easy row emits a token every tick; a hard row
+  spends ``1 + extra`` ticks on its token (soft embedding in, LoRA gated on for that row, K/V
+  into the deeper cache, logits accumulated).  Rows are independent, so every row's token
+  stream equals the reference schedule (two full-batch passes whenever any row is hard,
+  reference ``tah/model/utils.py:233-260`` + ``tah_model.py:580``), while the weights are read
+  once per tick for all rows.  A tick has static shapes and no host synchronisation: it is
+  captured once in a CUDA graph and replayed.
+
+The per-tick state (token, depth, position, KV lengths, page tables, free-page stacks, output
+buffers) lives on the device; see ``csrc/sampling.cu``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from tah_b200.engine.kv_cache import CacheGeometry, PagedKVCache
+from tah_b200.engine.weights import EngineWeights
+from tah_b200.model.iter_decider import (BernoulliIterDecider, IterLabelDecider, MLPIterDecider,
+                                         SimpleMLPIterDecider)
+from tah_b200.ops import cuda as K
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[List[int]]
+    iter_counts: List[float]            # mean passes per emitted token, per row
+    ticks: int = 0
+    tokens_emitted: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    extra: dict = field(default_factory=dict)
+
+
+class TaHEngine:
+    def __init__(self, model, max_rows: int = 64, max_seq_len: int = 2048, page_size: int = 16,
+                 deep_fraction: float = 0.25, use_cuda_graph: bool = True, tp=None):
+        self.model = model
+        base = model.simple_base_model
+        self.cfg = base.config
+        self.device = base.device
+        if self.device.type != "cuda":
+            raise RuntimeError("TaHEngine needs the model on a CUDA device")
+        self.max_iter = int(model.max_iter)
+        if self.max_iter > 4:
+            raise ValueError("the engine supports max_iter <= 4")
+        self.topk = int(model.input_topk)
+        self.tp = tp
+        self.w = EngineWeights(base, tp=tp)
+        self.max_rows, self.max_seq_len, self.page_size = max_rows, max_seq_len, page_size
+        self.deep_fraction = deep_fraction
+        self.use_cuda_graph = use_cuda_graph
+        self.kv: Optional[PagedKVCache] = None
+        self._graph = None
+        self._graph_key = None
+        self.hard_override: Optional[torch.Tensor] = None     # [rows, max_seq_len] int8: extra passes per position
+        inner = self._decider()[1]
+        thr = getattr(inner, "threshold", None)
+        self._thr = float(thr.detach().float().cpu()) if isinstance(thr, torch.Tensor) else 0.5
+        self.kernel_launches_per_tick = 0
+
+    # ------------------------------------------------------------------------------------------
+    # decider plumbing
+    # ------------------------------------------------------------------------------------------
+    def _decider(self):
+        d = self.model.eval_iter_decider or self.model.iter_decider
+        inner = d.inner if isinstance(d, BernoulliIterDecider) else d
+        return d, inner
+
+    def _tap_layers(self) -> Sequence[int]:
+        _, inner = self._decider()
+        if isinstance(inner, MLPIterDecider):
+            return list(inner.hidden_states_layer_nums)
+        if isinstance(inner, SimpleMLPIterDecider):
+            return list(inner.hidden_states_layer_nums[-1:]) or [self.cfg.num_hidden_layers]
+        return []
+
+    def _score(self, taps: Optional[torch.Tensor], topk_vals: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Decider logits ``z`` (fp32 ``[n]``) from tapped hidden states / sorted top-k values."""
+        _, inner = self._decider()
+        if isinstance(inner, MLPIterDecider):
+            return inner.score(taps, topk_vals.to(taps.dtype)).float()
+        if isinstance(inner, SimpleMLPIterDecider):
+            return inner.score(taps).float()
+        return None
+
+    def _needs_topk_for_decider(self) -> bool:
+        return isinstance(self._decider()[1], MLPIterDecider)
+
+    def make_bernoulli_override(self, rows: int, p: Sequence[float], seed: int = 0) -> torch.Tensor:
+        """Seeded hard-token mask: ``override[r, pos]`` = number of extra passes of the token at
+        ``pos`` (depth d continues with probability ``p[d]`` given it reached d)."""
+        g = torch.Generator().manual_seed(seed)
+        extra = torch.zeros(rows, self.max_seq_len, dtype=torch.int8)
+        alive = torch.ones(rows, self.max_seq_len, dtype=torch.bool)
+        for d in range(self.max_iter - 1):
+            pd = p[min(d, len(p) - 1)]
+            alive = alive & (torch.rand(rows, self.max_seq_len, generator=g) < pd)
+            extra += alive.to(torch.int8)
+        return extra.to(self.device)
+
+    # ------------------------------------------------------------------------------------------
+    # one backbone pass over packed tokens (prefill)
+    # ------------------------------------------------------------------------------------------
+    def _packed_pass(self, x, pos, depth: int, slots, seg_k, seg_v, seg_base, seg_count, taps_out=None):
+        """x ``[n, H]`` packed tokens at iteration ``depth``.  seg_k/seg_v: per layer lists of the
+        dense K/V of shallower passes; this pass's K/V are appended as the last segment.  Returns
+        (final-norm hidden, list of this pass's dense (k, v) per layer)."""
+        cfg, w = self.cfg, self.w
+        n = x.shape[0]
+        nq, nkv, hd = w.nq, w.nkv, cfg.head_dim
+        lora = depth >= 1 and w.r > 0
+        scale = hd ** -0.5
+        own = []
+        h = x
+        tap_layers = self._tap_layers()
+        for li, L in enumerate(w.layers):
+            if taps_out is not None and li in tap_layers:
+                taps_out[li] = h.clone()
+            xn = K.rms_norm(h, L.ln1, cfg.rms_norm_eps)
+            if lora:
+                t = K.gemm(xn, L.a_qkv)
+                qkv = K.gemm(xn, L.w_qkv, x2=t, w2=L.b_qkv)
+            else:
+                qkv = K.gemm(xn, L.w_qkv)
+            kd = torch.empty(n, nkv * hd, dtype=torch.bfloat16, device=x.device)
+            vd = torch.empty_like(kd)
+            q = K.qk_norm_rope_kv(qkv, L.q_norm, L.k_norm, pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
+                                  k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
+                                  page_size=self.page_size)
+            own.append((kd, vd))
+            ks = [sk[li] for sk in seg_k] + [kd]
+            vs = [sv[li] for sv in seg_v] + [vd]
+            o = K.varlen_attn_naive(q, ks, vs, seg_base, seg_count, nq, nkv, hd, scale)
+            o = w.tp_gather_heads(o)
+            if lora:
+                t = K.gemm(o, L.a_o)
+                h = K.gemm(o, L.w_o, x2=t, w2=L.b_o, residual=h)
+            else:
+                h = K.gemm(o, L.w_o, residual=h)
+            h = w.tp_reduce(h)
+            xn = K.rms_norm(h, L.ln2, cfg.rms_norm_eps)
+            if lora:
+                t = K.gemm(xn, L.a_gu)
+                act = K.gemm(xn, L.w_gu, x2=t, w2=L.b_gu, swiglu=True)
+                t = K.gemm(act, L.a_down)
+                h = K.gemm(act, L.w_down, x2=t, w2=L.b_down, residual=h)
+            else:
+                act = K.gemm(xn, L.w_gu, swiglu=True)
+                h = K.gemm(act, L.w_down, residual=h)
+            h = w.tp_reduce(h)
+        hn = K.rms_norm(h, w.final_norm, cfg.rms_norm_eps)
+        if taps_out is not None and cfg.num_hidden_layers in tap_layers:
+            taps_out[cfg.num_hidden_layers] = hn
+        return hn, own
+
+    # ------------------------------------------------------------------------------------------
+    # prefill
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor], max_new_tokens: int):
+        cfg, w, dev = self.cfg, self.w, self.device
+        B, T = input_ids.shape
+        valid = attention_mask[:, -T:].bool() if attention_mask is not None else torch.ones(B, T, dtype=torch.bool, device=dev)
+        lens = valid.sum(1)
+        max_total = int(lens.max()) + max_new_tokens + 1
+        if self.kv is None or self.kv.rows != B or self.kv.max_pages[0] * self.page_size < max_total:
+            geo = CacheGeometry(cfg.num_hidden_layers, w.nkv, cfg.head_dim, self.page_size)
+            self.kv = None
+            torch.cuda.empty_cache()
+            self.kv = PagedKVCache(geo, B, max(max_total, 1), self.max_iter, self.deep_fraction, dev)
+            self._graph = None
+        self.kv.reset()
+        rows_idx, cols_idx = valid.nonzero(as_tuple=True)
+        ids = input_ids[rows_idx, cols_idx].to(torch.int32).contiguous()
+        n0 = ids.numel()
+        seq_start = (torch.cumsum(lens, 0) - lens).to(torch.int32)
+        pos = (torch.arange(n0, device=dev, dtype=torch.int32) - seq_start[rows_idx]).contiguous()
+        seq = rows_idx.to(torch.int32)
+
+        # ---- pass 0 -------------------------------------------------------------------------
+        slots0 = self.kv.assign_prefill(0, lens)
+        x = K.embed_gather(w.embed, ids)
+        taps = {}
+        base0 = seq_start[rows_idx].contiguous()
+        count0 = (pos + 1).contiguous()
+        hn, kv0 = self._packed_pass(x, pos, 0, slots0, [], [], [base0], [count0], taps_out=taps)
+        seg_k, seg_v = [[k for k, _ in kv0]], [[v for _, v in kv0]]
+
+        # ---- continue decision for every prompt token ----------------------------------------
+        last_idx = (seq_start.long() + lens - 1)
+        is_last = torch.zeros(n0, dtype=torch.bool, device=dev)
+        is_last[last_idx] = True
+        extra = self._prompt_extra_passes(hn, taps, seq, pos)                 # [n0] int: extra passes wanted
+        cur_idx = torch.arange(n0, device=dev)                                # packed indices of the current set
+        cur_cum = None                                                        # cumulative logits of current set
+        final_last_logits = torch.empty(B, w.vocab, dtype=torch.bfloat16, device=dev)
+        # tokens needing logits after pass 0: last tokens + hard tokens
+        need0 = is_last | (extra > 0)
+        sel = need0.nonzero().flatten()
+        logits_sel = self._lm_head(hn[sel])
+        done_last = is_last[sel] & (extra[sel] == 0)
+        final_last_logits[seq[sel][done_last].long()] = logits_sel[done_last]
+        go = extra[sel] > 0
+        cur_idx = sel[go]
+        cur_cum = logits_sel[go]
+        prev_bases = [base0]
+        prev_counts = [count0]
+        depth = 1
+        iter_extra_prompt = extra.clone()
+        while depth < self.max_iter and cur_idx.numel() > 0:
+            n1 = cur_idx.numel()
+            rows1 = seq[cur_idx].long()
+            cnt1 = torch.bincount(rows1, minlength=B)
+            slots1 = self.kv.assign_prefill(depth, cnt1)
+            val, idx = K.topk_rows(cur_cum, self.topk)
+            x1 = K.soft_embed_rows(val, idx, w.embed)
+            pos1 = pos[cur_idx].contiguous()
+            start1 = (torch.cumsum(cnt1, 0) - cnt1).to(torch.int32)
+            rank1 = (torch.arange(n1, device=dev, dtype=torch.int32) - start1[rows1])
+            bases = [b[cur_idx].contiguous() for b in prev_bases] + [start1[rows1].contiguous()]
+            counts = [c[cur_idx].contiguous() for c in prev_counts] + [(rank1 + 1).contiguous()]
+            # shallower segments (1..depth-1) index into the packed arrays of those passes: their
+            # (base, count) were computed against those arrays when the passes ran
+            hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts)
+            logits1 = self._lm_head(hn1)
+            cum1 = cur_cum + logits1
+            want_more = (extra[cur_idx] > depth) & (depth + 1 < self.max_iter)
+            fin = ~want_more
+            lastfin = fin & is_last[cur_idx]
+            final_last_logits[rows1[lastfin]] = cum1[lastfin]
+            # next pass: subset of this one; its view of this pass's segment
+            seg_k.append([k for k, _ in kv1])
+            seg_v.append([v for _, v in kv1])
+            full_b = torch.zeros(n0, dtype=torch.int32, device=dev)
+            full_c = torch.zeros(n0, dtype=torch.int32, device=dev)
+            full_b[cur_idx] = bases[-1]
+            full_c[cur_idx] = counts[-1]
+            prev_bases.append(full_b)
+            prev_counts.append(full_c)
+            cur_idx = cur_idx[want_more]
+            cur_cum = cum1[want_more]
+            depth += 1
+        del seg_k, seg_v
+        return final_last_logits, lens, iter_extra_prompt
+
+    def _prompt_extra_passes(self, hn, taps, seq, pos) -> torch.Tensor:
+        """How many extra passes each prompt token takes (0 = easy)."""
+        n0 = hn.shape[0]
+        dev = hn.device
+        if self.max_iter <= 1:
+            return torch.zeros(n0, dtype=torch.int32, device=dev)
+        decider, inner = self._decider()
+        z = None
+        tl = self._tap_layers()
+        if isinstance(inner, (MLPIterDecider, SimpleMLPIterDecider)):
+            # scored in chunks: the MLP decider needs sorted top-k logits of every token
+            zs = []
+            step = 4096
+            for s in range(0, n0, step):
+                sl = slice(s, min(n0, s + step))
+                tcat = torch.cat([taps[i][sl] for i in tl], dim=-1) if tl else None
+                tv = None
+                if isinstance(inner, MLPIterDecider):
+                    tv, _ = K.topk_rows(self._lm_head(hn[sl]), inner.topk)
+                zs.append(self._score(tcat, tv))
+            z = torch.cat(zs)
+        if self.hard_override is not None:
+            return self.hard_override[seq.long(), pos.long()].to(torch.int32)
+        if isinstance(decider, BernoulliIterDecider):
+            raise RuntimeError("BernoulliIterDecider needs engine.hard_override (see make_bernoulli_override)")
+        if z is None:
+            return torch.zeros(n0, dtype=torch.int32, device=dev)
+        return (torch.sigmoid(z) > self._thr).to(torch.int32)
+
+    def _lm_head(self, hn: torch.Tensor) -> torch.Tensor:
+        out = K.gemm(hn.contiguous(), self.w.lm_head)
+        return self.w.tp_gather_vocab(out)
+
+    # ------------------------------------------------------------------------------------------
+    # decode tick
+    # ------------------------------------------------------------------------------------------
+    def _alloc_tick_buffers(self, B: int, max_new: int):
+        cfg, w, dev = self.cfg, self.w, self.device
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+        H = cfg.hidden_size
+        s = type("S", (), {})()
+        s.tok, s.depth, s.pos, s.finished, s.n_out = i32(B), i32(B), i32(B), i32(B), i32(B)
+        s.out_tokens, s.iter_sum, s.cur_iters, s.slot, s.gate = i32(B, max_new), i32(B), i32(B), i32(B), i32(B)
+        s.tokens_done = torch.zeros(1, dtype=torch.int64, device=dev)
+        s.need_soft, s.best, s.sampled = i32(B), i32(B), i32(B)
+        s.x_in, s.soft, s.h, s.xn = bf(B, H), bf(B, H), bf(B, H), bf(B, H)
+        s.qkv = bf(B, w.qkv_out)
+        s.q, s.o = bf(B, w.nq * cfg.head_dim), bf(B, w.nq * cfg.head_dim)
+        s.act = bf(B, w.inter)
+        s.t_qkv, s.t_o, s.t_gu, s.t_down = bf(B, w.r_qkv), bf(B, w.r_o), bf(B, w.r_gu), bf(B, w.r_down)
+        s.logits, s.cum = bf(B, w.vocab), bf(B, w.vocab)
+        s.topv = torch.zeros(B, self.topk, dtype=torch.float32, device=dev)
+        s.topi = i32(B, self.topk)
+        tl = self._tap_layers()
+        s.taps = bf(B, max(1, len(tl)) * H)
+        s.z = torch.zeros(B, dtype=torch.float32, device=dev)
+        kv = self.kv
+        pad = lambda lst: list(lst) + [lst[0]] * (4 - len(lst))
+        tensors = [s.tok, s.depth, s.pos, s.finished, s.n_out, s.out_tokens, s.iter_sum, s.cur_iters, s.slot, s.gate]
+        tensors += pad(kv.len) + pad(kv.page_table) + pad(kv.free_stack) + pad(kv.free_count)
+        tensors += [K.status_word(dev), s.tokens_done]
+        ints = pad(kv.max_pages) + [kv.n_depths, self.page_size, B, max_new, -1, self.max_iter]
+        s.ints = ints
+        s.tensors = tensors
+        return s
+
+    def _tick(self, s, sampling):
+        """Enqueue one decode tick on the current stream (graph-capturable)."""
+        cfg, w, kv = self.cfg, self.w, self.kv
+        B = s.tok.shape[0]
+        nq, nkv, hd = w.nq, w.nkv, cfg.head_dim
+        scale = hd ** -0.5
+        lora = w.r > 0 and self.max_iter > 1
+        tl = self._tap_layers()
+        H = cfg.hidden_size
+        s.binding.tick_begin(w.embed, s.soft, s.x_in)
+        h = s.x_in
+        pools = [[kv.layer_pool(d, li) for d in range(kv.n_depths)] for li in range(len(w.layers))]
+        for li, L in enumerate(w.layers):
+            if li in tl:
+                j = tl.index(li)
+                s.taps[:, j * H:(j + 1) * H].copy_(h)
+            K.rms_norm(h, L.ln1, cfg.rms_norm_eps, out=s.xn)
+            if lora:
+                K.lora_a_rows(s.xn, L.a_qkv, s.gate, out=s.t_qkv)
+                K.gemm(s.xn, L.w_qkv, x2=s.t_qkv, w2=L.b_qkv, out=s.qkv)
+            else:
+                K.gemm(s.xn, L.w_qkv, out=s.qkv)
+            K.qk_norm_rope_kv(s.qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
+                              q_out=s.q, caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size)
+            K.decode_attn(s.q, pools[li], kv.page_table, kv.len, s.depth, nq, nkv, hd, self.page_size, scale, out=s.o)
+            o = w.tp_gather_heads(s.o)
+            if lora:
+                K.lora_a_rows(o, L.a_o, s.gate, out=s.t_o)
+                K.gemm(o, L.w_o, x2=s.t_o, w2=L.b_o, residual=h, out=s.h)
+            else:
+                K.gemm(o, L.w_o, residual=h, out=s.h)
+            h = w.tp_reduce(s.h)
+            K.rms_norm(h, L.ln2, cfg.rms_norm_eps, out=s.xn)
+            if lora:
+                K.lora_a_rows(s.xn, L.a_gu, s.gate, out=s.t_gu)
+                K.gemm(s.xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act)
+                K.lora_a_rows(s.act, L.a_down, s.gate, out=s.t_down)
+                K.gemm(s.act, L.w_down, x2=s.t_down, w2=L.b_down, residual=h, out=s.h)
+            else:
+                K.gemm(s.xn, L.w_gu, swiglu=True, out=s.act)
+                K.gemm(s.act, L.w_down, residual=h, out=s.h)
+            h = w.tp_reduce(s.h)
+        K.rms_norm(h, w.final_norm, cfg.rms_norm_eps, out=s.xn)
+        if cfg.num_hidden_layers in tl:
+            j = tl.index(cfg.num_hidden_layers)
+            s.taps[:, j * H:(j + 1) * H].copy_(s.xn)
+        K.gemm(s.xn, w.lm_head, out=s.logits)
+        logits = w.tp_gather_vocab(s.logits)
+        K.logits_post(logits, s.cum, s.depth, s.best)
+        # decision
+        z = None
+        if self.max_iter > 1:
+            topk_done = False
+            if self._needs_topk_for_decider():
+                K.topk_rows(s.cum, self.topk, out_val=s.topv, out_idx=s.topi)
+                topk_done = True
+            zz = self._score(s.taps, s.topv)
+            if zz is not None:
+                s.z.copy_(zz)
+                z = s.z
+            K.decide(z, self._thr, self.hard_override, s.pos, s.depth, self.max_iter, s.need_soft)
+            if not topk_done:
+                K.topk_rows(s.cum, self.topk, flag=s.need_soft, out_val=s.topv, out_idx=s.topi)
+            K.soft_embed_rows(s.topv, s.topi, w.embed, flag=s.need_soft, out=s.soft)
+        nxt = s.best
+        if sampling is not None:
+            kk = sampling["top_k"]
+            val, idx = K.topk_rows(s.cum, kk)
+            K.sample_topk(val, idx, sampling["temperature"], sampling["top_p"], sampling["min_p"], sampling["seed"],
+                          step=s.pos, out=s.sampled)
+            nxt = s.sampled
+        s.binding.tick_end(s.need_soft, nxt)
+
+    # ------------------------------------------------------------------------------------------
+    # generate
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None, *,
+                 max_new_tokens: int = 128, do_sample: bool = False, temperature: float = 1.0, top_p: float = 1.0,
+                 top_k: int = 0, min_p: float = 0.0, eos_token_id: Optional[int] = None, seed: int = 0,
+                 max_ticks: Optional[int] = None, sync_every: int = 64, on_tick=None) -> GenerationResult:
+        dev = self.device
+        input_ids = input_ids.to(dev)
+        if attention_mask is not None:
+            attention_mask = attention_mask.to(dev)
+        B = input_ids.shape[0]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
+        last_logits, lens, _ = self.prefill(input_ids, attention_mask, max_new_tokens)
+        sampling = None
+        if do_sample:
+            if not (0 < top_k <= 128):
+                raise NotImplementedError("engine sampling needs 0 < top_k <= 128; use the loop path otherwise")
+            sampling = dict(temperature=temperature, top_p=top_p, min_p=min_p, top_k=top_k, seed=seed)
+        s = self._alloc_tick_buffers(B, max_new_tokens)
+        s.ints[8] = -1 if eos_token_id is None else int(eos_token_id)
+        s.binding = K.TickStateBinding(s.tensors, s.ints)
+        # first token from the prefill logits
+        if sampling is None:
+            first = last_logits.float().argmax(-1).to(torch.int32)
+        else:
+            val, idx = K.topk_rows(last_logits, top_k)
+            first = K.sample_topk(val, idx, temperature, top_p, min_p, seed, step=lens.to(torch.int32) - 1)
+        s.pos.copy_(lens.to(torch.int32) - 1)
+        s.need_soft.zero_()
+        s.binding.tick_end(s.need_soft, first)          # emits token 1, pos = len, depth = 0
+        s.cur_iters.zero_()
+        ev[1].record()
+        ticks = 0
+        limit = max_ticks if max_ticks is not None else max_new_tokens * self.max_iter + 1
+        if self.use_cuda_graph and limit > 0:
+            self._tick(s, sampling)            # eager tick: lazy one-time kernel setup happens outside capture
+            ticks = 1
+        run = self._tick_runner(s, sampling)
+        while ticks < limit:
+            run()
+            ticks += 1
+            if on_tick is not None:
+                on_tick(ticks, s)
+            if ticks % sync_every == 0 or ticks == limit:
+                done = bool(((s.finished != 0) | (s.n_out >= max_new_tokens)).all())
+                if done:
+                    break
+        ev[2].record()
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        n_out = s.n_out.tolist()
+        out = s.out_tokens.tolist()
+        iters = (s.iter_sum.float() / s.n_out.clamp(min=1).float()).tolist()
+        return GenerationResult(tokens=[row[:n] for row, n in zip(out, n_out)], iter_counts=iters, ticks=ticks,
+                                tokens_emitted=int(s.tokens_done.item()), prefill_ms=ev[0].elapsed_time(ev[1]),
+                                decode_ms=ev[1].elapsed_time(ev[2]))
+
+    def _tick_runner(self, s, sampling):
+        if not self.use_cuda_graph:
+            return lambda: self._tick(s, sampling)
+        # Capture records the launches of one tick without running them.  Everything a tick touches
+        # was allocated beforehand, so replays reuse the same addresses.
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                self._tick(s, sampling)
+        torch.cuda.current_stream().wait_stream(side)
+        self._graph = graph
+        return graph.replay
+
+
+_ENGINES = {}
+
+
+def get_engine(model, **kw) -> TaHEngine:
+    """One cached engine per model instance."""
+    key = id(model)
+    eng = _ENGINES.get(key)
+    if eng is None:
+        eng = TaHEngine(model, **kw)
+        _ENGINES[key] = eng
+    return eng

@@ -237,12 +237,15 @@ def decode_attn(q, caches: Sequence[torch.Tensor], page_tables: Sequence[torch.T
     return out
 
 
-def varlen_attn_naive(q, k0, v0, base0, count0, nq, nkv, hd, scale, k1=None, v1=None, base1=None, count1=None, out=None):
+def varlen_attn_naive(q, ks, vs, bases, counts, nq, nkv, hd, scale, out=None):
+    """Packed duo-causal attention: query i attends rows ``bases[s][i] + j, j < counts[s][i]`` of the
+    packed ``ks[s]``/``vs[s]`` for each of up to three segments ``s``."""
     if out is None:
         out = torch.empty_like(q)
-    _rc(lib().tahb_varlen_attn_naive(_p(q), _p(out), _p(k0), _p(v0), _p(k1), _p(v1), _p(base0), _p(count0), _p(base1),
-                                     _p(count1), c_int(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale),
-                                     _stream()), "tahb_varlen_attn_naive")
+    n = len(ks)
+    _rc(lib().tahb_varlen_attn_naive(_p(q), _p(out), _ptr_array(ks), _ptr_array(vs), _ptr_array(bases),
+                                     _ptr_array(counts), c_int(n), c_int(q.shape[0]), c_int(nq), c_int(nkv),
+                                     c_int(hd), c_float(scale), _stream()), "tahb_varlen_attn_naive")
     return out
 
 

@@ -170,7 +170,7 @@ def test_varlen_attention_duo_segments():
         off1 += len(hs)
     q = _rand(n1, nq * hd, seed=5)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
-    out = Kc.varlen_attn_naive(q, k0, v0, i32(b0), i32(c0), nq, nkv, hd, hd ** -0.5, k1=k1, v1=v1, base1=i32(b1), count1=i32(c1))
+    out = Kc.varlen_attn_naive(q, [k0, k1], [v0, v1], [i32(b0), i32(b1)], [i32(c0), i32(c1)], nq, nkv, hd, hd ** -0.5)
     G = nq // nkv
     for i in range(n1):
         k = torch.cat([k0[b0[i]:b0[i] + c0[i]], k1[b1[i]:b1[i] + c1[i]]]).view(-1, nkv, hd).float().repeat_interleave(G, 1)
