@@ -204,6 +204,17 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_smem_addr, uint32_t
   return v;
 }
 
+__device__ __forceinline__ float4 ld_dsmem_v4(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t raddr;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_smem_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(raddr)
+               : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------------------------------------
 // numerics
 // ---------------------------------------------------------------------------------------------

@@ -17,9 +17,10 @@
 //   DUAL       two accumulators per CTA, gate = rows f and up = rows up_off + f of W:
 //              out = bf16(silu(bf16(gate))) * bf16(up)             (SwiGLU)
 //
-// Split-K: a thread-block cluster of S CTAs along z splits the k-blocks; partial accumulators go
-// to each CTA's own shared memory and every CTA reduces a slice of the token columns from all
-// peers through distributed shared memory, in rank order (deterministic).  No global scratch.
+// Split-K: a thread-block cluster of S CTAs along z splits the k-blocks; the partial accumulators
+// of columns owned by other ranks go to the CTA's own shared memory, and every CTA adds to its own
+// slice (kept in tensor memory) the matching blocks of all peers, read through distributed shared
+// memory with 16-byte loads, in a fixed order (deterministic).  No global scratch.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31).
@@ -52,7 +53,8 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
   static constexpr int NS_RAW = (196 * 1024) / STAGE_BYTES;
   static constexpr int NS = NS_RAW > 8 ? 8 : NS_RAW;
-  static constexpr int COLS = BN * (DUAL ? 2 : 1);
+  static constexpr int NACC = DUAL ? 2 : 1;
+  static constexpr int COLS = BN * NACC;
   static constexpr int TMEM_COLS = COLS < 32 ? 32 : COLS;     // power of two >= 32 (BN is a power of two)
   static constexpr int SMEM_BYTES = NS * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
   static constexpr int CHUNK = BN >= 32 ? 32 : 16;
@@ -189,15 +191,29 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
       }
     } else {
-      // partial accumulator -> own shared memory, column-major [col][128 rows]
+      // Split-K: the token columns are dealt out to the S ranks (per = BN / S each, per
+      // accumulator).  A rank keeps its own columns in tensor memory and parks the columns that
+      // belong to rank d in shared-memory block j(d) = d - (d > rank), laid out [128 rows][NACC *
+      // per + 4] floats (the 4-float pad makes the float4 accesses bank-conflict free).
       float* red = reinterpret_cast<float*>(smem);
+      const int per = BN / S;
+      const int rs = C::NACC * per + 4;
 #pragma unroll 1
-      for (int c0 = 0; c0 < C::COLS; c0 += C::CHUNK) {
-        float a[C::CHUNK];
-        tmem_ld_chunk<C::CHUNK>(trow + c0, a);
-        tmem_ld_wait();
+      for (int d = 0; d < S; ++d) {
+        if (d == rank) continue;
+        float* blk = red + ((size_t)(d < rank ? d : d - 1) * 128 + row) * rs;
+#pragma unroll 1
+        for (int acc = 0; acc < C::NACC; ++acc) {
+#pragma unroll 1
+          for (int c = 0; c < per; c += 16) {
+            float a[16];
+            tmem_ld16(trow + acc * BN + d * per + c, a);
+            tmem_ld_wait();
+            float4* dst = reinterpret_cast<float4*>(blk + acc * per + c);
 #pragma unroll
-        for (int j = 0; j < C::CHUNK; ++j) red[(c0 + j) * 128 + row] = a[j];
+            for (int j = 0; j < 4; ++j) dst[j] = make_float4(a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
+          }
+        }
       }
     }
     tc_fence_before();
@@ -207,20 +223,47 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // every thread of every CTA in the cluster takes part in both barriers
     cluster_sync_all();
     if (warp >= 2) {
+      tc_fence_after();
       const int q = warp & 3;
       const int row = q * 32 + lane;
       const int f = f0 + row;
       const int per = BN / S;
+      const int rs = C::NACC * per + 4;
+      const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       const uint32_t red_addr = smem_u32(smem);
-      for (int c = rank * per; c < (rank + 1) * per; ++c) {
-        float a = 0.f, u = 0.f;
-        for (int r = 0; r < S; ++r) {
-          a += ld_dsmem_f32(red_addr + (c * 128 + row) * 4, r);
-          if constexpr (DUAL) u += ld_dsmem_f32(red_addr + ((BN + c) * 128 + row) * 4, r);
+#pragma unroll 1
+      for (int c = 0; c < per; c += 16) {
+        float a[16];
+        float u[DUAL ? 16 : 1];
+        tmem_ld16(trow + rank * per + c, a);
+        if constexpr (DUAL) tmem_ld16(trow + BN + rank * per + c, u);
+        tmem_ld_wait();
+#pragma unroll 1
+        for (int peer = 0; peer < S; ++peer) {
+          if (peer == rank) continue;
+          // block of peer's shared memory that holds the columns destined to this rank
+          const uint32_t addr = red_addr + ((((rank < peer ? rank : rank - 1) * 128 + row) * rs) + c) * 4;
+          float4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = ld_dsmem_v4(addr + j * 16, peer);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { a[4 * j] += v[j].x; a[4 * j + 1] += v[j].y; a[4 * j + 2] += v[j].z; a[4 * j + 3] += v[j].w; }
+          if constexpr (DUAL) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = ld_dsmem_v4(addr + per * 4 + j * 16, peer);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { u[4 * j] += v[j].x; u[4 * j + 1] += v[j].y; u[4 * j + 2] += v[j].z; u[4 * j + 3] += v[j].w; }
+          }
         }
-        const int t = t0 + c;
-        if (f < p.F && t < p.M) store_one<DUAL>(p, t, f, a, u);
+        if (f < p.F) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + rank * per + c + j;
+            if (t < p.M) store_one<DUAL>(p, t, f, a[j], DUAL ? u[j] : 0.f);
+          }
+        }
       }
+      tc_fence_before();
     }
     cluster_sync_all();
   }
@@ -277,7 +320,10 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -10;
     configured = true;
   }
-  if (p.splits > 1 && (size_t)C::COLS * 512 > (size_t)C::NS * C::STAGE_BYTES) return -11;
+  if (p.splits > 1) {
+    const int per = BN / p.splits;
+    if (per % 16 || (size_t)(p.splits - 1) * 128 * (C::NACC * per + 4) * 4 > (size_t)C::NS * C::STAGE_BYTES) return -11;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.F + 127) / 128, (p.M + BN - 1) / BN, p.splits);
   cfg.blockDim = dim3(192, 1, 1);
@@ -310,10 +356,9 @@ extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* re
   if (M <= 0 || F <= 0) return 0;
   if (K % 64 || R % 64 || K <= 0) return -20;
   if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  if (dual && bn > 128) bn = 128;   // two accumulators: 2*BN tensor-memory columns, keep <= 256
   if (splits < 1) splits = 1;
   const int kb = K / 64 + R / 64;
-  while (splits > 1 && (splits > kb || bn % splits)) splits >>= 1;
+  while (splits > 1 && (splits > kb || bn % splits || (bn / splits) % 16)) splits >>= 1;
   const long long w_rows = dual ? (long long)up_off + F : F;
   CUtensorMap mw, mx, mw2, mx2;
   int rc;
@@ -346,8 +391,7 @@ extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* re
     TAHB_LAUNCH(32)
     TAHB_LAUNCH(64)
     TAHB_LAUNCH(128)
-    case 256:
-      return dual ? -21 : launch<256, false>(mw, mx, mw2, mx2, p, stream);
+    TAHB_LAUNCH(256)
     default:
       return -22;
   }

@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bflo
   if (flag != nullptr && flag[r] == 0) return;
   const __nv_bfloat16* xr = x + (size_t)r * ldx;
   __shared__ int hist[256];
+  __shared__ int whist[TOPK_THREADS / 32][256];   // per-warp histograms: logits cluster in few bins
   __shared__ int s_bin, s_above;
   __shared__ int warp_cnt[2][32];
   __shared__ uint32_t sel_key[128];
@@ -48,9 +49,11 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bflo
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   // pass 1: high byte
-  if (tid < 256) hist[tid] = 0;
+  for (int i = tid; i < (TOPK_THREADS / 32) * 256; i += TOPK_THREADS) (&whist[0][0])[i] = 0;
   __syncthreads();
-  for (int i = tid; i < V; i += TOPK_THREADS) atomicAdd(&hist[order_key(xr[i]) >> 8], 1);
+  for (int i = tid; i < V; i += TOPK_THREADS) atomicAdd(&whist[warp][order_key(xr[i]) >> 8], 1);
+  __syncthreads();
+  if (tid < 256) { int t = 0; for (int w = 0; w < TOPK_THREADS / 32; ++w) t += whist[w][tid]; hist[tid] = t; }
   __syncthreads();
   if (tid == 0) { int ab; s_bin = find_bin(hist, K, &ab); s_above = ab; }
   __syncthreads();
@@ -58,12 +61,14 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bflo
   const int above1 = s_above;
   __syncthreads();
   // pass 2: low byte among keys whose high byte is b1
-  if (tid < 256) hist[tid] = 0;
+  for (int i = tid; i < (TOPK_THREADS / 32) * 256; i += TOPK_THREADS) (&whist[0][0])[i] = 0;
   __syncthreads();
   for (int i = tid; i < V; i += TOPK_THREADS) {
     const uint32_t k = order_key(xr[i]);
-    if ((int)(k >> 8) == b1) atomicAdd(&hist[k & 255], 1);
+    if ((int)(k >> 8) == b1) atomicAdd(&whist[warp][k & 255], 1);
   }
+  __syncthreads();
+  if (tid < 256) { int t = 0; for (int w = 0; w < TOPK_THREADS / 32; ++w) t += whist[w][tid]; hist[tid] = t; }
   __syncthreads();
   if (tid == 0) { int ab; s_bin = find_bin(hist, K - above1, &ab); s_above = ab; s_ngt = 0; s_neq = 0; }
   __syncthreads();
@@ -251,7 +256,14 @@ __global__ void __launch_bounds__(128) tick_begin_kernel(const TickState s, cons
                                                          __nv_bfloat16* __restrict__ x_in, int H) {
   const int r = blockIdx.x;
   const int d = s.depth[r];
-  if (threadIdx.x == 0) {
+  // a row that has finished (EOS or max_new tokens) keeps its slot in the batch but stops
+  // consuming KV pages: it recomputes over its existing cache and its outputs are ignored
+  const bool done = s.finished[r] != 0 || s.n_out[r] >= s.max_new;
+  if (threadIdx.x == 0 && done) {
+    s.slot[r] = -1;
+    s.gate[r] = d > 0;
+  }
+  if (threadIdx.x == 0 && !done) {
     const int L = s.len[d][r];
     int page;
     if (L % s.page_size == 0) {
@@ -306,6 +318,7 @@ __global__ void decide_kernel(const float* __restrict__ z, float threshold, cons
 __global__ void tick_end_kernel(const TickState s, const int* __restrict__ need_soft, const int* __restrict__ next_tok) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= s.rows) return;
+  if (s.finished[r] != 0 || s.n_out[r] >= s.max_new) return;   // done rows are frozen
   s.cur_iters[r] += 1;
   if (need_soft[r]) {
     s.depth[r] += 1;

@@ -21,6 +21,7 @@ buffers) lives on the device; see ``csrc/sampling.cu``.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -61,7 +62,7 @@ class TaHEngine:
         self.w = EngineWeights(base, tp=tp)
         self.max_rows, self.max_seq_len, self.page_size = max_rows, max_seq_len, page_size
         self.deep_fraction = deep_fraction
-        self.use_cuda_graph = use_cuda_graph
+        self.use_cuda_graph = use_cuda_graph and os.environ.get("TAH_B200_NO_GRAPH", "0") != "1"
         self.kv: Optional[PagedKVCache] = None
         self._graph = None
         self._graph_key = None

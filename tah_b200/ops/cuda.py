@@ -94,16 +94,18 @@ SM_COUNT = 148
 def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
     """Split-K cluster size: fill the 148 SMs when the tile grid alone is too small (decode)."""
     bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-    if dual and bn > 128:
-        bn = 128
-    cols = bn * (2 if dual else 1)
-    stage = 16384 * (2 if dual else 1) + bn * 128
+    nacc = 2 if dual else 1
+    stage = 16384 * nacc + bn * 128
     ns = min(8, (196 * 1024) // stage)
     tiles = ((F + 127) // 128) * ((M + bn - 1) // bn)
     kb = K // 64 + R // 64
+
+    def fits(s):
+        per = bn // s
+        return bn % s == 0 and per % 16 == 0 and (s - 1) * 128 * (nacc * per + 4) * 4 <= ns * stage
+
     s = 1
-    while s < 8 and tiles * s * 2 <= SM_COUNT and kb // (s * 2) >= 2 and bn % (s * 2) == 0 \
-            and cols * 512 <= ns * stage:
+    while s < 8 and tiles * s * 2 <= SM_COUNT and kb // (s * 2) >= 2 and fits(s * 2):
         s *= 2
     return s
 

@@ -23,7 +23,7 @@ def _setup(max_iter=2, B=3, T=20, n_new=24, p=(0.3,)):
     ref = copy.deepcopy(model).float()
     ref.iter_decider = ref.eval_iter_decider = type(ref.iter_decider)(max_iter=max_iter)
     model = model.cuda().eval()
-    eng = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, use_cuda_graph=True)
+    eng = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, use_cuda_graph=True, deep_fraction=1.0)
     eng.hard_override = eng.make_bernoulli_override(B, p, seed=5)
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 1024, (B, T), generator=g)

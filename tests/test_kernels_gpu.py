@@ -35,7 +35,7 @@ def test_gemm_plain(M, F, K, splits):
     _close(out, x.float() @ w.float().t(), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M,F,K,R", [(64, 256, 256, 64), (48, 4096, 2048, 192), (256, 2048, 6144, 64), (7, 128, 64, 128)])
+@pytest.mark.parametrize("M,F,K,R", [(64, 256, 256, 64), (48, 4096, 2048, 192), (256, 2048, 6144, 64), (7, 128, 64, 128), (256, 4096, 2048, 192), (128, 2048, 2048, 64)])
 @pytest.mark.parametrize("splits", [1, None])
 def test_gemm_lora_extension_and_residual(M, F, K, R, splits):
     Kc = _cuda()
@@ -49,7 +49,7 @@ def test_gemm_lora_extension_and_residual(M, F, K, R, splits):
     _close(out, ref, atol=3e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M,I,K", [(64, 768, 256), (16, 6144, 2048), (200, 1536, 512)])
+@pytest.mark.parametrize("M,I,K", [(64, 768, 256), (16, 6144, 2048), (200, 1536, 512), (256, 6144, 2048), (130, 768, 2048)])
 @pytest.mark.parametrize("splits", [1, None])
 def test_gemm_swiglu(M, I, K, splits):
     Kc = _cuda()
