@@ -42,7 +42,9 @@ struct GemmParams {
   int kb_main;  // K / 64
   int kb_ext;   // R / 64
   int splits;   // cluster size along z (1 = no split-K)
+  int tma_out;  // 1: stage the output tile in shared memory and write it with a TMA store
   int* status;
+  unsigned long long* trace;   // optional [n_ctas][8] globaltimer stamps (debug aid), else nullptr
 };
 
 template <int BN, bool DUAL>
@@ -78,10 +80,30 @@ __device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, flo
   p.out[(size_t)t * p.ld_out + f] = __float2bfloat16_rn(y);
 }
 
+// Epilogue value into the shared staging tile; with `add_res` the slot already holds the residual
+// element (brought in by a TMA load).
+template <bool DUAL>
+__device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u, bool add_res) {
+  float y;
+  if constexpr (DUAL) {
+    y = bf16_round(silu(bf16_round(a))) * bf16_round(u);
+  } else {
+    y = a;
+    if (add_res) y = bf16_round(a) + __bfloat162float(*slot);
+  }
+  *slot = __float2bfloat16_rn(y);
+}
+
+// bytes of the split-K receive area: (S - 1) source blocks of [cols_per_rank][128] floats
+__host__ __device__ constexpr int split_stage_offset(int S, int cols_per_rank) {
+  return (((S - 1) * 128 * cols_per_rank * 4) + 1023) & ~1023;
+}
+
 template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192, 1)
 gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_x2,
+               const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
                const GemmParams p) {
   using C = GemmCfg<BN, DUAL>;
   extern __shared__ uint8_t smem_raw[];
@@ -89,7 +111,8 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::NS * C::STAGE_BYTES);
   uint64_t* empty_bar = full_bar + C::NS;
   uint64_t* accum_bar = empty_bar + C::NS;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* res_bar = accum_bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -109,6 +132,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(accum_bar, 1);
+    mbar_init(res_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tensormap(&tm_w);
@@ -122,6 +146,8 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 0] = globaltimer_ns();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -174,7 +200,17 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     mbar_wait(accum_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
     tc_fence_after();
+    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 1] = globaltimer_ns();
     if (S == 1) {
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [BN tokens][128 features]
+      const bool res_tma = p.tma_out && p.residual != nullptr;
+      if (res_tma) {
+        if (threadIdx.x == 64) {
+          mbar_expect_tx(res_bar, BN * 256);
+          tma_load_2d(stg, &tm_res, f0, t0, res_bar);
+        }
+        mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += C::CHUNK) {
         float a[C::CHUNK];
@@ -182,7 +218,11 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tmem_ld_chunk<C::CHUNK>(trow + c0, a);
         if constexpr (DUAL) tmem_ld_chunk<C::CHUNK>(trow + BN + c0, u);
         tmem_ld_wait();
-        if (f < p.F) {
+        if (p.tma_out) {
+#pragma unroll
+          for (int j = 0; j < C::CHUNK; ++j)
+            stage_one<DUAL>(stg + (c0 + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
+        } else if (f < p.F) {
 #pragma unroll
           for (int j = 0; j < C::CHUNK; ++j) {
             const int t = t0 + c0 + j;
@@ -190,29 +230,13 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
-    } else {
-      // Split-K: the token columns are dealt out to the S ranks (per = BN / S each, per
-      // accumulator).  A rank keeps its own columns in tensor memory and parks the columns that
-      // belong to rank d in shared-memory block j(d) = d - (d > rank), laid out [128 rows][NACC *
-      // per + 4] floats (the 4-float pad makes the float4 accesses bank-conflict free).
-      float* red = reinterpret_cast<float*>(smem);
-      const int per = BN / S;
-      const int rs = C::NACC * per + 4;
-#pragma unroll 1
-      for (int d = 0; d < S; ++d) {
-        if (d == rank) continue;
-        float* blk = red + ((size_t)(d < rank ? d : d - 1) * 128 + row) * rs;
-#pragma unroll 1
-        for (int acc = 0; acc < C::NACC; ++acc) {
-#pragma unroll 1
-          for (int c = 0; c < per; c += 16) {
-            float a[16];
-            tmem_ld16(trow + acc * BN + d * per + c, a);
-            tmem_ld_wait();
-            float4* dst = reinterpret_cast<float4*>(blk + acc * per + c);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) dst[j] = make_float4(a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
-          }
+      if (p.tma_out) {
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) {
+          tma_store_2d(&tm_out, stg, f0, t0);
+          tma_store_commit();
+          tma_store_wait_read();
         }
       }
     }
@@ -220,8 +244,45 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   }
 
   if (S > 1) {
-    // every thread of every CTA in the cluster takes part in both barriers
+    // Split-K reduction.  The token columns are dealt out to the S ranks (per = BN / S each, per
+    // accumulator).  After a first cluster barrier (every CTA has finished its main loop, so the
+    // pipeline buffers are free) a rank PUSHES the partial columns owned by rank d into d's shared
+    // memory (remote stores need no round trip), block index = source rank - (source > d), laid
+    // out [NACC * per columns][128 rows] floats; after a second barrier each rank adds the received
+    // blocks to its own columns, which never left tensor memory, in a fixed order.  Every thread
+    // of every CTA takes part in both barriers.
     cluster_sync_all();
+    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 4] = globaltimer_ns();
+    if (warp >= 2) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int row = q * 32 + lane;
+      const int per = BN / S;
+      const int rs = C::NACC * per + 4;
+      const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t red_addr = smem_u32(smem);
+#pragma unroll 1
+      for (int d = 0; d < S; ++d) {
+        if (d == rank) continue;
+        // block of rank d's shared memory reserved for this source: [NACC * per columns][128 rows];
+        // the 32 lanes of a warp write 32 consecutive floats, i.e. one 128-byte remote packet
+        const uint32_t dst = dsmem_addr(red_addr + ((rank < d ? rank : rank - 1) * C::NACC * per * 128 + row) * 4, d);
+#pragma unroll 1
+        for (int acc = 0; acc < C::NACC; ++acc) {
+#pragma unroll 1
+          for (int c = 0; c < per; c += 16) {
+            float a[16];
+            tmem_ld16(trow + acc * BN + d * per + c, a);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) st_dsmem_f32(dst + ((acc * per + c + j) * 128) * 4, a[j]);
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    cluster_sync_all();
+    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 5] = globaltimer_ns();
     if (warp >= 2) {
       tc_fence_after();
       const int q = warp & 3;
@@ -230,7 +291,17 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const int per = BN / S;
       const int rs = C::NACC * per + 4;
       const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      const uint32_t red_addr = smem_u32(smem);
+      const float* red = reinterpret_cast<const float*>(smem);
+      // output staging tile [per tokens][128 features] lives behind the received blocks
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + split_stage_offset(S, C::NACC * per));
+      const bool res_tma = p.tma_out && p.residual != nullptr;
+      if (res_tma) {
+        if (threadIdx.x == 64) {
+          mbar_expect_tx(res_bar, per * 256);
+          tma_load_2d(stg, &tm_res, f0, t0 + rank * per, res_bar);
+        }
+        mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
+      }
 #pragma unroll 1
       for (int c = 0; c < per; c += 16) {
         float a[16];
@@ -239,23 +310,19 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if constexpr (DUAL) tmem_ld16(trow + BN + rank * per + c, u);
         tmem_ld_wait();
 #pragma unroll 1
-        for (int peer = 0; peer < S; ++peer) {
-          if (peer == rank) continue;
-          // block of peer's shared memory that holds the columns destined to this rank
-          const uint32_t addr = red_addr + ((((rank < peer ? rank : rank - 1) * 128 + row) * rs) + c) * 4;
-          float4 v[4];
+        for (int blk = 0; blk < S - 1; ++blk) {
+          const float* src = red + ((size_t)blk * C::NACC * per + c) * 128 + row;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) v[j] = ld_dsmem_v4(addr + j * 16, peer);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) { a[4 * j] += v[j].x; a[4 * j + 1] += v[j].y; a[4 * j + 2] += v[j].z; a[4 * j + 3] += v[j].w; }
+          for (int j = 0; j < 16; ++j) a[j] += src[j * 128];
           if constexpr (DUAL) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = ld_dsmem_v4(addr + per * 4 + j * 16, peer);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { u[4 * j] += v[j].x; u[4 * j + 1] += v[j].y; u[4 * j + 2] += v[j].z; u[4 * j + 3] += v[j].w; }
+            for (int j = 0; j < 16; ++j) u[j] += src[(per + j) * 128];
           }
         }
-        if (f < p.F) {
+        if (p.tma_out) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stage_one<DUAL>(stg + (c + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
+        } else if (f < p.F) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = t0 + rank * per + c + j;
@@ -263,12 +330,23 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
+      if (p.tma_out) {
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) {
+          tma_store_2d(&tm_out, stg, f0, t0 + rank * per);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+      }
       tc_fence_before();
     }
-    cluster_sync_all();
+    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 6] = globaltimer_ns();
   }
 
+  if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 2] = globaltimer_ns();
   __syncthreads();
+  if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 3] = globaltimer_ns();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -295,24 +373,26 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2D bf16 row-major [rows, cols] with leading dimension ld (elements); box = {64, box_rows}, 128B swizzle.
-static int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+// 2D bf16 row-major [rows, cols] with leading dimension ld (elements).  Operand maps use a
+// {64, box_rows} box with the 128-byte swizzle; output/residual maps a {128, box_rows} box, unswizzled.
+static int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows,
+                    bool operand) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {operand ? 64u : 128u, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
 template <int BN, bool DUAL>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mw2, const CUtensorMap& mx2,
-                  const GemmParams& p, cudaStream_t stream) {
+                  const CUtensorMap& mo, const CUtensorMap& mr, const GemmParams& p, cudaStream_t stream) {
   using C = GemmCfg<BN, DUAL>;
   static bool configured = false;
   auto kern = gemm_fl_kernel<BN, DUAL>;
@@ -322,7 +402,9 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
   }
   if (p.splits > 1) {
     const int per = BN / p.splits;
-    if (per % 16 || (size_t)(p.splits - 1) * 128 * (C::NACC * per + 4) * 4 > (size_t)C::NS * C::STAGE_BYTES) return -11;
+    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 >
+                        (size_t)C::NS * C::STAGE_BYTES)
+      return -11;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.F + 127) / 128, (p.M + BN - 1) / BN, p.splits);
@@ -336,13 +418,18 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
   attr[0].val.clusterDim.z = p.splits;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, mw2, mx2, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, mw2, mx2, mo, mr, p);
   return e == cudaSuccess ? 0 : -12;
 }
 
 }  // namespace tahb
 
 using namespace tahb;
+
+static unsigned long long* g_gemm_trace = nullptr;
+// Debug aid: when set, every GEMM CTA writes four globaltimer stamps (set-up done, accumulator
+// ready, epilogue done, after the final CTA barrier) to trace[cta * 8 ..].
+extern "C" void tahb_gemm_set_trace(unsigned long long* trace) { g_gemm_trace = trace; }
 
 // out[M, F] = X[M, K] W[F, K]^T (+ X2[M, R] W2[F, R]^T) (+ residual) ; dual != 0 => SwiGLU over W rows
 // [0, F) (gate) and [up_off, up_off + F) (up).  All matrices bf16 row-major; K and R multiples of 64.
@@ -362,16 +449,23 @@ extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* re
   const long long w_rows = dual ? (long long)up_off + F : F;
   CUtensorMap mw, mx, mw2, mx2;
   int rc;
-  if ((rc = make_map(&mw, W, w_rows, K, ldw, 128))) return rc;
-  if ((rc = make_map(&mx, X, M, K, ldx, bn))) return rc;
+  if ((rc = make_map(&mw, W, w_rows, K, ldw, 128, true))) return rc;
+  if ((rc = make_map(&mx, X, M, K, ldx, bn, true))) return rc;
   if (R > 0) {
-    if ((rc = make_map(&mw2, W2, w_rows, R, ldw2, 128))) return rc;
-    if ((rc = make_map(&mx2, X2, M, R, ldx2, bn))) return rc;
+    if ((rc = make_map(&mw2, W2, w_rows, R, ldw2, 128, true))) return rc;
+    if ((rc = make_map(&mx2, X2, M, R, ldx2, bn, true))) return rc;
   } else {
     mw2 = mw;
     mx2 = mx;
   }
+  // output (and residual) through TMA when their layout allows it, else element-wise stores
+  CUtensorMap mo, mr;
+  int tma_out = make_map(&mo, out, M, F, ldo, bn / splits, false) == 0;
+  if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F, ldr, bn / splits, false) == 0;
+  if (!tma_out) mo = mw;
+  if (!tma_out || residual == nullptr) mr = mo;
   GemmParams p;
+  p.tma_out = tma_out;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ld_out = (int)ldo;
@@ -383,9 +477,10 @@ extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* re
   p.kb_ext = R / 64;
   p.splits = splits;
   p.status = status;
+  p.trace = g_gemm_trace;
 #define TAHB_LAUNCH(BN_)                                                              \
   case BN_:                                                                           \
-    return dual ? launch<BN_, true>(mw, mx, mw2, mx2, p, stream) : launch<BN_, false>(mw, mx, mw2, mx2, p, stream);
+    return dual ? launch<BN_, true>(mw, mx, mw2, mx2, mo, mr, p, stream) : launch<BN_, false>(mw, mx, mw2, mx2, mo, mr, p, stream);
   switch (bn) {
     TAHB_LAUNCH(16)
     TAHB_LAUNCH(32)

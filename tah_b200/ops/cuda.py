@@ -91,23 +91,50 @@ def _check_bf16_2d(t: torch.Tensor, name: str):
 SM_COUNT = 148
 
 
-def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
-    """Split-K cluster size: fill the 148 SMs when the tile grid alone is too small (decode)."""
-    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-    nacc = 2 if dual else 1
+def _fits(bn: int, s: int, nacc: int) -> bool:
     stage = 16384 * nacc + bn * 128
     ns = min(8, (196 * 1024) // stage)
-    tiles = ((F + 127) // 128) * ((M + bn - 1) // bn)
+    if s == 1:
+        return True
+    per = bn // s
+    if bn % s or per % 16:
+        return False
+    red = ((s - 1) * 128 * nacc * per * 4 + 1023) // 1024 * 1024
+    return red + per * 256 <= ns * stage
+
+
+def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
+    """Pick the token-tile width and the split-K cluster size with a small cost model.
+
+    Measured on B200: a k-block (64 of K) costs about 0.3 us of load latency per CTA unless the
+    tensor-core time of the tile is larger, the epilogue about 0.5 us + 8 ns per token column,
+    and clusters larger than 4 CTAs (one ~200 KB CTA per SM) no longer fit in one wave.
+    """
+    nacc = 2 if dual else 1
     kb = K // 64 + R // 64
+    base = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+    cands = [base] + ([128, 64] if base == 256 else [64] if base == 128 else [])
+    best = None
+    for bn in cands:
+        for s in (1, 2, 4):
+            if s > 1 and (kb // s < 2 or not _fits(bn, s, nacc)):
+                continue
+            ctas = ((F + 127) // 128) * ((M + bn - 1) // bn) * s
+            waves = (ctas + SM_COUNT - 1) // SM_COUNT
+            t_kb = max(0.30, 128 * bn * 64 * 2 * nacc / 8192 / 1900.0)
+            per = bn // s
+            t_cta = (kb / s) * t_kb + 0.5 + 0.009 * per
+            if s > 1:
+                pushed_kb = (s - 1) * per * nacc * 0.5            # KiB sent to the peers through DSMEM
+                t_cta += 1.0 + pushed_kb / 19.0 + (0.07 * per if dual else 0.0)
+            t = waves * t_cta
+            if best is None or t < best[0] - 1e-9:
+                best = (t, bn, s)
+    return best[1], best[2]
 
-    def fits(s):
-        per = bn // s
-        return bn % s == 0 and per % 16 == 0 and (s - 1) * 128 * (nacc * per + 4) * 4 <= ns * stage
 
-    s = 1
-    while s < 8 and tiles * s * 2 <= SM_COUNT and kb // (s * 2) >= 2 and fits(s * 2):
-        s *= 2
-    return s
+def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
+    return plan_gemm(M, F, K, R, dual)[1]
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
@@ -135,8 +162,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         _check_bf16_2d(out, "out")
     if residual is not None:
         _check_bf16_2d(residual, "residual")
-    if splits is None:
-        splits = pick_splits(M, F, K, R, swiglu)
+    if splits is None and bn == 0:
+        bn, splits = plan_gemm(M, F, K, R, swiglu)
+    elif splits is None:
+        splits = 1
     rc = lib().tahb_gemm(_p(w), _p(x), _p(out), _p(residual), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R),
                          c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
                          c_ll(residual.stride(0) if residual is not None else 0),
