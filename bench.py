@@ -31,6 +31,9 @@ sys.path.insert(0, ROOT)
 
 MODEL = "tah-plus-1.7b"
 BATCH, PROMPT, NEW_TOKENS, HARD_P, LORA_R = 256, 256, 2048, 0.06, 64
+# profiling aid only: a shorter prompt makes the (unprofiled) prefill cheap under ncu; results printed
+# with this override are not benchmark values
+PROMPT = int(os.environ.get("TAH_B200_BENCH_PROMPT", PROMPT))
 
 
 def _unavailable(reason: str):

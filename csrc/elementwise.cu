@@ -178,37 +178,39 @@ __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ E, const i
 
 // ---------------------------------------------------------------------------------------------
 // LoRA-A on gated rows:  T[r, :] = gate[r] ? x[r, :] A^T : 0        (A: [R, K], T: [M, ldt])
-// One CTA per row; rows whose gate is 0 only clear their output.  Meant for decode ticks where
-// a handful of rows are at depth >= 1; dense passes use the tensor-core GEMM instead.
+// Rows whose gate is 0 only clear their output.  Meant for decode ticks where a handful of rows
+// are at depth >= 1; dense passes use the tensor-core GEMM instead.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ A,
                                                           __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
                                                           int K, int R, long long ldx, long long ldt) {
+  // grid (rows, ceil(R / 8)): a CTA owns 8 outputs of one row, one per warp, so that a gated row's
+  // product is spread over R / 8 CTAs instead of running serially in one
   const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.y * 8 + warp;
+  if (j >= R) return;
   __nv_bfloat16* out = T + (size_t)r * ldt;
   if (gate != nullptr && gate[r] == 0) {
-    for (int i = threadIdx.x; i < R; i += blockDim.x) out[i] = __float2bfloat16_rn(0.f);
+    if (lane == 0) out[j] = __float2bfloat16_rn(0.f);
     return;
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
-  for (int j = warp; j < R; j += 8) {
-    const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)j * K);
-    float acc = 0.f;
-    for (int i = lane; i < K / 8; i += 32) {
-      uint4 xv = xr[i], av = ar[i];
-      const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
-      const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
+  const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)j * K);
+  float acc = 0.f;
+  for (int i = lane; i < K / 8; i += 32) {
+    uint4 xv = xr[i], av = ar[i];
+    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float2 a = __bfloat1622float2(xh[q]), b = __bfloat1622float2(ah[q]);
-        acc += a.x * b.x + a.y * b.y;
-      }
+    for (int q = 0; q < 4; ++q) {
+      float2 a = __bfloat1622float2(xh[q]), b = __bfloat1622float2(ah[q]);
+      acc += a.x * b.x + a.y * b.y;
     }
-    acc = warp_sum(acc);
-    if (lane == 0) out[j] = __float2bfloat16_rn(acc);
   }
+  acc = warp_sum(acc);
+  if (lane == 0) out[j] = __float2bfloat16_rn(acc);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -350,7 +352,7 @@ extern "C" int tahb_lora_a_rows(const void* x, const void* A, void* T, const int
                                 long long ldx, long long ldt, cudaStream_t stream) {
   if (M <= 0 || R <= 0) return 0;
   if (K % 8) return -1;
-  lora_a_rows_kernel<<<M, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+  lora_a_rows_kernel<<<dim3(M, (R + 7) / 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                             reinterpret_cast<const __nv_bfloat16*>(A),
                                             reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
