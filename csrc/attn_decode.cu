@@ -26,39 +26,73 @@ struct DecodeAttnParams {
   const int* len[MAX_CACHES];
   const int* depth;             // [rows] (nullptr: every row sees n_caches caches)
   float* ws;                    // [rows, nq, n_split, HD + 2]  (n_split > 1)
+  int* status;                  // bounded-wait status word
   int n_caches, rows, nq, nkv, page_size, max_pages[MAX_CACHES], n_split;
   float scale_log2;             // softmax scale * log2(e)
 };
 
+// Geometry of the pipelined kernel: pages of 16 tokens; a pipeline stage holds STAGE_PAGES pages
+// (K and V blocks of one KV head: 2 * 16 * HD bf16 each page), NSTAGE stages in flight per CTA.
+constexpr int ATT_PAGE = 16;
+constexpr int ATT_STAGE_PAGES = 2;
+constexpr int ATT_NSTAGE = 3;
+
+template <int HD>
+struct AttCfg {
+  static constexpr int BLK_ELEMS = ATT_PAGE * HD;                          // one K (or V) block of a page
+  static constexpr int STAGE_ELEMS = ATT_STAGE_PAGES * 2 * BLK_ELEMS;
+  static constexpr int STAGE_BYTES = STAGE_ELEMS * 2;
+  static constexpr int SMEM_BYTES = ATT_NSTAGE * STAGE_BYTES + 256;
+};
+
+// Maps the i-th visible page of a row (pages of cache 0 first, then cache 1, ...) to its cache and
+// to the page index inside that cache.
+__device__ __forceinline__ void locate_page(int i, const int* seg_pages, int& c, int& local) {
+  c = 0;
+  local = i;
+#pragma unroll
+  for (int cc = 0; cc < MAX_CACHES - 1; ++cc)
+    if (c == cc && local >= seg_pages[cc]) { local -= seg_pages[cc]; c = cc + 1; }
+}
+
 template <int HD, int G>
-__global__ void __launch_bounds__(128) decode_attn_kernel(const DecodeAttnParams p) {
-  constexpr int DPL = HD / 8;        // dims per lane
-  constexpr int VEC = DPL / 8;       // uint4 loads per lane per row
-  constexpr int U = 4;               // tokens per group per step
+__global__ void __launch_bounds__(160, (HD * G <= 256) ? 4 : 2) decode_attn_kernel(const DecodeAttnParams p) {
+  using C = AttCfg<HD>;
+  constexpr int VEC = HD / 64;       // 16-byte chunks per lane per row: lane gl owns chunks gl, gl + 8, ...
+  constexpr int DPL = VEC * 8;       // dims per lane
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(att_smem);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(att_smem + ATT_NSTAGE * C::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + ATT_NSTAGE;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + ATT_NSTAGE);
+
   const int kvh = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int grp = warp * 4 + (lane >> 3);   // 0..15
-  const int gl = lane & 7;
 
-  int seg_len[MAX_CACHES];
-  int total = 0;
+  int seg_len[MAX_CACHES], seg_pages[MAX_CACHES];
+  int total_pages = 0;
   const int visible = p.depth ? min(p.depth[row] + 1, p.n_caches) : p.n_caches;
 #pragma unroll
   for (int c = 0; c < MAX_CACHES; ++c) {
     seg_len[c] = (c < visible) ? p.len[c][row] : 0;
-    total += seg_len[c];
+    seg_pages[c] = (seg_len[c] + ATT_PAGE - 1) / ATT_PAGE;
+    total_pages += seg_pages[c];
   }
-  const int chunk = (total + p.n_split - 1) / p.n_split;
-  const int begin = split * chunk;
-  const int end = min(total, begin + chunk);
+  const int ppc = (total_pages + p.n_split - 1) / p.n_split;
+  const int pb = split * ppc;
+  const int pe = min(total_pages, pb + ppc);
+  const int n_iter = pe > pb ? (pe - pb + ATT_STAGE_PAGES - 1) / ATT_STAGE_PAGES : 0;
 
-  float qv[G][DPL];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = p.q + ((size_t)row * p.nq + kvh * G + g) * HD + gl * DPL;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) qv[g][i] = __bfloat162float(qp[i]) * p.scale_log2;
+  if (tid == 0) {
+    for (int s = 0; s < ATT_NSTAGE; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);          // one arrival per consumer warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
   }
+  __syncthreads();
+
   float m[G], l[G], acc[G][DPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -67,109 +101,160 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const DecodeAttnParams
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
+  const int grp = (warp & 3) * 4 + (lane >> 3);   // token slot inside a page (consumer warps only)
+  const int gl = lane & 7;
 
-  // The trip count is the same for every lane of the CTA (groups past the end run masked
-  // iterations): the shuffles below name all 32 lanes, so no lane may leave the loop early.
-  const int n_steps = (end - begin + 16 * U - 1) / (16 * U);
-  for (int step = 0; step < n_steps; ++step) {
-    const int base = begin + grp + step * 16 * U;
-    uint4 kreg[U][VEC], vreg[U][VEC];
-    bool ok[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      int i = base + u * 16;
-      ok[u] = i < end;
-      if (!ok[u]) i = begin;   // any valid token; its contribution is masked below
-      int c = 0;
-#pragma unroll
-      for (int cc = 0; cc < MAX_CACHES - 1; ++cc)
-        if (c == cc && i >= seg_len[cc]) { i -= seg_len[cc]; c = cc + 1; }
-      const int page = p.page_table[c][(size_t)row * p.max_pages[c] + i / p.page_size];
-      const int off = i % p.page_size;
-      const __nv_bfloat16* kp =
-          p.cache[c] + ((((size_t)page * 2 + 0) * p.nkv + kvh) * p.page_size + off) * HD + gl * DPL;
-      const __nv_bfloat16* vp = kp + (size_t)p.nkv * p.page_size * HD;
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) {
-        kreg[u][v] = reinterpret_cast<const uint4*>(kp)[v];
-        vreg[u][v] = reinterpret_cast<const uint4*>(vp)[v];
+  if (warp == 4) {
+    // ---------------- producer: bulk copies of whole K / V page blocks ----------------
+    if (lane == 0) {
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % ATT_NSTAGE;
+        const uint32_t ph = (it / ATT_NSTAGE) & 1;
+        mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_STAGE_EMPTY);
+        const int first = pb + it * ATT_STAGE_PAGES;
+        const int n_here = min(ATT_STAGE_PAGES, pe - first);
+        mbar_expect_tx(&full_bar[s], n_here * 2 * C::BLK_ELEMS * 2);
+        for (int u = 0; u < n_here; ++u) {
+          int c, local;
+          locate_page(first + u, seg_pages, c, local);
+          const int page = p.page_table[c][(size_t)row * p.max_pages[c] + local];
+          const __nv_bfloat16* kp = p.cache[c] + (((size_t)page * 2 + 0) * p.nkv + kvh) * C::BLK_ELEMS;
+          const __nv_bfloat16* vp = kp + (size_t)p.nkv * C::BLK_ELEMS;
+          __nv_bfloat16* dst = stages + (size_t)s * C::STAGE_ELEMS + (size_t)u * 2 * C::BLK_ELEMS;
+          bulk_load(dst, kp, C::BLK_ELEMS * 2, &full_bar[s]);
+          bulk_load(dst + C::BLK_ELEMS, vp, C::BLK_ELEMS * 2, &full_bar[s]);
+        }
       }
     }
-    float s[U][G];
+    __syncwarp();
+  } else {
+    // ---------------- consumers: 16 groups of 8 lanes, one token of each page per group ----------------
+    float qv[G][DPL];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int g = 0; g < G; ++g) {
+      const __nv_bfloat16* qp = p.q + ((size_t)row * p.nq + kvh * G + g) * HD;
 #pragma unroll
-      for (int g = 0; g < G; ++g) s[u][g] = 0.f;
+      for (int v = 0; v < VEC; ++v)
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) {
-        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kreg[u][v]);
+        for (int i = 0; i < 8; ++i) qv[g][v * 8 + i] = __bfloat162float(qp[(v * 8 + gl) * 8 + i]) * p.scale_log2;
+    }
+    for (int it = 0; it < n_iter; ++it) {
+      const int s = it % ATT_NSTAGE;
+      const uint32_t ph = (it / ATT_NSTAGE) & 1;
+      mbar_wait(&full_bar[s], ph, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
+      const __nv_bfloat16* st = stages + (size_t)s * C::STAGE_ELEMS;
+      float sc[ATT_STAGE_PAGES][G];
+      bool ok[ATT_STAGE_PAGES];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 kf = __bfloat1622float2(kh[j]);
+      for (int u = 0; u < ATT_STAGE_PAGES; ++u) {
+        const int gi = pb + it * ATT_STAGE_PAGES + u;
+        ok[u] = false;
+        if (gi < pe) {
+          int c, local;
+          locate_page(gi, seg_pages, c, local);
+          int len_c = seg_len[0];
 #pragma unroll
-          for (int g = 0; g < G; ++g) s[u][g] += qv[g][v * 8 + 2 * j] * kf.x + qv[g][v * 8 + 2 * j + 1] * kf.y;
+          for (int cc = 1; cc < MAX_CACHES; ++cc) if (c == cc) len_c = seg_len[cc];
+          ok[u] = local * ATT_PAGE + grp < len_c;
+        }
+        const __nv_bfloat16* kp = st + (size_t)u * 2 * C::BLK_ELEMS + grp * HD;
+        float se[G], so[G];            // two partial sums per head: shorter dependent FMA chains
+#pragma unroll
+        for (int g = 0; g < G; ++g) { se[g] = 0.f; so[g] = 0.f; }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          const uint4 kr = *reinterpret_cast<const uint4*>(kp + (v * 8 + gl) * 8);
+          const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kr);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 kf = __bfloat1622float2(kh[j]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              se[g] = fmaf(qv[g][v * 8 + 2 * j], kf.x, se[g]);
+              so[g] = fmaf(qv[g][v * 8 + 2 * j + 1], kf.y, so[g]);
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float t = se[g] + so[g];
+          t += __shfl_xor_sync(0xffffffffu, t, 1);
+          t += __shfl_xor_sync(0xffffffffu, t, 2);
+          t += __shfl_xor_sync(0xffffffffu, t, 4);
+          sc[u][g] = ok[u] ? t : -INFINITY;
         }
       }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        float t = s[u][g];
-        t += __shfl_xor_sync(0xffffffffu, t, 1);
-        t += __shfl_xor_sync(0xffffffffu, t, 2);
-        t += __shfl_xor_sync(0xffffffffu, t, 4);
-        s[u][g] = ok[u] ? t : -INFINITY;
+        float mx = m[g];
+#pragma unroll
+        for (int u = 0; u < ATT_STAGE_PAGES; ++u) mx = fmaxf(mx, sc[u][g]);
+        const float corr = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mx);
+        m[g] = mx;
+        l[g] *= corr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] *= corr;
       }
-    }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float mx = m[g];
+      for (int u = 0; u < ATT_STAGE_PAGES; ++u) {
+        const __nv_bfloat16* vp = st + (size_t)u * 2 * C::BLK_ELEMS + C::BLK_ELEMS + grp * HD;
+        float pw[G];
 #pragma unroll
-      for (int u = 0; u < U; ++u) mx = fmaxf(mx, s[u][g]);
-      const float corr = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mx);
-      m[g] = mx;
-      l[g] *= corr;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[g][i] *= corr;
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const float pw = ok[u] ? exp2f(s[u][g] - mx) : 0.f;
-        l[g] += pw;
+        for (int g = 0; g < G; ++g) {
+          pw[g] = ok[u] ? exp2f(sc[u][g] - m[g]) : 0.f;
+          l[g] += pw[g];
+        }
+        if (!ok[u]) continue;   // never touch stage memory that holds no page: it may contain NaN bits
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-          const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vreg[u][v]);
+          const uint4 vr = *reinterpret_cast<const uint4*>(vp + (v * 8 + gl) * 8);
+          const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vr);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float2 vf = __bfloat1622float2(vh[j]);
-            acc[g][v * 8 + 2 * j] += pw * vf.x;
-            acc[g][v * 8 + 2 * j + 1] += pw * vf.y;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              acc[g][v * 8 + 2 * j] += pw[g] * vf.x;
+              acc[g][v * 8 + 2 * j + 1] += pw[g] * vf.y;
+            }
           }
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
   }
 
-  // merge the 16 groups through shared memory
-  __shared__ float sm_m[16][G], sm_l[16][G];
-  __shared__ float sm_acc[16][G][HD];
-  if (gl == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) { sm_m[grp][g] = m[g]; sm_l[grp][g] = l[g]; }
-  }
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) sm_acc[grp][g][gl * DPL + i] = acc[g][i];
+  // merge the 16 groups through shared memory (the pipeline buffers are free now)
   __syncthreads();
-  for (int idx = tid; idx < G * HD; idx += 128) {
+  float* sm_m = reinterpret_cast<float*>(att_smem);          // [16][G]
+  float* sm_l = sm_m + 16 * G;                               // [16][G]
+  float* sm_acc = sm_l + 16 * G;                             // [16][G][HD]
+  if (warp < 4) {
+    if (gl == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) { sm_m[grp * G + g] = m[g]; sm_l[grp * G + g] = l[g]; }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sm_acc[(grp * G + g) * HD + (v * 8 + gl) * 8 + i] = acc[g][v * 8 + i];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * HD; idx += 160) {
     const int g = idx / HD, d = idx % HD;
     float mx = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < 16; ++k) mx = fmaxf(mx, sm_m[k][g]);
+    for (int k = 0; k < 16; ++k) mx = fmaxf(mx, sm_m[k * G + g]);
     float num = 0.f, den = 0.f;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
-      const float w = (sm_m[k][g] == -INFINITY) ? 0.f : exp2f(sm_m[k][g] - mx);
-      num += w * sm_acc[k][g][d];
-      den += w * sm_l[k][g];
+      const float mk = sm_m[k * G + g];
+      const float w = (mk == -INFINITY) ? 0.f : exp2f(mk - mx);
+      num += w * sm_acc[(k * G + g) * HD + d];
+      den += w * sm_l[k * G + g];
     }
     const int head = kvh * G + g;
     if (p.n_split == 1) {
@@ -258,7 +343,14 @@ __global__ void __launch_bounds__(128) varlen_attn_naive_kernel(const VarlenAttn
 template <int HD, int G>
 static int launch_decode(const DecodeAttnParams& p, cudaStream_t stream) {
   dim3 grid(p.nkv, p.rows, p.n_split);
-  decode_attn_kernel<HD, G><<<grid, 128, 0, stream>>>(p);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attn_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             AttCfg<HD>::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  decode_attn_kernel<HD, G><<<grid, 160, AttCfg<HD>::SMEM_BYTES, stream>>>(p);
   if (p.n_split > 1) decode_attn_merge_kernel<HD><<<p.rows * p.nq, HD, 0, stream>>>(p.ws, p.out, p.n_split);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -275,8 +367,9 @@ extern "C" long long tahb_decode_attn_ws_floats(int rows, int nq, int hd, int n_
 extern "C" int tahb_decode_attn(const void* q, void* out, void* const* caches, const int* const* page_tables,
                                 const int* const* lens, const int* max_pages, int n_caches, const int* depth,
                                 int rows, int nq, int nkv, int hd, int page_size, float scale, int n_split,
-                                float* ws, cudaStream_t stream) {
+                                float* ws, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (page_size != ATT_PAGE) return -5;
   if (n_caches < 1 || n_caches > MAX_CACHES) return -1;
   if (n_split < 1) n_split = 1;
   if (n_split > 1 && ws == nullptr) return -4;
@@ -292,6 +385,7 @@ extern "C" int tahb_decode_attn(const void* q, void* out, void* const* caches, c
   }
   p.depth = depth;
   p.ws = ws;
+  p.status = status;
   p.n_caches = n_caches; p.rows = rows; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.n_split = n_split;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int G = nq / nkv;

@@ -1,0 +1,231 @@
+// Tensor-parallel collectives fused with the ops around them, over NVLink peer memory.
+//
+// fused_reduce_residual_norm: the row-parallel GEMMs (attention output, MLP down) leave on every
+// rank a partial [M, H] bf16 result in that rank's *symmetric* buffer.  This kernel replaces the
+// NCCL all-reduce + residual add + RMSNorm + (all-gather) sequence by one launch per rank:
+//
+//   rows are dealt out to the ranks in contiguous blocks; for each row it owns a rank
+//     1. sums the row over all ranks' partial buffers  - NVLS `multimem.ld_reduce` (the switch adds)
+//        when a multicast mapping exists, otherwise one peer load per rank,
+//     2. adds the residual stream h (which stays sharded by row on its owner),
+//     3. RMS-normalises the new h row, and
+//     4. broadcasts the normalised row into every rank's x buffer - `multimem.st` or peer stores -
+//        where the next column-parallel GEMM reads it locally.
+//
+// Ranks synchronise inside the kernel with flags in symmetric memory: CTA b of every rank meets
+// CTA b of the other ranks at the start (all partial GEMMs are complete) and at the end (all
+// broadcast rows have landed).  The grid is the same on every rank and small enough to be
+// co-resident.  Waits are bounded: a rank that sees no peer within WAIT_TIMEOUT_NS records
+// STATUS_TIMEOUT_PEER_FLAG in the status word and returns.
+//
+// No TMA load touches peer memory here, and nothing in this library uses cluster multicast.
+#include "common.cuh"
+
+namespace tahb {
+
+constexpr int COMM_MAX_RANKS = 8;
+
+struct FusedReduceParams {
+  const __nv_bfloat16* partial[COMM_MAX_RANKS];   // every rank's partial buffer (peer pointers); [M, H]
+  __nv_bfloat16* xout[COMM_MAX_RANKS];            // every rank's normalised-activation buffer [M, H]
+  const __nv_bfloat16* mc_partial;                // multicast address of the partial buffer or nullptr
+  __nv_bfloat16* mc_xout;                         // multicast address of the x buffer or nullptr
+  __nv_bfloat16* h;                               // local residual stream [M, H] (owned rows are live)
+  const __nv_bfloat16* ln_w;
+  uint32_t* flags[COMM_MAX_RANKS];                // every rank's flag array [grid][world]
+  uint32_t* epoch;                                // local [grid] barrier counters
+  int* status;
+  int M, H, rank, world, rows_per_rank;
+  float eps;
+  int add_residual;                               // 0: h = sum (first use), 1: h += sum
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// 8 bf16 lanes summed over all ranks by the NVSwitch, fp32 accumulation
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// CTA `b` of this rank meets CTA `b` of every other rank.  One thread signals and polls; the
+// rest of the CTA waits at the barrier that follows.  Returns false after a timeout.
+__device__ __forceinline__ bool cross_rank_barrier(const FusedReduceParams& p, int b, uint32_t epoch) {
+  bool ok = true;
+  __syncthreads();   // every thread's earlier writes happen-before thread 0's release below
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int q = 0; q < p.world; ++q) st_release_sys(p.flags[q] + (size_t)b * p.world + p.rank, epoch);
+    const uint32_t* mine = p.flags[p.rank] + (size_t)b * p.world;
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    for (int q = 0; q < p.world && ok; ++q) {
+      while ((int32_t)(ld_acquire_sys(mine + q) - epoch) < 0) {
+        if ((++spins & 0xff) == 0) {
+          const unsigned long long now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > WAIT_TIMEOUT_NS) {
+            atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER_FLAG);
+            ok = false;
+            break;
+          }
+        }
+      }
+    }
+  }
+  return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(256) fused_reduce_residual_norm_kernel(const FusedReduceParams p) {
+  const int b = blockIdx.x;
+  __shared__ uint32_t s_epoch;
+  __shared__ float red[8];
+  if (threadIdx.x == 0) {
+    s_epoch = p.epoch[b];
+    p.epoch[b] = s_epoch + 2;
+  }
+  __syncthreads();
+  const uint32_t e0 = s_epoch;
+  if (!cross_rank_barrier(p, b, e0 + 1)) return;      // peers' partial results are complete
+
+  const int nvec = p.H / 8;
+  const int row_lo = p.rank * p.rows_per_rank;
+  const int row_hi = min(p.M, row_lo + p.rows_per_rank);
+  for (int row = row_lo + b; row < row_hi; row += gridDim.x) {
+    const size_t off = (size_t)row * p.H;
+    float v[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nvec) {
+        float a[8];
+        if (p.mc_partial != nullptr) {
+          const uint4 r = multimem_ld_reduce_bf16x8(p.mc_partial + off + idx * 8);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); a[2 * j] = f.x; a[2 * j + 1] = f.y; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] = 0.f;
+          for (int q = 0; q < p.world; ++q) {
+            const uint4 r = ld_relaxed_sys_v4(p.partial[q] + off + idx * 8);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); a[2 * j] += f.x; a[2 * j + 1] += f.y; }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] = bf16_round(a[j]);
+        }
+        uint4 hr = make_uint4(0, 0, 0, 0);
+        if (p.add_residual) hr = *reinterpret_cast<const uint4*>(p.h + off + idx * 8);
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&hr);
+        uint4 ho;
+        __nv_bfloat162* ho2 = reinterpret_cast<__nv_bfloat162*>(&ho);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(hh[j]);
+          const float x0 = bf16_round(a[2 * j] + f.x), x1 = bf16_round(a[2 * j + 1] + f.y);
+          v[i][2 * j] = x0;
+          v[i][2 * j + 1] = x1;
+          ss += x0 * x0 + x1 * x1;
+          ho2[j] = __floats2bfloat162_rn(x0, x1);
+        }
+        *reinterpret_cast<uint4*>(p.h + off + idx * 8) = ho;
+      }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float rstd = rsqrtf(tot / (float)p.H + p.eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nvec) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(p.ln_w + idx * 8);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = __bfloat1622float2(wh[j]);
+          oh[j] = __floats2bfloat162_rn(g.x * bf16_round(v[i][2 * j] * rstd), g.y * bf16_round(v[i][2 * j + 1] * rstd));
+        }
+        if (p.mc_xout != nullptr) {
+          multimem_st_v4(p.mc_xout + off + idx * 8, o);
+        } else {
+          for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.xout[q] + off + idx * 8) = o;
+        }
+      }
+    }
+  }
+  cross_rank_barrier(p, b, e0 + 2);                   // every rank's rows have landed everywhere
+}
+
+}  // namespace tahb
+
+using namespace tahb;
+
+// partial / xout / flags: arrays of `world` device pointers (entry `rank` is the local buffer).
+// mc_partial / mc_xout: NVLS multicast addresses of the same buffers, or null for the peer-load /
+// peer-store path.  epoch: local uint32[grid] zero-initialised once; flags: uint32[grid * world]
+// per rank, zero-initialised once.  The grid (`grid` CTAs, <= 592) must be equal on all ranks.
+extern "C" int tahb_fused_reduce_residual_norm(void* const* partial, void* const* xout, void* mc_partial,
+                                               void* mc_xout, void* h, const void* ln_w, void* const* flags,
+                                               void* epoch, int* status, int M, int H, int rank, int world,
+                                               float eps, int add_residual, int grid, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (world < 1 || world > COMM_MAX_RANKS || H % 8) return -1;
+  FusedReduceParams p;
+  for (int q = 0; q < COMM_MAX_RANKS; ++q) {
+    const int qq = q < world ? q : 0;
+    p.partial[q] = reinterpret_cast<const __nv_bfloat16*>(partial[qq]);
+    p.xout[q] = reinterpret_cast<__nv_bfloat16*>(xout[qq]);
+    p.flags[q] = reinterpret_cast<uint32_t*>(flags[qq]);
+  }
+  p.mc_partial = reinterpret_cast<const __nv_bfloat16*>(mc_partial);
+  p.mc_xout = reinterpret_cast<__nv_bfloat16*>(mc_xout);
+  p.h = reinterpret_cast<__nv_bfloat16*>(h);
+  p.ln_w = reinterpret_cast<const __nv_bfloat16*>(ln_w);
+  p.epoch = reinterpret_cast<uint32_t*>(epoch);
+  p.status = status;
+  p.M = M; p.H = H; p.rank = rank; p.world = world;
+  p.rows_per_rank = (M + world - 1) / world;
+  p.eps = eps;
+  p.add_residual = add_residual;
+  const int nvec = H / 8;
+  if (grid < 1) grid = 1;
+  if (nvec <= 256) fused_reduce_residual_norm_kernel<1><<<grid, 256, 0, stream>>>(p);
+  else if (nvec <= 512) fused_reduce_residual_norm_kernel<2><<<grid, 256, 0, stream>>>(p);
+  else if (nvec <= 1024) fused_reduce_residual_norm_kernel<4><<<grid, 256, 0, stream>>>(p);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -236,7 +236,8 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
 __global__ void __launch_bounds__(1024) logits_post_kernel(const __nv_bfloat16* __restrict__ logits,
                                                            __nv_bfloat16* __restrict__ cum,
                                                            const int* __restrict__ depth, int* __restrict__ best,
-                                                           int V, long long ld_logits, long long ld_cum) {
+                                                           float* __restrict__ best_val, int V,
+                                                           long long ld_logits, long long ld_cum) {
   const int r = blockIdx.x;
   const bool add = depth != nullptr && depth[r] > 0;
   const __nv_bfloat16* lr = logits + (size_t)r * ld_logits;
@@ -287,7 +288,10 @@ __global__ void __launch_bounds__(1024) logits_post_kernel(const __nv_bfloat16* 
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) best[r] = bi;
+    if (lane == 0) {
+      best[r] = bi;
+      if (best_val != nullptr) best_val[r] = bv;   // lets a vocabulary-parallel caller merge shards
+    }
   }
 }
 
@@ -369,11 +373,11 @@ extern "C" int tahb_swiglu(const void* gu, void* out, int M, int I, long long ld
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int tahb_logits_post(const void* logits, void* cum, const int* depth, int* best, int M, int V,
-                                long long ld_logits, long long ld_cum, cudaStream_t stream) {
+extern "C" int tahb_logits_post(const void* logits, void* cum, const int* depth, int* best, float* best_val, int M,
+                                int V, long long ld_logits, long long ld_cum, cudaStream_t stream) {
   if (M <= 0) return 0;
   if ((ld_logits % 8) || (ld_cum % 8)) return -1;
   logits_post_kernel<<<M, 1024, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits),
-                                             reinterpret_cast<__nv_bfloat16*>(cum), depth, best, V, ld_logits, ld_cum);
+                                             reinterpret_cast<__nv_bfloat16*>(cum), depth, best, best_val, V, ld_logits, ld_cum);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -303,12 +303,15 @@ class TaHEngine:
         s.out_tokens, s.iter_sum, s.cur_iters, s.slot, s.gate = i32(B, max_new), i32(B), i32(B), i32(B), i32(B)
         s.tokens_done = torch.zeros(1, dtype=torch.int64, device=dev)
         s.need_soft, s.best, s.sampled = i32(B), i32(B), i32(B)
+        s.best_val = torch.zeros(B, dtype=torch.float32, device=dev)
+        s.samp_v = torch.zeros(B, 128, dtype=torch.float32, device=dev)
+        s.samp_i = i32(B, 128)
         s.x_in, s.soft, s.h, s.xn = bf(B, H), bf(B, H), bf(B, H), bf(B, H)
         s.qkv = bf(B, w.qkv_out)
         s.q, s.o = bf(B, w.nq * cfg.head_dim), bf(B, w.nq * cfg.head_dim)
         s.act = bf(B, w.inter)
         s.t_qkv, s.t_o, s.t_gu, s.t_down = bf(B, w.r_qkv), bf(B, w.r_o), bf(B, w.r_gu), bf(B, w.r_down)
-        s.logits, s.cum = bf(B, w.vocab), bf(B, w.vocab)
+        s.logits, s.cum = bf(B, w.vocab_shard[2]), bf(B, w.vocab_shard[2])
         s.topv = torch.zeros(B, self.topk, dtype=torch.float32, device=dev)
         s.topi = i32(B, self.topk)
         tl = self._tap_layers()
@@ -324,61 +327,77 @@ class TaHEngine:
         s.tensors = tensors
         return s
 
+    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M):
+        """Row-parallel projection + residual + the RMSNorm that follows it.
+
+        One GPU: the GEMM epilogue adds the residual in place and a norm kernel follows.  Tensor
+        parallel: the GEMM writes this rank's partial result into symmetric memory and the fused
+        NVLink kernel does all-reduce + residual + norm + broadcast; ``h`` stays row-sharded."""
+        cfg, tp = self.cfg, self.tp
+        lora = a_ is not None and t_buf is not None
+        if lora:
+            if gate is not None:
+                K.lora_a_rows(x, a_, gate, out=t_buf)
+            else:
+                K.gemm(x, a_, out=t_buf)
+        kw = dict(x2=t_buf, w2=b_) if lora else {}
+        if tp is None:
+            K.gemm(x, w_, residual=h, out=h, **kw)
+            return K.rms_norm(h, ln_w, cfg.rms_norm_eps, out=xn_out)
+        K.gemm(x, w_, out=tp.partial[:M], **kw)
+        return tp.fused_reduce_norm(M, h, ln_w, cfg.rms_norm_eps, add_residual=True)
+
     def _tick(self, s, sampling):
         """Enqueue one decode tick on the current stream (graph-capturable)."""
-        cfg, w, kv = self.cfg, self.w, self.kv
+        cfg, w, kv, tp = self.cfg, self.w, self.kv, self.tp
         B = s.tok.shape[0]
         nq, nkv, hd = w.nq, w.nkv, cfg.head_dim
         scale = hd ** -0.5
         lora = w.r > 0 and self.max_iter > 1
         tl = self._tap_layers()
         H = cfg.hidden_size
+        nL = len(w.layers)
         s.binding.tick_begin(w.embed, s.soft, s.x_in)
-        h = s.x_in
-        pools = [[kv.layer_pool(d, li) for d in range(kv.n_depths)] for li in range(len(w.layers))]
+        s.h.copy_(s.x_in)
+        pools = [[kv.layer_pool(d, li) for d in range(kv.n_depths)] for li in range(nL)]
+        xn = K.rms_norm(s.h, w.layers[0].ln1, cfg.rms_norm_eps, out=s.xn)
         for li, L in enumerate(w.layers):
             if li in tl:
                 j = tl.index(li)
-                s.taps[:, j * H:(j + 1) * H].copy_(h)
-            K.rms_norm(h, L.ln1, cfg.rms_norm_eps, out=s.xn)
+                s.taps[:, j * H:(j + 1) * H].copy_(s.h if tp is None else tp.gather_rows(s.h, B))
             if lora:
-                K.lora_a_rows(s.xn, L.a_qkv, s.gate, out=s.t_qkv)
-                K.gemm(s.xn, L.w_qkv, x2=s.t_qkv, w2=L.b_qkv, out=s.qkv)
+                K.lora_a_rows(xn, L.a_qkv, s.gate, out=s.t_qkv)
+                K.gemm(xn, L.w_qkv, x2=s.t_qkv, w2=L.b_qkv, out=s.qkv)
             else:
-                K.gemm(s.xn, L.w_qkv, out=s.qkv)
+                K.gemm(xn, L.w_qkv, out=s.qkv)
             K.qk_norm_rope_kv(s.qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
                               q_out=s.q, caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size)
             K.decode_attn(s.q, pools[li], kv.page_table, kv.len, s.depth, nq, nkv, hd, self.page_size, scale, out=s.o)
-            o = w.tp_gather_heads(s.o)
+            xn = self._row_parallel(s.o, L.w_o, L.a_o if lora else None, L.b_o, s.t_o, s.gate, s.h, L.ln2, s.xn, B)
             if lora:
-                K.lora_a_rows(o, L.a_o, s.gate, out=s.t_o)
-                K.gemm(o, L.w_o, x2=s.t_o, w2=L.b_o, residual=h, out=s.h)
+                K.lora_a_rows(xn, L.a_gu, s.gate, out=s.t_gu)
+                K.gemm(xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act)
             else:
-                K.gemm(o, L.w_o, residual=h, out=s.h)
-            h = w.tp_reduce(s.h)
-            K.rms_norm(h, L.ln2, cfg.rms_norm_eps, out=s.xn)
-            if lora:
-                K.lora_a_rows(s.xn, L.a_gu, s.gate, out=s.t_gu)
-                K.gemm(s.xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act)
-                K.lora_a_rows(s.act, L.a_down, s.gate, out=s.t_down)
-                K.gemm(s.act, L.w_down, x2=s.t_down, w2=L.b_down, residual=h, out=s.h)
-            else:
-                K.gemm(s.xn, L.w_gu, swiglu=True, out=s.act)
-                K.gemm(s.act, L.w_down, residual=h, out=s.h)
-            h = w.tp_reduce(s.h)
-        K.rms_norm(h, w.final_norm, cfg.rms_norm_eps, out=s.xn)
+                K.gemm(xn, L.w_gu, swiglu=True, out=s.act)
+            next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
+            xn = self._row_parallel(s.act, L.w_down, L.a_down if lora else None, L.b_down, s.t_down, s.gate, s.h,
+                                    next_ln, s.xn, B)
+        # xn is now the final-norm output of every row
         if cfg.num_hidden_layers in tl:
             j = tl.index(cfg.num_hidden_layers)
-            s.taps[:, j * H:(j + 1) * H].copy_(s.xn)
-        K.gemm(s.xn, w.lm_head, out=s.logits)
-        logits = w.tp_gather_vocab(s.logits)
-        K.logits_post(logits, s.cum, s.depth, s.best)
+            s.taps[:, j * H:(j + 1) * H].copy_(xn)
+        K.gemm(xn, w.lm_head, out=s.logits)
+        lo, hi, _ = w.vocab_shard
+        logits, cum = s.logits[:, :hi - lo], s.cum[:, :hi - lo]
+        K.logits_post(logits, cum, s.depth, s.best, s.best_val)
+        if tp is not None:
+            s.best.copy_(tp.merge_argmax(s.best_val, s.best, lo))
         # decision
         z = None
         if self.max_iter > 1:
             topk_done = False
             if self._needs_topk_for_decider():
-                K.topk_rows(s.cum, self.topk, out_val=s.topv, out_idx=s.topi)
+                self._topk(cum, self.topk, None, s.topv, s.topi)
                 topk_done = True
             zz = self._score(s.taps, s.topv)
             if zz is not None:
@@ -386,16 +405,24 @@ class TaHEngine:
                 z = s.z
             K.decide(z, self._thr, self.hard_override, s.pos, s.depth, self.max_iter, s.need_soft)
             if not topk_done:
-                K.topk_rows(s.cum, self.topk, flag=s.need_soft, out_val=s.topv, out_idx=s.topi)
+                self._topk(cum, self.topk, s.need_soft, s.topv, s.topi)
             K.soft_embed_rows(s.topv, s.topi, w.embed, flag=s.need_soft, out=s.soft)
         nxt = s.best
         if sampling is not None:
             kk = sampling["top_k"]
-            val, idx = K.topk_rows(s.cum, kk)
-            K.sample_topk(val, idx, sampling["temperature"], sampling["top_p"], sampling["min_p"], sampling["seed"],
-                          step=s.pos, out=s.sampled)
+            self._topk(cum, kk, None, s.samp_v, s.samp_i)
+            K.sample_topk(s.samp_v, s.samp_i, sampling["temperature"], sampling["top_p"], sampling["min_p"],
+                          sampling["seed"], step=s.pos, out=s.sampled)
             nxt = s.sampled
         s.binding.tick_end(s.need_soft, nxt)
+
+    def _topk(self, x, k, flag, out_val, out_idx):
+        """Sorted top-k of (this rank's vocabulary shard of) ``x``; merged across shards under TP."""
+        K.topk_rows(x, k, flag=flag, out_val=out_val, out_idx=out_idx)
+        if self.tp is not None:
+            v, i = self.tp.merge_topk(out_val, out_idx, self.w.vocab_shard[0], k)
+            out_val.copy_(v)
+            out_idx.copy_(i)
 
     # ------------------------------------------------------------------------------------------
     # generate

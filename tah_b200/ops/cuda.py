@@ -242,8 +242,8 @@ def swiglu(gate_up, out=None):
     return out
 
 
-def logits_post(logits, cum, depth, best):
-    _rc(lib().tahb_logits_post(_p(logits), _p(cum), _p(depth), _p(best), c_int(logits.shape[0]),
+def logits_post(logits, cum, depth, best, best_val=None):
+    _rc(lib().tahb_logits_post(_p(logits), _p(cum), _p(depth), _p(best), _p(best_val), c_int(logits.shape[0]),
                                c_int(logits.shape[1]), c_ll(logits.stride(0)), c_ll(cum.stride(0)), _stream()),
         "tahb_logits_post")
     return best
@@ -264,7 +264,7 @@ def decode_attn(q, caches: Sequence[torch.Tensor], page_tables: Sequence[torch.T
         ws = torch.empty(int(lib().tahb_decode_attn_ws_floats(rows, nq, hd, n_split)), dtype=torch.float32, device=q.device)
     _rc(lib().tahb_decode_attn(_p(q), _p(out), _ptr_array(caches), _ptr_array(page_tables), _ptr_array(lens), mp,
                                c_int(n), _p(depth), c_int(rows), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
-                               c_float(scale), c_int(n_split), _p(ws), _stream()), "tahb_decode_attn")
+                               c_float(scale), c_int(n_split), _p(ws), _p(status_word(q.device)), _stream()), "tahb_decode_attn")
     return out
 
 
@@ -319,6 +319,19 @@ def decide(z, threshold: float, override, pos, depth, max_iter: int, need_soft):
     _rc(lib().tahb_decide(_p(z), c_float(threshold), _p(override), c_int(override.shape[1] if override is not None else 0),
                           _p(pos), _p(depth), c_int(max_iter), _p(need_soft), c_int(rows), _stream()), "tahb_decide")
     return need_soft
+
+
+def fused_reduce_residual_norm(partial_ptrs, xout_ptrs, mc_partial: int, mc_xout: int, h, ln_w, flag_ptrs, epoch,
+                               M: int, H: int, rank: int, world: int, eps: float, add_residual: bool, grid: int):
+    """Row-parallel epilogue over NVLink: all-reduce of the ranks' partial [M, H] results + residual
+    add + RMSNorm + broadcast of the normalised rows, one launch per rank (see csrc/comm.cu)."""
+    n = len(partial_ptrs)
+    arr = lambda ptrs: (c_void_p * n)(*ptrs)
+    _rc(lib().tahb_fused_reduce_residual_norm(arr(partial_ptrs), arr(xout_ptrs), c_void_p(mc_partial),
+                                              c_void_p(mc_xout), _p(h), _p(ln_w), arr(flag_ptrs), _p(epoch),
+                                              _p(status_word(h.device)), c_int(M), c_int(H), c_int(rank),
+                                              c_int(world), c_float(eps), c_int(1 if add_residual else 0),
+                                              c_int(grid), _stream()), "tahb_fused_reduce_residual_norm")
 
 
 class TickStateBinding:

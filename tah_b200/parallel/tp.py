@@ -1,0 +1,142 @@
+"""Tensor parallelism over one NVLink/NVSwitch node.
+
+One process per GPU (``torch.distributed`` / NCCL for the plumbing and the cold paths).  The
+hot path does not call NCCL: activations that cross ranks live in *symmetric memory* (the same
+allocation mapped by every rank, plus an NVLS multicast address when the fabric supports it) and
+the hand-written kernel in ``csrc/comm.cu`` performs
+
+    all-reduce of the row-parallel partial results + residual add + RMSNorm + broadcast
+
+in a single launch per rank, synchronising with flags it polls itself (bounded waits).
+
+Sharding plan (Megatron style, built in :class:`tah_b200.engine.weights.EngineWeights`):
+QKV and gate/up are column-parallel (heads / intermediate channels split), O and down are
+row-parallel, the LM head is vocabulary-parallel, KV caches hold the local heads only, and the
+residual stream stays sharded by token rows on the rank that owns them.
+
+The reference has no tensor parallelism of its own: its ``tah`` backend ignores ``tp_size``
+(reference ``tah/evaluate/backends.py:155``) and only the external sglang backend shards.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from tah_b200.ops import cuda as K
+
+MAX_GRID = 148          # CTAs of the fused kernel must all be resident: they wait for their peers
+
+
+class TensorParallel:
+    def __init__(self, group, device: torch.device, hidden_size: Optional[int] = None, max_tokens: int = 0,
+                 use_multicast: Optional[bool] = None):
+        self.group = group
+        self.device = device
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        self.hidden = hidden_size
+        self.max_tokens = 0
+        self.partial = self.xout = None
+        self._symm = None
+        if use_multicast is None:
+            use_multicast = os.environ.get("TAH_B200_NVLS", "1") != "0"
+        self.use_multicast = use_multicast
+        if hidden_size is not None and max_tokens > 0:
+            self.allocate(hidden_size, max_tokens)
+
+    # ------------------------------------------------------------------------------------------
+    def allocate(self, hidden_size: int, max_tokens: int) -> None:
+        """(Re)create the symmetric buffers: partial [T, H], xout [T, H] (bf16) and the flag array."""
+        import torch.distributed._symmetric_memory as symm_mem
+        if self.partial is not None and self.hidden == hidden_size and self.max_tokens >= max_tokens:
+            return
+        self.hidden, self.max_tokens = hidden_size, max_tokens
+        try:
+            symm_mem.enable_symm_mem_for_group(self.group.group_name)
+        except Exception:
+            pass
+        mk = lambda n, dt: symm_mem.empty(n, dtype=dt, device=self.device)
+        self._partial_flat = mk(max_tokens * hidden_size, torch.bfloat16)
+        self._xout_flat = mk(max_tokens * hidden_size, torch.bfloat16)
+        self._flags = mk(MAX_GRID * self.world_size, torch.int32)
+        self._flags.zero_()
+        self._partial_flat.zero_()
+        self._xout_flat.zero_()
+        hp = symm_mem.rendezvous(self._partial_flat, self.group)
+        hx = symm_mem.rendezvous(self._xout_flat, self.group)
+        hf = symm_mem.rendezvous(self._flags, self.group)
+        self._handles = (hp, hx, hf)
+        self.partial_ptrs = [int(p) for p in hp.buffer_ptrs]
+        self.xout_ptrs = [int(p) for p in hx.buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in hf.buffer_ptrs]
+        mc_p = int(getattr(hp, "multicast_ptr", 0) or 0)
+        mc_x = int(getattr(hx, "multicast_ptr", 0) or 0)
+        if not self.use_multicast or mc_p == 0 or mc_x == 0:
+            mc_p = mc_x = 0
+        self.mc_partial, self.mc_xout = mc_p, mc_x
+        self.partial = self._partial_flat.view(max_tokens, hidden_size)
+        self.xout = self._xout_flat.view(max_tokens, hidden_size)
+        self.epoch = torch.zeros(MAX_GRID, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    # ------------------------------------------------------------------------------------------
+    def rows_of(self, M: int) -> Tuple[int, int]:
+        per = (M + self.world_size - 1) // self.world_size
+        lo = min(M, self.rank * per)
+        return lo, min(M, lo + per)
+
+    def fused_reduce_norm(self, M: int, h: torch.Tensor, ln_w: torch.Tensor, eps: float,
+                          add_residual: bool = True) -> torch.Tensor:
+        """``self.partial[:M]`` holds this rank's partial result.  Afterwards ``h`` (rows owned by
+        this rank) is the updated residual stream and the returned ``xout[:M]`` the RMS-normalised
+        rows of all ranks."""
+        per = (M + self.world_size - 1) // self.world_size
+        grid = max(1, min(MAX_GRID, per))
+        K.fused_reduce_residual_norm(self.partial_ptrs, self.xout_ptrs, self.mc_partial, self.mc_xout, h, ln_w,
+                                     self.flag_ptrs, self.epoch, M, self.hidden, self.rank, self.world_size, eps,
+                                     add_residual, grid)
+        return self.xout[:M]
+
+    # ---- cold paths: NCCL -----------------------------------------------------------------------
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def all_gather_cat(self, t: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        parts = [torch.empty_like(t) for _ in range(self.world_size)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return torch.cat(parts, dim=dim)
+
+    def gather_rows(self, h: torch.Tensor, M: int) -> torch.Tensor:
+        """Full [M, H] residual stream from the row-sharded ``h`` (owners hold their rows)."""
+        per = (M + self.world_size - 1) // self.world_size
+        pad = h.new_zeros(per * self.world_size, h.shape[1])
+        pad[:M] = h[:M]
+        mine = pad[self.rank * per:(self.rank + 1) * per].contiguous()
+        out = torch.empty_like(pad)
+        dist.all_gather_into_tensor(out, mine, group=self.group)
+        return out[:M]
+
+    def merge_argmax(self, best_val: torch.Tensor, best_idx: torch.Tensor, vocab_lo: int) -> torch.Tensor:
+        """Global argmax from per-shard (value, local index): lowest global index wins ties."""
+        pack = torch.stack([best_val.float(), (best_idx + vocab_lo).float()], dim=-1)      # [B, 2]
+        allp = torch.empty(self.world_size, *pack.shape, dtype=pack.dtype, device=pack.device)
+        dist.all_gather_into_tensor(allp, pack.contiguous(), group=self.group)
+        vals, idx = allp[..., 0], allp[..., 1]                                            # [ws, B]
+        top = vals.max(dim=0, keepdim=True).values
+        cand = torch.where(vals == top, idx, torch.full_like(idx, float("inf")))
+        return cand.min(dim=0).values.to(torch.int32)
+
+    def merge_topk(self, vals: torch.Tensor, idx: torch.Tensor, vocab_lo: int, k: int):
+        """Sorted global top-k from per-shard sorted top-k lists (``vals`` fp32 [B, k], ``idx`` int32)."""
+        gv = self.all_gather_cat(vals, dim=-1)
+        gi = self.all_gather_cat((idx + vocab_lo).to(torch.int32), dim=-1)
+        # order by value desc, index asc (the order the single-GPU kernel produces): stable sorts
+        o1 = gi.argsort(dim=-1, stable=True)
+        gv, gi = gv.gather(1, o1), gi.gather(1, o1)
+        o2 = gv.argsort(dim=-1, descending=True, stable=True)[:, :k]
+        return gv.gather(1, o2).contiguous(), gi.gather(1, o2).contiguous()
