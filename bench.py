@@ -212,7 +212,9 @@ def run_ours(args):
         }
         print(json.dumps(out))
     if world > 1:
-        dist.destroy_process_group()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)      # skip process-group teardown (it can block while symmetric memory is mapped)
 
 
 def run_eager(args):

@@ -119,25 +119,29 @@ class TaHEngine:
         """x ``[n, H]`` packed tokens at iteration ``depth``.  seg_k/seg_v: per layer lists of the
         dense K/V of shallower passes; this pass's K/V are appended as the last segment.  Returns
         (final-norm hidden, list of this pass's dense (k, v) per layer)."""
-        cfg, w = self.cfg, self.w
+        cfg, w, tp = self.cfg, self.w, self.tp
         n = x.shape[0]
         nq, nkv, hd = w.nq, w.nkv, cfg.head_dim
         lora = depth >= 1 and w.r > 0
         scale = hd ** -0.5
         own = []
-        h = x
+        nL = len(w.layers)
+        bf = lambda *shape: torch.empty(*shape, dtype=torch.bfloat16, device=x.device)
+        h = x.clone()                                   # residual stream (row-sharded under TP)
+        xn_buf = bf(n, cfg.hidden_size)
+        t_o = bf(n, w.r_o) if lora else None
+        t_down = bf(n, w.r_down) if lora else None
         tap_layers = self._tap_layers()
+        xn = K.rms_norm(h, w.layers[0].ln1, cfg.rms_norm_eps, out=xn_buf)
         for li, L in enumerate(w.layers):
             if taps_out is not None and li in tap_layers:
-                taps_out[li] = h.clone()
-            xn = K.rms_norm(h, L.ln1, cfg.rms_norm_eps)
+                taps_out[li] = h.clone() if tp is None else tp.gather_rows(h, n)
             if lora:
                 t = K.gemm(xn, L.a_qkv)
                 qkv = K.gemm(xn, L.w_qkv, x2=t, w2=L.b_qkv)
             else:
                 qkv = K.gemm(xn, L.w_qkv)
-            kd = torch.empty(n, nkv * hd, dtype=torch.bfloat16, device=x.device)
-            vd = torch.empty_like(kd)
+            kd, vd = bf(n, nkv * hd), bf(n, nkv * hd)
             q = K.qk_norm_rope_kv(qkv, L.q_norm, L.k_norm, pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
                                   k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
                                   page_size=self.page_size)
@@ -145,24 +149,16 @@ class TaHEngine:
             ks = [sk[li] for sk in seg_k] + [kd]
             vs = [sv[li] for sv in seg_v] + [vd]
             o = K.varlen_attn_naive(q, ks, vs, seg_base, seg_count, nq, nkv, hd, scale)
-            o = w.tp_gather_heads(o)
-            if lora:
-                t = K.gemm(o, L.a_o)
-                h = K.gemm(o, L.w_o, x2=t, w2=L.b_o, residual=h)
-            else:
-                h = K.gemm(o, L.w_o, residual=h)
-            h = w.tp_reduce(h)
-            xn = K.rms_norm(h, L.ln2, cfg.rms_norm_eps)
+            xn = self._row_parallel(o, L.w_o, L.a_o if lora else None, L.b_o, t_o, None, h, L.ln2, xn_buf, n)
             if lora:
                 t = K.gemm(xn, L.a_gu)
                 act = K.gemm(xn, L.w_gu, x2=t, w2=L.b_gu, swiglu=True)
-                t = K.gemm(act, L.a_down)
-                h = K.gemm(act, L.w_down, x2=t, w2=L.b_down, residual=h)
             else:
                 act = K.gemm(xn, L.w_gu, swiglu=True)
-                h = K.gemm(act, L.w_down, residual=h)
-            h = w.tp_reduce(h)
-        hn = K.rms_norm(h, w.final_norm, cfg.rms_norm_eps)
+            next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
+            xn = self._row_parallel(act, L.w_down, L.a_down if lora else None, L.b_down, t_down, None, h, next_ln,
+                                    xn_buf, n)
+        hn = xn.clone()
         if taps_out is not None and cfg.num_hidden_layers in tap_layers:
             taps_out[cfg.num_hidden_layers] = hn
         return hn, own
@@ -184,6 +180,8 @@ class TaHEngine:
             self.kv = PagedKVCache(geo, B, max(max_total, 1), self.max_iter, self.deep_fraction, dev)
             self._graph = None
         self.kv.reset()
+        if self.tp is not None:
+            self.tp.allocate(cfg.hidden_size, max(int(valid.sum()), B))
         rows_idx, cols_idx = valid.nonzero(as_tuple=True)
         ids = input_ids[rows_idx, cols_idx].to(torch.int32).contiguous()
         n0 = ids.numel()
@@ -207,7 +205,7 @@ class TaHEngine:
         extra = self._prompt_extra_passes(hn, taps, seq, pos)                 # [n0] int: extra passes wanted
         cur_idx = torch.arange(n0, device=dev)                                # packed indices of the current set
         cur_cum = None                                                        # cumulative logits of current set
-        final_last_logits = torch.empty(B, w.vocab, dtype=torch.bfloat16, device=dev)
+        final_last_logits = torch.empty(B, w.vocab_shard[1] - w.vocab_shard[0], dtype=torch.bfloat16, device=dev)
         # tokens needing logits after pass 0: last tokens + hard tokens
         need0 = is_last | (extra > 0)
         sel = need0.nonzero().flatten()
@@ -226,7 +224,9 @@ class TaHEngine:
             rows1 = seq[cur_idx].long()
             cnt1 = torch.bincount(rows1, minlength=B)
             slots1 = self.kv.assign_prefill(depth, cnt1)
-            val, idx = K.topk_rows(cur_cum, self.topk)
+            val = torch.zeros(n1, self.topk, dtype=torch.float32, device=dev)
+            idx = torch.zeros(n1, self.topk, dtype=torch.int32, device=dev)
+            self._topk(cur_cum, self.topk, None, val, idx)
             x1 = K.soft_embed_rows(val, idx, w.embed)
             pos1 = pos[cur_idx].contiguous()
             start1 = (torch.cumsum(cnt1, 0) - cnt1).to(torch.int32)
@@ -275,7 +275,9 @@ class TaHEngine:
                 tcat = torch.cat([taps[i][sl] for i in tl], dim=-1) if tl else None
                 tv = None
                 if isinstance(inner, MLPIterDecider):
-                    tv, _ = K.topk_rows(self._lm_head(hn[sl]), inner.topk)
+                    lg = self._lm_head(hn[sl])
+                    tv = torch.zeros(lg.shape[0], inner.topk, dtype=torch.float32, device=dev)
+                    self._topk(lg, inner.topk, None, tv, torch.zeros(lg.shape[0], inner.topk, dtype=torch.int32, device=dev))
                 zs.append(self._score(tcat, tv))
             z = torch.cat(zs)
         if self.hard_override is not None:
@@ -287,8 +289,15 @@ class TaHEngine:
         return (torch.sigmoid(z) > self._thr).to(torch.int32)
 
     def _lm_head(self, hn: torch.Tensor) -> torch.Tensor:
-        out = K.gemm(hn.contiguous(), self.w.lm_head)
-        return self.w.tp_gather_vocab(out)
+        """Logits of this rank's vocabulary shard (the whole vocabulary on one GPU)."""
+        lo, hi, _ = self.w.vocab_shard
+        return K.gemm(hn.contiguous(), self.w.lm_head)[:, :hi - lo]
+
+    def _argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        val, idx = logits.float().max(dim=-1)
+        if self.tp is None:
+            return idx.to(torch.int32)
+        return self.tp.merge_argmax(val, idx.to(torch.int32), self.w.vocab_shard[0])
 
     # ------------------------------------------------------------------------------------------
     # decode tick
@@ -446,13 +455,18 @@ class TaHEngine:
                 raise NotImplementedError("engine sampling needs 0 < top_k <= 128; use the loop path otherwise")
             sampling = dict(temperature=temperature, top_p=top_p, min_p=min_p, top_k=top_k, seed=seed)
         s = self._alloc_tick_buffers(B, max_new_tokens)
+        if sampling is not None:
+            s.samp_v = torch.zeros(B, top_k, dtype=torch.float32, device=dev)
+            s.samp_i = torch.zeros(B, top_k, dtype=torch.int32, device=dev)
         s.ints[8] = -1 if eos_token_id is None else int(eos_token_id)
         s.binding = K.TickStateBinding(s.tensors, s.ints)
         # first token from the prefill logits
         if sampling is None:
-            first = last_logits.float().argmax(-1).to(torch.int32)
+            first = self._argmax(last_logits)
         else:
-            val, idx = K.topk_rows(last_logits, top_k)
+            val = torch.zeros(B, top_k, dtype=torch.float32, device=dev)
+            idx = torch.zeros(B, top_k, dtype=torch.int32, device=dev)
+            self._topk(last_logits, top_k, None, val, idx)
             first = K.sample_topk(val, idx, temperature, top_p, min_p, seed, step=lens.to(torch.int32) - 1)
         s.pos.copy_(lens.to(torch.int32) - 1)
         s.need_soft.zero_()

@@ -126,13 +126,3 @@ class EngineWeights:
         self.r_qkv, self.r_o, self.r_gu, self.r_down = width(l0.a_qkv), width(l0.a_o), width(l0.a_gu), width(l0.a_down)
         if self.r > 0 and min(self.r_qkv, self.r_o, self.r_gu, self.r_down) == 0:
             raise NotImplementedError("the engine expects LoRA on all seven projections (target_modules='all-linear')")
-
-    # ---- tensor-parallel hooks (identity on one GPU) ------------------------------------------
-    def tp_gather_heads(self, o):
-        return o
-
-    def tp_reduce(self, h):
-        return h if self.tp is None else self.tp.all_reduce(h)
-
-    def tp_gather_vocab(self, logits):
-        return logits if self.tp is None else self.tp.gather_vocab(logits, self.vocab_shard, self.vocab)
