@@ -13,6 +13,7 @@
 // handled together, so K/V are read once.  Online softmax in base 2; groups are merged through
 // shared memory; with n_split > 1 partial (m, l, acc) go to a workspace and a second kernel merges.
 #include "common.cuh"
+#include "tah_b200_noalloc.h"
 
 namespace tahb {
 
@@ -395,6 +396,43 @@ extern "C" int tahb_decode_attn(const void* q, void* out, void* const* caches, c
   TAHB_DEC(64, 1) TAHB_DEC(64, 2) TAHB_DEC(64, 4)
 #undef TAHB_DEC
   return -2;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in tah_b200_noalloc.h).
+// ---------------------------------------------------------------------------------------------
+constexpr long long NOALLOC_WS_FLOATS = 1ll << 20;     // 4 MiB of scratch per GPU
+static __device__ __align__(256) float g_noalloc_ws[NOALLOC_WS_FLOATS];
+
+extern "C" long long tahb_decode_attn_noalloc_capacity(void) { return NOALLOC_WS_FLOATS; }
+
+// In host code `g_noalloc_ws` is only a handle for the symbol, not an address a kernel can use:
+// the device address is looked up once per device and cached here.
+static float* noalloc_ws_for_current_device(void) {
+  constexpr int MAX_DEVICES = 64;
+  static float* cached[MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  if (cached[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_ws) != cudaSuccess) return nullptr;
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
+
+extern "C" int tahb_decode_attn_noalloc(const void* q, void* out, void* const* caches,
+                                        const int* const* page_tables, const int* const* lens,
+                                        const int* max_pages, int n_caches, const int* depth, int rows, int nq,
+                                        int nkv, int hd, int page_size, float scale, int n_split, int* status,
+                                        cudaStream_t stream) {
+  if (n_split < 1) n_split = 1;
+  const long long need = tahb_decode_attn_ws_floats(rows, nq, hd, n_split);
+  if (need > NOALLOC_WS_FLOATS) return -7;     // request exceeds the built-in scratch area
+  float* ws = noalloc_ws_for_current_device();
+  if (ws == nullptr) return -8;
+  return tahb_decode_attn(q, out, caches, page_tables, lens, max_pages, n_caches, depth, rows, nq, nkv, hd,
+                          page_size, scale, n_split, ws, status, stream);
 }
 
 extern "C" int tahb_varlen_attn_naive(const void* q, void* out, void* const* ks, void* const* vs,
