@@ -500,15 +500,21 @@ class TaHEngine:
 
     def _tick_runner(self, s, sampling):
         if not self.use_cuda_graph:
-            return lambda: self._tick(s, sampling)
+            def run_eager():
+                before = K.launch_count
+                self._tick(s, sampling)
+                self.kernel_launches_per_tick = K.launch_count - before
+            return run_eager
         # Capture records the launches of one tick without running them.  Everything a tick touches
         # was allocated beforehand, so replays reuse the same addresses.
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         graph = torch.cuda.CUDAGraph()
+        before = K.launch_count
         with torch.cuda.stream(side):
             with torch.cuda.graph(graph, stream=side):
                 self._tick(s, sampling)
+        self.kernel_launches_per_tick = K.launch_count - before      # own kernels recorded in the graph
         torch.cuda.current_stream().wait_stream(side)
         self._graph = graph
         return graph.replay

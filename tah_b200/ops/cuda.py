@@ -75,7 +75,12 @@ def check_status(device=None) -> None:
         raise KernelTimeout(f"tah_b200 kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
+launch_count = 0      # number of library entry points called (each launches at least one kernel)
+
+
 def _rc(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed on the host side (code {rc})")
 

@@ -1,0 +1,1 @@
+"""Parallelism: tensor parallel (symmetric memory + fused NVLink kernels) and ZeRO data parallel."""

@@ -1,0 +1,118 @@
+"""CPU (gloo) worker for the multi-process tests: ``python dist_worker_cpu.py <case> <out.json>`` under torchrun."""
+import json
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def case_zero(out):
+    """N-rank ZeroAdamW on each rank's micro-batch == single-process AdamW on the global batch."""
+    from tah_b200.parallel.zero import ZeroAdamW
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(0)
+    lin = torch.nn.Sequential(torch.nn.Linear(7, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+    ref = torch.nn.Sequential(torch.nn.Linear(7, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+    ref.load_state_dict(lin.state_dict())
+    opt = ZeroAdamW(lin.parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=0.5)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    g = torch.Generator().manual_seed(1)
+    for step in range(4):
+        x, y = torch.randn(world, 6, 7, generator=g), torch.randn(world, 6, 3, generator=g)
+        loss = ((lin(x[rank]) - y[rank]) ** 2).mean()
+        loss.backward()
+        gn = opt.step()
+        opt.zero_grad()
+        rl = sum(((ref(x[r]) - y[r]) ** 2).mean() for r in range(world)) / world
+        rl.backward()
+        rgn = torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        ropt.step()
+        ropt.zero_grad()
+        assert abs(float(gn) - float(rgn)) < 1e-5, (float(gn), float(rgn))
+    err = max(float((a - b).abs().max()) for a, b in zip(lin.parameters(), ref.parameters()))
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
+    out.update(err=err, shard=opt.hi - opt.lo, numel=opt.numel)
+    assert err < 1e-5, err
+
+
+def case_trainer(out):
+    """The trainer on N ranks follows the same loss curve as on one (same global data, ZeRO optimizer)."""
+    from tah_b200.train import CustomTaHDataCollator, CustomTaHTrainer, TaHTrainingArguments
+    from tests.helpers import tiny_tah
+    rank, world = dist.get_rank(), dist.get_world_size()
+    model = tiny_tah(seed=0)
+    g = torch.Generator().manual_seed(3)
+    rows = []
+    for _ in range(8):
+        ids = torch.randint(0, 1024, (24,), generator=g).tolist()
+        hard = [1] * 24
+        hard[7] = 2
+        rows.append(dict(input_ids=ids, attention_mask=[1] * 24, labels=[-100] * 3 + ids[3:], iter_count_labels=hard))
+    args = TaHTrainingArguments(output_dir=os.environ["TAH_TEST_OUT"], per_device_train_batch_size=1,
+                                gradient_accumulation_steps=4 // world if world <= 4 else 1, learning_rate=1e-3,
+                                max_grad_norm=1.0, num_train_epochs=1, logging_steps=1, save_strategy="no", seed=0)
+    tr = CustomTaHTrainer(model, args, rows, None, data_collator=CustomTaHDataCollator(None, pad_token_id=0))
+    tr.train()
+    out.update(losses=[h["loss"] for h in tr.state.log_history if "loss" in h], steps=tr.state.global_step)
+
+
+def case_heartbeat(out):
+    """Rank 1 leaves between steps; rank 0 learns of it from the store before its next collective."""
+    from tah_b200.utils.failure import RankFailure, RankHeartbeat
+    rank, world = dist.get_rank(), dist.get_world_size()
+    store = dist.distributed_c10d._get_default_store()
+    hb = RankHeartbeat(store, rank, world, interval_s=0.1).start()
+    t = torch.ones(1)
+    dist.all_reduce(t)                       # step 1: everyone is here
+    if rank == 1:
+        hb.stop()
+        out.update(left=True)
+        return "leave"
+    detected, t0 = None, time.time()
+    while time.time() - t0 < 10:
+        try:
+            hb.check_peers(timeout_s=0.6)
+        except RankFailure as exc:
+            detected = exc.dead
+            break
+        time.sleep(0.1)
+    hb.stop()
+    out.update(detected=detected, seconds=time.time() - t0)
+    assert detected == [1]
+    return "leave"
+
+
+def case_collective_timeout(out):
+    """A rank that never joins turns the others' next collective into an error after the group timeout."""
+    rank = dist.get_rank()
+    if rank == 1:
+        time.sleep(6)
+        return "leave"
+    t0 = time.time()
+    try:
+        dist.all_reduce(torch.ones(1))
+        out.update(raised=False)
+    except Exception as exc:
+        out.update(raised=True, seconds=time.time() - t0, kind=type(exc).__name__)
+    return "leave"
+
+
+if __name__ == "__main__":
+    import datetime
+    case, path = sys.argv[1], sys.argv[2]
+    timeout = datetime.timedelta(seconds=3 if case == "collective_timeout" else 120)
+    dist.init_process_group("gloo", timeout=timeout)
+    result = {}
+    how = globals()[f"case_{case}"](result)
+    with open(f"{path}.rank{dist.get_rank()}", "w") as fh:
+        json.dump(result, fh)
+    if how == "leave":
+        os._exit(0)
+    dist.barrier()
+    dist.destroy_process_group()

@@ -1,0 +1,211 @@
+"""CPU tests of the glue around the model: checkpoints, collator, preprocessing, eval driver, scripts."""
+import csv
+import json
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+from tah_b200 import TaHConfig, TaHForCausalLM
+from tah_b200.evaluate import codeeval
+from tah_b200.evaluate.jobs import _free_port, combine_job_results, parse_data_range, run_single_job
+from tah_b200.train import CustomTaHDataCollator
+from tah_b200.train.schedule import lr_factor
+from tah_b200.utils.data_prepare import _build_sft_example, _filter_keep
+from tests.helpers import tiny_tah
+
+
+def test_checkpoint_layout_and_round_trip(tmp_path):
+    from safetensors import safe_open
+    model = tiny_tah(decider="MLPIterDecider",
+                     decider_kwargs=dict(topk=10, hidden_states_size=256, hidden_states_layer_nums=[1, 4],
+                                         hidden_dims=[32, 32], dropout_rate=0.0, threshold=0.8, dtype=torch.float32)).eval()
+    model.save_pretrained(str(tmp_path))
+    names = set(os.listdir(tmp_path))
+    assert {"config.json", "generation_config.json", "model.safetensors", "lora", "iter_decider.bin", "tah_config.json"} <= names
+    assert set(os.listdir(tmp_path / "lora")) == {"adapter_config.json", "adapter_model.safetensors"}
+    with safe_open(str(tmp_path / "model.safetensors"), "pt") as fh:
+        keys = set(fh.keys())
+    assert "model.layers.0.self_attn.q_proj.weight" in keys and "model.layers.3.mlp.up_proj.weight" in keys
+    assert "model.embed_tokens.weight" in keys and "lm_head.weight" not in keys        # tied head is not duplicated
+    assert not any("lora" in k or "base_layer" in k or "qkv_proj" in k for k in keys)
+    with safe_open(str(tmp_path / "lora" / "adapter_model.safetensors"), "pt") as fh:
+        lkeys = set(fh.keys())
+    assert "base_model.model.model.layers.2.mlp.down_proj.lora_B.weight" in lkeys
+    assert "base_model.model.model.layers.0.self_attn.k_proj.lora_A.weight" in lkeys
+    acfg = json.load(open(tmp_path / "lora" / "adapter_config.json"))
+    assert acfg["r"] == 8 and acfg["peft_type"] == "LORA" and "base_grad" not in acfg
+    hf = json.load(open(tmp_path / "config.json"))
+    assert hf["model_type"] == "qwen3" and hf["num_hidden_layers"] == 4 and hf["tie_word_embeddings"] is True
+    loaded = TaHForCausalLM.from_pretrained(str(tmp_path)).eval()
+    ids = torch.randint(0, 1024, (2, 12))
+    hard = torch.ones(2, 12, dtype=torch.long)
+    hard[:, 5] = 2
+    with torch.no_grad():
+        a, b = model(ids), loaded(ids)
+    torch.testing.assert_close(a.logits, b.logits)
+    assert torch.equal(a.iter_count, b.iter_count)
+    # an override of the eval threshold wins over the stored decider state
+    over = TaHConfig(iter_decider_kwargs=dict(model.tah_config.iter_decider_kwargs, threshold=0.3))
+    l2 = TaHForCausalLM.from_pretrained(str(tmp_path), tah_config=over)
+    assert abs(float(l2.iter_decider.threshold.detach()) - 0.3) < 1e-6
+
+
+def test_sharded_safetensors_round_trip(tmp_path):
+    model = tiny_tah().eval()
+    model.save_pretrained(str(tmp_path), max_shard_bytes=2_000_000)
+    assert os.path.exists(tmp_path / "model.safetensors.index.json")
+    loaded = TaHForCausalLM.from_pretrained(str(tmp_path)).eval()
+    ids = torch.randint(0, 1024, (1, 9))
+    with torch.no_grad():
+        torch.testing.assert_close(model(ids).logits, loaded(ids).logits)
+
+
+def test_hf_backbone_parity():
+    """The fused backbone computes what HuggingFace's Qwen3 computes with the same weights."""
+    transformers = pytest.importorskip("transformers")
+    from tah_b200.models import from_hf_model
+    cfg = transformers.Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6,
+                                   tie_word_embeddings=True, rope_parameters={"rope_theta": 1e6, "rope_type": "default"})
+    torch.manual_seed(0)
+    hf = transformers.Qwen3ForCausalLM(cfg).float().eval()
+    mine = from_hf_model(hf).eval()
+    ids = torch.randint(0, 512, (2, 17))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits
+        out = mine(input_ids=ids)
+    torch.testing.assert_close(out, ref, atol=2e-4, rtol=1e-4)
+
+
+def test_collator_pads_on_tokenizer_side():
+    class Tok:
+        pad_token_id, padding_side = 9, "left"
+    feats = [dict(input_ids=[1, 2, 3], attention_mask=[1, 1, 1], labels=[-100, 2, 3], iter_count_labels=[1, 1, 2]),
+             dict(input_ids=[4], attention_mask=[1], labels=[4], iter_count_labels=[1])]
+    b = CustomTaHDataCollator(Tok())(feats)
+    assert b["input_ids"].tolist() == [[1, 2, 3], [9, 9, 4]]
+    assert b["attention_mask"].tolist() == [[1, 1, 1], [0, 0, 1]]
+    assert b["labels"].tolist() == [[-100, 2, 3], [-100, -100, 4]]
+    assert b["iter_count_labels"].tolist() == [[1, 1, 2], [-100, -100, 1]]
+    Tok.padding_side = "right"
+    b = CustomTaHDataCollator(Tok(), pad_to_multiple_of=4)(feats)
+    assert b["input_ids"].tolist()[1] == [4, 9, 9, 9] and b["iter_count_labels"].tolist()[1] == [1, -100, -100, -100]
+
+
+def test_build_sft_example_and_filter():
+    ex = _build_sft_example([5, 6, 7, 8, 9], [0, 0, 1, 1, 1], [1, 0, 1, 0, 0], max_iter=2, max_length=None,
+                            truncate=True, query_iter_count=1)
+    assert ex["labels"] == [-100, -100, 7, 8, 9] and ex["iter_count_labels"] == [1, 1, 2, 1, 1]
+    assert ex["attention_mask"] == [1] * 5
+    ex = _build_sft_example([5, 6, 7], [0, 1, 1], [0, 2, 0], 3, None, True, 1)
+    assert ex["iter_count_labels"] == [1, 3, 1]                      # counts written by the labeller: mismatch + 1
+    assert _build_sft_example([1, 2], [0, 0], [0, 0], 2, None, True, 1) is None
+    assert _build_sft_example([1, 2, 3], [1, 1, 1], None, 2, 2, False, 1) is None
+    assert len(_build_sft_example([1, 2, 3], [1, 1, 1], None, 2, 2, True, 1)["input_ids"]) == 2
+    batch = {"real_token": [[1, 2, 3], [1, 2, 3], [1, 2, 3, 4]], "mask": [[0, 1, 1], [0, 0, 0], [0, 1, 1, 1]],
+             "mismatch": [[0, 1, 0], [0, 0, 0], [0, 0, 0, 1]]}
+    assert _filter_keep(batch, max_length=3, truncate=True) == [True, False, False]
+    assert _filter_keep(batch, max_length=3, truncate=False) == [True, False, False]
+    assert _filter_keep(batch, max_length=None, truncate=True) == [True, False, True]
+
+
+def test_lr_schedule_cosine_with_min_lr():
+    assert lr_factor(0, 100, 10) == 0.0 and abs(lr_factor(5, 100, 10) - 0.5) < 1e-9
+    assert abs(lr_factor(10, 100, 10, "cosine_with_min_lr", 0.1) - 1.0) < 1e-9
+    assert abs(lr_factor(100, 100, 10, "cosine_with_min_lr", 0.1) - 0.1) < 1e-9
+    assert abs(lr_factor(55, 100, 10, "cosine_with_min_lr", 0.1) - 0.55) < 1e-9
+    assert lr_factor(100, 100, 0, "linear") == 0.0
+
+
+def test_parse_data_range_and_free_port():
+    assert parse_data_range([5], 100) == (0, 5) and parse_data_range([2, 9], 6) == (2, 6)
+    assert parse_data_range(None, 7) == (0, 7)
+    with pytest.raises(ValueError):
+        parse_data_range([5, 5], 10)
+    with pytest.raises(ValueError):
+        parse_data_range([1, 2, 3])
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        busy = s.getsockname()[1]
+        s.listen(1)
+        got = _free_port(busy)
+        assert got != busy and busy < got < busy + 100
+
+
+class _FakeTok:
+    chat_template = None
+    pad_token = eos_token = "<e>"
+
+    def encode(self, text):
+        return text.split()
+
+
+def test_run_single_job_and_combine(tmp_path, monkeypatch):
+    from tah_b200.evaluate import jobs, matheval
+
+    class Grader:
+        def rule_judge(self, out, gold):
+            ans = out.strip().split()[-1] if out.strip() else ""
+            return (ans == gold, ans or "No extracted answer")
+    monkeypatch.setitem(matheval.evaluator_map, "toy", Grader())
+
+    def factory(backend, config, model_path, tokenizer, tp_size=1):
+        def infer(prompts):
+            return [(f"the answer is {len(p.split())}", 0.5) for p in prompts]
+        return object(), infer
+
+    mapping = {"id_field": "id", "question_field": "question", "answer_field": "answer", "answer_type": "boxed"}
+    for job_id, probs in enumerate([[{"id": "toy_0", "question": "a b c", "answer": "3"}],
+                                    [{"id": "toy_1", "question": "a b", "answer": "5"}]]):
+        run_single_job(config={"batch_size": 2, "repeat_size": 2}, combined_dataset_name="toy", output_dir=str(tmp_path),
+                       timestamp="ts", model_path="", job_id=job_id, job_nums=2, start_idx=0, end_idx=1, tp_size=1,
+                       backend="tah", data_range=None, problems_data=probs, field_mapping=mapping,
+                       unified_code_solutions_file=None, tokenizer=_FakeTok(), backend_factory=factory)
+    base = tmp_path / "toy_tah" / "ts"
+    assert (base / "job_0" / "details" / "toy_0" / "sample_1.json").exists()
+    summary = combine_job_results(base, 2)
+    assert summary == {"total": 4, "correct": 2, "accuracy": 0.5}
+    rows = list(csv.DictReader(open(base / "detailed_results.csv")))
+    assert len(rows) == 4 and rows[0]["processing_time"] == "0.5" and set(rows[0]) == set(jobs._CSV_FIELDS)
+    assert sum(1 for _ in open(base / "samples.jsonl")) == 4
+    assert "Total Accuracy" in open(base / "evaluation_stats.csv").read()
+
+
+def test_code_sanitize_and_evaluate(tmp_path):
+    text = "Here you go:\n```python\nimport math\n\ndef helper(x):\n    return x + 1\n\ndef unused():\n    return 0\n\ndef add1(x):\n    return helper(x)\n```\nthanks"
+    code = codeeval.sanitize(text, "add1")
+    assert "def add1" in code and "def helper" in code and "import math" in code
+    problems = tmp_path / "p.jsonl"
+    problems.write_text(json.dumps({"task_id": "t/0", "entry_point": "add1",
+                                    "test": "def check(f):\n    assert f(1) == 2\n"}) + "\n")
+    samples = tmp_path / "s.jsonl"
+    samples.write_text(json.dumps({"task_id": "t/0", "solution": code}) + "\n" +
+                       json.dumps({"task_id": "t/0", "solution": "def add1(x):\n    return x"}) + "\n")
+    res = codeeval.evaluate("toy", str(samples), problems_path=str(problems), parallel=2, ks=(1, 2))
+    assert abs(res["pass_at_k"]["pass@1"] - 0.5) < 1e-9 and res["pass_at_k"]["pass@2"] == 1.0
+
+
+def test_download_retries_with_backoff(monkeypatch):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "script", "preparation"))
+    import download
+    calls, sleeps = [], []
+    monkeypatch.setattr(download.time, "sleep", lambda s: sleeps.append(s))
+
+    def flaky(**kw):
+        calls.append(kw)
+        if len(calls) < 4:
+            raise ConnectionError("boom")
+        return "/tmp/x"
+    assert download.download_with_retry("a/b", "/tmp/x", downloader=flaky) == "/tmp/x"
+    assert len(calls) == 4 and sleeps == [1.0, 2.0, 4.0]
+
+
+def test_labeller_helpers():
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "script", "preparation"))
+    import label
+    assert label._categorize_masks([1, 2, 151667, 3, 4]) == [0, 0, 1, 1, 1]
+    mm = label._calculate_mismatch(torch.tensor([5, 6, 7, 8]), torch.tensor([1, 5, 9, 7]))
+    assert mm.tolist() == [0, 1, 0, 0]                                # pred[i] vs real[i+1]; last stays 0
