@@ -58,6 +58,39 @@ def main():
                 print(f"fused_reduce_norm multicast={use_mc} iter={it}: max err h {e1:.4f} xn {e2:.4f} {'ok' if good else 'BAD'}")
         dist.barrier()
 
+    # ---- ZeRO optimizer: fused reduce-scatter + AdamW + parameter broadcast over peer memory -----
+    from tah_b200.parallel.zero import ZeroAdamW
+    for use_mc in (False, True):
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(torch.nn.Linear(64, 96), torch.nn.Tanh(), torch.nn.Linear(96, 40)).to(dev).bfloat16()
+        ref = [p.detach().float().clone().requires_grad_(True) for p in net.parameters()]
+        opt = ZeroAdamW(net.parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=0.7, use_multicast=use_mc)
+        ropt = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.01)
+        err = 0.0
+        for step in range(3):
+            g = torch.Generator(device=dev).manual_seed(10 * step + rank)
+            x = torch.randn(16, 64, generator=g, device=dev).bfloat16()
+            (net(x).float() ** 2).mean().backward()
+            grads = [p.grad.detach().float().clone() for p in net.parameters()]
+            for gg in grads:
+                dist.all_reduce(gg)
+                gg /= world
+            gn = opt.step()
+            opt.zero_grad()
+            K.check_status(dev)
+            for r, gg in zip(ref, grads):
+                r.grad = gg
+            rgn = torch.nn.utils.clip_grad_norm_(ref, 0.7)
+            ropt.step()
+            err = max(err, abs(float(gn) - float(rgn)) / float(rgn))
+        perr = max(float((p.detach().float() - r.detach().to(torch.bfloat16).float()).abs().max())
+                   for p, r in zip(net.parameters(), ref))
+        good = err < 5e-3 and perr < 2e-2
+        ok = ok and good
+        if rank == 0:
+            print(f"ZeroAdamW world={world} multicast={use_mc and opt.mc_grad != 0}: grad-norm rel err {err:.2e}, param err {perr:.2e} {'ok' if good else 'BAD'}")
+        dist.barrier()
+
     # ---- engine parity: TP vs single GPU -------------------------------------------------------
     from tests.helpers import tiny_tah
     from tah_b200.engine import TaHEngine
