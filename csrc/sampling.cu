@@ -9,16 +9,26 @@ namespace tahb {
 
 // ---------------------------------------------------------------------------------------------
 // Sorted top-k (k <= 128) of one bf16 row of V values per CTA, for rows whose flag is set.
-// Radix select on the 16-bit order-preserving key (two 256-bin histogram passes), then an
-// index-ordered gather (ties at the threshold are taken lowest index first, so the result is
-// deterministic), then a 128-wide bitonic sort by (value desc, index asc).
+//
+// Fast path (two sweeps over the row): a 4096-bin histogram of the top 12 bits of the 16-bit
+// order-preserving key locates the bin holding the k-th largest value; every key in or above that
+// bin is a candidate (k plus a few dozen for real logits) and is collected unordered; each
+// candidate then counts the candidates that precede it in (value desc, index asc) order, which is
+// its output slot.  The result is exact and deterministic (ties: lowest index first).
+// Fallback (more than 1024 candidates, e.g. a constant row): two 256-bin radix passes, an
+// index-ordered gather and a 128-wide bitonic sort.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t order_key(__nv_bfloat16 v) {
   const uint16_t u = __bfloat16_as_ushort(v);
   return (u & 0x8000) ? (uint16_t)~u : (uint16_t)(u | 0x8000);
 }
+__device__ __forceinline__ float key_value(uint32_t k) {
+  const uint16_t u = (k & 0x8000) ? (uint16_t)(k & 0x7fff) : (uint16_t)~k;
+  return __bfloat162float(__ushort_as_bfloat16(u));
+}
 
 constexpr int TOPK_THREADS = 1024;
+constexpr int TOPK_CAND = 1024;
 
 __device__ __forceinline__ int find_bin(const int* hist, int want, int* above) {
   // largest b with sum_{j > b} hist[j] < want <= sum_{j >= b} hist[j]
@@ -31,64 +41,60 @@ __device__ __forceinline__ int find_bin(const int* hist, int want, int* above) {
   return 0;
 }
 
-__global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                 const int* __restrict__ flag,
-                                                                 float* __restrict__ out_val,
-                                                                 int* __restrict__ out_idx, int V, int K,
-                                                                 long long ldx) {
-  const int r = blockIdx.x;
-  if (flag != nullptr && flag[r] == 0) return;
-  const __nv_bfloat16* xr = x + (size_t)r * ldx;
-  __shared__ int hist[256];
-  __shared__ int whist[TOPK_THREADS / 32][256];   // per-warp histograms: logits cluster in few bins
-  __shared__ int s_bin, s_above;
-  __shared__ int warp_cnt[2][32];
-  __shared__ uint32_t sel_key[128];
-  __shared__ int sel_idx[128];
-  __shared__ int s_ngt, s_neq;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+struct TopkShared {
+  int scratch[8192];            // fast path: two 4096-bin histograms; fallback: 32 per-warp 256-bin histograms
+  uint32_t cand_key[TOPK_CAND];
+  int cand_idx[TOPK_CAND];
+  int hist[256];
+  int warp_cnt[2][32];
+  int s_bin, s_above, s_ngt, s_neq, s_cnt;
+};
 
-  // pass 1: high byte
-  for (int i = tid; i < (TOPK_THREADS / 32) * 256; i += TOPK_THREADS) (&whist[0][0])[i] = 0;
+// Fallback: exact for any input, index-ordered gather with two block barriers per 1024 elements.
+__device__ __noinline__ void topk_ordered_path(TopkShared& sh, const __nv_bfloat16* __restrict__ xr, float* out_val,
+                                               int* out_idx, int V, int K) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int (*whist)[256] = reinterpret_cast<int (*)[256]>(sh.scratch);
+  uint32_t* sel_key = sh.cand_key;
+  int* sel_idx = sh.cand_idx;
+  __syncthreads();
+  for (int i = tid; i < (TOPK_THREADS / 32) * 256; i += TOPK_THREADS) sh.scratch[i] = 0;
   __syncthreads();
   for (int i = tid; i < V; i += TOPK_THREADS) atomicAdd(&whist[warp][order_key(xr[i]) >> 8], 1);
   __syncthreads();
-  if (tid < 256) { int t = 0; for (int w = 0; w < TOPK_THREADS / 32; ++w) t += whist[w][tid]; hist[tid] = t; }
+  if (tid < 256) { int t = 0; for (int w = 0; w < TOPK_THREADS / 32; ++w) t += whist[w][tid]; sh.hist[tid] = t; }
   __syncthreads();
-  if (tid == 0) { int ab; s_bin = find_bin(hist, K, &ab); s_above = ab; }
+  if (tid == 0) { int ab; sh.s_bin = find_bin(sh.hist, K, &ab); sh.s_above = ab; }
   __syncthreads();
-  const int b1 = s_bin;
-  const int above1 = s_above;
+  const int b1 = sh.s_bin;
+  const int above1 = sh.s_above;
   __syncthreads();
-  // pass 2: low byte among keys whose high byte is b1
-  for (int i = tid; i < (TOPK_THREADS / 32) * 256; i += TOPK_THREADS) (&whist[0][0])[i] = 0;
+  for (int i = tid; i < (TOPK_THREADS / 32) * 256; i += TOPK_THREADS) sh.scratch[i] = 0;
   __syncthreads();
   for (int i = tid; i < V; i += TOPK_THREADS) {
     const uint32_t k = order_key(xr[i]);
     if ((int)(k >> 8) == b1) atomicAdd(&whist[warp][k & 255], 1);
   }
   __syncthreads();
-  if (tid < 256) { int t = 0; for (int w = 0; w < TOPK_THREADS / 32; ++w) t += whist[w][tid]; hist[tid] = t; }
+  if (tid < 256) { int t = 0; for (int w = 0; w < TOPK_THREADS / 32; ++w) t += whist[w][tid]; sh.hist[tid] = t; }
   __syncthreads();
-  if (tid == 0) { int ab; s_bin = find_bin(hist, K - above1, &ab); s_above = ab; s_ngt = 0; s_neq = 0; }
+  if (tid == 0) { int ab; sh.s_bin = find_bin(sh.hist, K - above1, &ab); sh.s_above = ab; sh.s_ngt = 0; sh.s_neq = 0; }
   __syncthreads();
-  const uint32_t thr = ((uint32_t)b1 << 8) | (uint32_t)s_bin;
-  const int n_gt_total = above1 + s_above;     // keys strictly above the threshold (< K)
+  const uint32_t thr = ((uint32_t)b1 << 8) | (uint32_t)sh.s_bin;
+  const int n_gt_total = above1 + sh.s_above;  // keys strictly above the threshold (< K)
   const int need_eq = K - n_gt_total;          // how many threshold ties to take (>= 1)
   if (tid < 128) { sel_key[tid] = 0; sel_idx[tid] = 0x7fffffff; }
   __syncthreads();
-
-  // pass 3: index-ordered gather
   for (int base = 0; base < V; base += TOPK_THREADS) {
     const int i = base + tid;
     uint32_t k = 0;
     bool gt = false, eq = false;
     if (i < V) { k = order_key(xr[i]); gt = k > thr; eq = k == thr; }
     const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
-    if (lane == 0) { warp_cnt[0][warp] = __popc(mg); warp_cnt[1][warp] = __popc(me); }
+    if (lane == 0) { sh.warp_cnt[0][warp] = __popc(mg); sh.warp_cnt[1][warp] = __popc(me); }
     __syncthreads();
-    int og = s_ngt, oe = s_neq;
-    for (int w = 0; w < warp; ++w) { og += warp_cnt[0][w]; oe += warp_cnt[1][w]; }
+    int og = sh.s_ngt, oe = sh.s_neq;
+    for (int w = 0; w < warp; ++w) { og += sh.warp_cnt[0][w]; oe += sh.warp_cnt[1][w]; }
     og += __popc(mg & ((1u << lane) - 1));
     oe += __popc(me & ((1u << lane) - 1));
     if (gt && og < 128) { sel_key[og] = k; sel_idx[og] = i; }
@@ -96,8 +102,8 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bflo
     __syncthreads();
     if (tid == 0) {
       int tg = 0, te = 0;
-      for (int w = 0; w < TOPK_THREADS / 32; ++w) { tg += warp_cnt[0][w]; te += warp_cnt[1][w]; }
-      s_ngt += tg; s_neq += te;
+      for (int w = 0; w < TOPK_THREADS / 32; ++w) { tg += sh.warp_cnt[0][w]; te += sh.warp_cnt[1][w]; }
+      sh.s_ngt += tg; sh.s_neq += te;
     }
     __syncthreads();
   }
@@ -120,10 +126,105 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bflo
     }
   }
   if (tid < K) {
-    const uint32_t k = sel_key[tid];
-    const uint16_t u = (k & 0x8000) ? (uint16_t)(k & 0x7fff) : (uint16_t)~k;
-    out_val[(size_t)r * K + tid] = __bfloat162float(__ushort_as_bfloat16(u));
-    out_idx[(size_t)r * K + tid] = sel_idx[tid];
+    out_val[tid] = key_value(sel_key[tid]);
+    out_idx[tid] = sel_idx[tid];
+  }
+}
+
+__global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const int* __restrict__ flag,
+                                                                 float* __restrict__ out_val,
+                                                                 int* __restrict__ out_idx, int V, int K,
+                                                                 long long ldx, int force_ordered) {
+  const int r = blockIdx.x;
+  if (flag != nullptr && flag[r] == 0) return;
+  const __nv_bfloat16* xr = x + (size_t)r * ldx;
+  float* ov = out_val + (size_t)r * K;
+  int* oi = out_idx + (size_t)r * K;
+  __shared__ TopkShared sh;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (force_ordered) { topk_ordered_path(sh, xr, ov, oi, V, K); return; }
+  const bool vec = (V % 8 == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+
+  // sweep 1: 4096-bin histogram of key >> 4 (two replicas, by warp parity, to thin out conflicts)
+  for (int i = tid; i < 8192; i += TOPK_THREADS) sh.scratch[i] = 0;
+  if (tid == 0) sh.s_cnt = 0;
+  __syncthreads();
+  int* myhist = sh.scratch + (warp & 1) * 4096;
+  if (vec) {
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    for (int i = tid; i < V / 8; i += TOPK_THREADS) {
+      const uint4 u = xv[i];
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&myhist[order_key(e[j]) >> 4], 1);
+    }
+  } else {
+    for (int i = tid; i < V; i += TOPK_THREADS) atomicAdd(&myhist[order_key(xr[i]) >> 4], 1);
+  }
+  __syncthreads();
+  // locate the bin of the K-th largest: thread t owns bins 4t..4t+3; suffix sums over threads
+  int hb[4], own = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { hb[j] = sh.scratch[4 * tid + j] + sh.scratch[4096 + 4 * tid + j]; own += hb[j]; }
+  int sfx = own;                                 // sum over lanes >= lane of this warp
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_down_sync(0xffffffffu, sfx, o);
+    if (lane + o < 32) sfx += y;
+  }
+  if (lane == 0) sh.warp_cnt[0][warp] = sfx;
+  __syncthreads();
+  int higher = 0;
+  for (int w = warp + 1; w < TOPK_THREADS / 32; ++w) higher += sh.warp_cnt[0][w];
+  const int above_grp = sfx - own + higher;      // keys in bins above this thread's four
+  if (above_grp < K && K <= above_grp + own) {
+    int acc = above_grp;
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      if (acc < K && K <= acc + hb[j]) { sh.s_bin = 4 * tid + j; sh.s_above = acc; }
+      acc += hb[j];
+    }
+  }
+  __syncthreads();
+  const uint32_t bin12 = (uint32_t)sh.s_bin;
+  // sweep 2: collect every key in or above that bin
+  if (vec) {
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    for (int i = tid; i < V / 8; i += TOPK_THREADS) {
+      const uint4 u = xv[i];
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t k = order_key(e[j]);
+        if ((k >> 4) >= bin12) {
+          const int slot = atomicAdd(&sh.s_cnt, 1);
+          if (slot < TOPK_CAND) { sh.cand_key[slot] = k; sh.cand_idx[slot] = i * 8 + j; }
+        }
+      }
+    }
+  } else {
+    for (int i = tid; i < V; i += TOPK_THREADS) {
+      const uint32_t k = order_key(xr[i]);
+      if ((k >> 4) >= bin12) {
+        const int slot = atomicAdd(&sh.s_cnt, 1);
+        if (slot < TOPK_CAND) { sh.cand_key[slot] = k; sh.cand_idx[slot] = i; }
+      }
+    }
+  }
+  __syncthreads();
+  const int C = sh.s_cnt;
+  if (C > TOPK_CAND) { topk_ordered_path(sh, xr, ov, oi, V, K); return; }
+  // rank every candidate among the candidates: its rank is its slot in the sorted output
+  for (int c = tid; c < C; c += TOPK_THREADS) {
+    const uint32_t kc = sh.cand_key[c];
+    const int ic = sh.cand_idx[c];
+    int rank = 0;
+    for (int j = 0; j < C; ++j) {
+      const uint32_t kj = sh.cand_key[j];
+      rank += (kj > kc) || (kj == kc && sh.cand_idx[j] < ic);
+    }
+    if (rank < K) { ov[rank] = key_value(kc); oi[rank] = ic; }
   }
 }
 
@@ -345,13 +446,24 @@ __global__ void tick_end_kernel(const TickState s, const int* __restrict__ need_
 
 using namespace tahb;
 
-extern "C" int tahb_topk_rows(const void* x, const int* flag, float* out_val, int* out_idx, int rows, int V, int K,
-                              long long ldx, cudaStream_t stream) {
+static int topk_launch(const void* x, const int* flag, float* out_val, int* out_idx, int rows, int V, int K,
+                       long long ldx, int force_ordered, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (K < 1 || K > 128 || K > V) return -1;
   topk_rows_kernel<<<rows, TOPK_THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), flag, out_val,
-                                                      out_idx, V, K, ldx);
+                                                      out_idx, V, K, ldx, force_ordered);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_topk_rows(const void* x, const int* flag, float* out_val, int* out_idx, int rows, int V, int K,
+                              long long ldx, cudaStream_t stream) {
+  return topk_launch(x, flag, out_val, out_idx, rows, V, K, ldx, 0, stream);
+}
+
+// Same result through the index-ordered path only (the fast path's fallback), for testing.
+extern "C" int tahb_topk_rows_ordered(const void* x, const int* flag, float* out_val, int* out_idx, int rows, int V,
+                                      int K, long long ldx, cudaStream_t stream) {
+  return topk_launch(x, flag, out_val, out_idx, rows, V, K, ldx, 1, stream);
 }
 
 extern "C" int tahb_soft_embed_rows(const float* val, const int* idx, const int* flag, const void* E, void* out,

@@ -115,9 +115,10 @@ class TaHEngine:
     # ------------------------------------------------------------------------------------------
     # one backbone pass over packed tokens (prefill)
     # ------------------------------------------------------------------------------------------
-    def _packed_pass(self, x, pos, depth: int, slots, seg_k, seg_v, seg_base, seg_count, taps_out=None):
+    def _packed_pass(self, x, pos, depth: int, slots, seg_k, seg_v, seg_base, seg_count, seq_counts, taps_out=None):
         """x ``[n, H]`` packed tokens at iteration ``depth``.  seg_k/seg_v: per layer lists of the
-        dense K/V of shallower passes; this pass's K/V are appended as the last segment.  Returns
+        dense K/V of shallower passes; this pass's K/V are appended as the last segment.
+        ``seq_counts [B]``: how many of the packed tokens each sequence owns (query tiling).  Returns
         (final-norm hidden, list of this pass's dense (k, v) per layer)."""
         cfg, w, tp = self.cfg, self.w, self.tp
         n = x.shape[0]
@@ -132,6 +133,9 @@ class TaHEngine:
         t_o = bf(n, w.r_o) if lora else None
         t_down = bf(n, w.r_down) if lora else None
         tap_layers = self._tap_layers()
+        tensor_core_attn = hd in (64, 128) and os.environ.get("TAH_B200_NAIVE_PREFILL", "0") != "1"
+        if tensor_core_attn:
+            tile_q0, tile_qn = K.attn_tiles(seq_counts)
         xn = K.rms_norm(h, w.layers[0].ln1, cfg.rms_norm_eps, out=xn_buf)
         for li, L in enumerate(w.layers):
             if taps_out is not None and li in tap_layers:
@@ -148,7 +152,10 @@ class TaHEngine:
             own.append((kd, vd))
             ks = [sk[li] for sk in seg_k] + [kd]
             vs = [sv[li] for sv in seg_v] + [vd]
-            o = K.varlen_attn_naive(q, ks, vs, seg_base, seg_count, nq, nkv, hd, scale)
+            if tensor_core_attn:
+                o = K.prefill_attn(q, ks, vs, seg_base, seg_count, tile_q0, tile_qn, nq, nkv, hd, scale)
+            else:
+                o = K.varlen_attn_naive(q, ks, vs, seg_base, seg_count, nq, nkv, hd, scale)
             xn = self._row_parallel(o, L.w_o, L.a_o if lora else None, L.b_o, t_o, None, h, L.ln2, xn_buf, n)
             if lora:
                 t = K.gemm(xn, L.a_gu)
@@ -195,7 +202,7 @@ class TaHEngine:
         taps = {}
         base0 = seq_start[rows_idx].contiguous()
         count0 = (pos + 1).contiguous()
-        hn, kv0 = self._packed_pass(x, pos, 0, slots0, [], [], [base0], [count0], taps_out=taps)
+        hn, kv0 = self._packed_pass(x, pos, 0, slots0, [], [], [base0], [count0], lens, taps_out=taps)
         seg_k, seg_v = [[k for k, _ in kv0]], [[v for _, v in kv0]]
 
         # ---- continue decision for every prompt token ----------------------------------------
@@ -235,7 +242,7 @@ class TaHEngine:
             counts = [c[cur_idx].contiguous() for c in prev_counts] + [(rank1 + 1).contiguous()]
             # shallower segments (1..depth-1) index into the packed arrays of those passes: their
             # (base, count) were computed against those arrays when the passes ran
-            hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts)
+            hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts, cnt1)
             logits1 = self._lm_head(hn1)
             cum1 = cur_cum + logits1
             want_more = (extra[cur_idx] > depth) & (depth + 1 < self.max_iter)

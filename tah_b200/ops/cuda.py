@@ -285,17 +285,53 @@ def varlen_attn_naive(q, ks, vs, bases, counts, nq, nkv, hd, scale, out=None):
     return out
 
 
+def attn_tiles(seq_counts: torch.Tensor, tile: int = 128):
+    """Query tiles for :func:`prefill_attn`: every sequence's packed tokens (``seq_counts[b]`` of
+    them, sequences laid out back to back) are cut into runs of at most ``tile`` tokens.  Returns
+    int32 ``(tile_q0, tile_qn)``."""
+    cnt = seq_counts.to(torch.int64)
+    per = (cnt + tile - 1) // tile
+    n_tiles = int(per.sum())
+    dev = cnt.device
+    seq_of = torch.repeat_interleave(torch.arange(cnt.numel(), device=dev), per, output_size=n_tiles)
+    rank = torch.arange(n_tiles, device=dev) - (torch.cumsum(per, 0) - per)[seq_of]
+    q0 = (torch.cumsum(cnt, 0) - cnt)[seq_of] + tile * rank
+    qn = torch.clamp(cnt[seq_of] - tile * rank, max=tile)
+    return q0.to(torch.int32).contiguous(), qn.to(torch.int32).contiguous()
+
+
+def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, out=None):
+    """Packed duo-causal attention on the tensor cores (``csrc/attn_prefill.cu``).  Same contract as
+    :func:`varlen_attn_naive` plus the query tiling of :func:`attn_tiles`: the tokens of a tile belong
+    to one sequence, share ``bases[s]`` and have non-decreasing ``counts[s]``."""
+    if out is None:
+        out = torch.empty_like(q)
+    n = len(ks)
+    for t in (q, out, *ks, *vs):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("prefill_attn wants contiguous bf16 tensors")
+    n_kv = (c_ll * n)(*[k.shape[0] for k in ks])
+    _rc(lib().tahb_prefill_attn(_p(q), _p(out), _ptr_array(ks), _ptr_array(vs), n_kv, _ptr_array(bases),
+                                _ptr_array(counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
+                                c_ll(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale),
+                                _p(status_word(q.device)), _stream()), "tahb_prefill_attn")
+    return out
+
+
 # -------------------------------------------------------------------------------------------
 # sampling / control
 # -------------------------------------------------------------------------------------------
-def topk_rows(x, k: int, flag=None, out_val=None, out_idx=None):
+def topk_rows(x, k: int, flag=None, out_val=None, out_idx=None, ordered: bool = False):
+    """Sorted top-``k`` (value desc, index asc) of every flagged bf16 row.  ``ordered=True`` forces
+    the kernel's slower index-ordered path (its fallback for rows with > 1024 near-threshold ties)."""
     rows, V = x.shape
     if out_val is None:
         out_val = torch.zeros(rows, k, dtype=torch.float32, device=x.device)
     if out_idx is None:
         out_idx = torch.zeros(rows, k, dtype=torch.int32, device=x.device)
-    _rc(lib().tahb_topk_rows(_p(x), _p(flag), _p(out_val), _p(out_idx), c_int(rows), c_int(V), c_int(k),
-                             c_ll(x.stride(0)), _stream()), "tahb_topk_rows")
+    fn = lib().tahb_topk_rows_ordered if ordered else lib().tahb_topk_rows
+    _rc(fn(_p(x), _p(flag), _p(out_val), _p(out_idx), c_int(rows), c_int(V), c_int(k), c_ll(x.stride(0)), _stream()),
+        "tahb_topk_rows")
     return out_val, out_idx
 
 

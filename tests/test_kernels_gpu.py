@@ -180,6 +180,70 @@ def test_varlen_attention_duo_segments():
         _close(out[i].view(nq, hd), ref, atol=2e-2, rtol=2e-2)
 
 
+def _ref_duo_attention(q, ks, vs, bases, counts, nq, nkv, hd):
+    G = nq // nkv
+    out = torch.zeros(q.shape[0], nq, hd, dtype=torch.float32, device=q.device)
+    for i in range(q.shape[0]):
+        kk = torch.cat([k[b[i]:b[i] + c[i]] for k, b, c in zip(ks, bases, counts)])
+        vv = torch.cat([v[b[i]:b[i] + c[i]] for v, b, c in zip(vs, bases, counts)])
+        kk = kk.view(-1, nkv, hd).float().repeat_interleave(G, 1)
+        vv = vv.view(-1, nkv, hd).float().repeat_interleave(G, 1)
+        s = torch.einsum("hd,nhd->hn", q[i].view(nq, hd).float(), kk) * hd ** -0.5
+        out[i] = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), vv)
+    return out
+
+
+@pytest.mark.parametrize("hd,seqlens", [(64, [9, 30, 1]), (128, [200, 5, 131, 128]), (128, [300])])
+def test_prefill_attention_tcgen05_causal(hd, seqlens):
+    """Pass-0 packed causal attention on the tensor cores against an fp32 softmax reference."""
+    Kc = _cuda()
+    nq, nkv = 4, 2
+    n0 = sum(seqlens)
+    starts = [sum(seqlens[:i]) for i in range(len(seqlens))]
+    q = _rand(n0, nq * hd, seed=11)
+    k0, v0 = _rand(n0, nkv * hd, seed=12), _rand(n0, nkv * hd, seed=13)
+    b0 = [starts[s] for s, L in enumerate(seqlens) for _ in range(L)]
+    c0 = [j + 1 for L in seqlens for j in range(L)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    tq0, tqn = Kc.attn_tiles(torch.tensor(seqlens, device="cuda"))
+    out = Kc.prefill_attn(q, [k0], [v0], [i32(b0)], [i32(c0)], tq0, tqn, nq, nkv, hd, hd ** -0.5)
+    Kc.check_status()
+    ref = _ref_duo_attention(q, [k0], [v0], [b0], [c0], nq, nkv, hd)
+    _close(out.view(n0, nq, hd), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_prefill_attention_tcgen05_duo_segments(hd):
+    """Deeper pass: hard tokens attend all depth-0 keys up to their position plus the depth-1 keys
+    of earlier hard tokens of the same sequence (two segments, several key blocks)."""
+    Kc = _cuda()
+    nq, nkv = 4, 2
+    seqlens = [260, 40, 3]
+    starts = [0, 260, 300]
+    n0 = sum(seqlens)
+    g = torch.Generator().manual_seed(5)
+    hard = [sorted(torch.randperm(L, generator=g)[: max(1, (L * 3) // 5)].tolist()) for L in seqlens]
+    k0, v0 = _rand(n0, nkv * hd, seed=1), _rand(n0, nkv * hd, seed=2)
+    n1 = sum(len(h) for h in hard)
+    k1, v1 = _rand(n1, nkv * hd, seed=3), _rand(n1, nkv * hd, seed=4)
+    b0, c0, b1, c1 = [], [], [], []
+    off1 = 0
+    for s, hs in enumerate(hard):
+        for j, p in enumerate(hs):
+            b0.append(starts[s]); c0.append(p + 1); b1.append(off1); c1.append(j + 1)
+        off1 += len(hs)
+    q = _rand(n1, nq * hd, seed=5)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    tq0, tqn = Kc.attn_tiles(torch.tensor([len(h) for h in hard], device="cuda"))
+    out = Kc.prefill_attn(q, [k0, k1], [v0, v1], [i32(b0), i32(b1)], [i32(c0), i32(c1)], tq0, tqn, nq, nkv, hd,
+                          hd ** -0.5)
+    Kc.check_status()
+    ref = _ref_duo_attention(q, [k0, k1], [v0, v1], [b0, b1], [c0, c1], nq, nkv, hd)
+    _close(out.view(n1, nq, hd), ref, atol=2e-2, rtol=2e-2)
+    naive = Kc.varlen_attn_naive(q, [k0, k1], [v0, v1], [i32(b0), i32(b1)], [i32(c0), i32(c1)], nq, nkv, hd, hd ** -0.5)
+    _close(out, naive.float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("V,K", [(1024, 100), (151936, 100), (151936, 20), (5000, 1)])
 def test_topk_rows_sorted(V, K):
     Kc = _cuda()
@@ -194,6 +258,25 @@ def test_topk_rows_sorted(V, K):
     # ties at equal value are ordered by index
     same = val[keep][:, 1:] == val[keep][:, :-1]
     assert (idx[keep][:, 1:][same] > idx[keep][:, :-1][same]).all()
+    # the index-ordered fallback path gives the identical result
+    val2, idx2 = Kc.topk_rows(x, K, flag=flag, ordered=True)
+    assert torch.equal(val2[keep], val[keep]) and torch.equal(idx2[keep], idx[keep])
+
+
+def test_topk_rows_many_ties_takes_fallback():
+    """A row with far more ties at the threshold than the candidate buffer holds: the kernel falls
+    back to the index-ordered path and returns the lowest indices."""
+    Kc = _cuda()
+    V, K = 20000, 50
+    x = torch.zeros(3, V, dtype=torch.bfloat16, device="cuda")
+    x[1, 777] = 2.0
+    x[2, ::2] = -1.0
+    val, idx = Kc.topk_rows(x, K)
+    assert torch.equal(idx[0].cpu(), torch.arange(K, dtype=torch.int32))
+    assert idx[1, 0].item() == 777 and val[1, 0].item() == 2.0
+    assert torch.equal(idx[1, 1:].cpu(), torch.arange(K - 1, dtype=torch.int32))
+    assert torch.equal(idx[2].cpu(), torch.arange(1, 2 * K, 2, dtype=torch.int32))
+    assert (val[2] == 0).all()
 
 
 def test_soft_embed_and_logits_post():
