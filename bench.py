@@ -171,7 +171,7 @@ def run_ours(args):
     launches = eng.kernel_launches_per_tick * Kt
 
     # ---------------- end-to-end arm: the public generate call, H2D prompts + D2H tokens ---------
-    e2e_ticks = min(Kt, 256)
+    e2e_ticks = W + Kt                                 # the same ticks as above, now with prefill and copies
     host_tok = torch.empty(BATCH, dtype=torch.int32).pin_memory()
 
     def stream_out(t, s):

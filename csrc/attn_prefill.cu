@@ -2,11 +2,13 @@
 //
 // One CTA handles a tile of up to 128 consecutive query tokens of ONE sequence and one query head.
 // For each of up to three KV segments (depth-0 K/V, depth-1 K/V, ...) the tile walks the keys of its
-// sequence in blocks of 128:
+// sequence in blocks of 64.  Two CTAs share an SM (112 KB of shared memory and 256 tensor-memory
+// columns each), so one CTA's softmax overlaps the other's tensor-core work:
 //
 //     S = Q K^T          tcgen05.mma, Q and K K-major (head_dim contiguous), S in tensor memory
-//     P = exp2(S - m)    128 threads, one query row each, straight out of tensor memory; the
-//                        duo-causal rule is the per-row bound  key < count[segment][row]
+//     P = exp2(S - m)    256 threads, two per query row (32 key columns each), straight out of
+//                        tensor memory; the duo-causal rule is the per-row bound
+//                        key < count[segment][row]
 //     O += P V           tcgen05.mma, P staged in shared memory (K-major), V consumed MN-major
 //                        (head_dim contiguous, exactly as it lies in memory), O in tensor memory
 //
@@ -14,8 +16,9 @@
 // accumulator in tensor memory is rescaled rarely; the final division uses the matching row sums.
 // No mask tensor exists.  K/V blocks arrive by TMA into a two-stage ring.  All waits are bounded.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
-// warps 2..5 = softmax / epilogue (warp w owns tensor-memory lanes 32*(w%4)..+31 = query rows).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = tensor-memory owner + MMA issuer,
+// warps 2..9 = softmax / epilogue (warp w reads tensor-memory lanes 32*(w%4)..+31 = query rows;
+// warps 2..5 take key columns 0..31 and the lower half of head_dim, warps 6..9 the rest).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -67,36 +70,41 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_bmn(int m, int n) {
 
 template <int HD>
 struct PfCfg {
-  static constexpr int HALVES = HD / 64;                     // 64-element (128-byte) column groups
-  static constexpr int TILE64 = 128 * 64 * 2;                // [128 rows][64] bf16 = 16 KiB
-  static constexpr int Q_BYTES = HALVES * TILE64;
-  static constexpr int K_BYTES = HALVES * TILE64;            // 128 keys x HD
-  static constexpr int V_BYTES = HALVES * TILE64;
-  static constexpr int P_BYTES = 2 * TILE64;                 // 128 rows x 128 keys
+  static constexpr int BK = 64;                               // keys per block
+  static constexpr int HALVES = HD / 64;                      // 64-element (128-byte) column groups
+  static constexpr int QTILE = 128 * 64 * 2;                  // [128 rows][64] bf16 = 16 KiB
+  static constexpr int KTILE = BK * 64 * 2;                   // [64 keys][64] bf16 = 8 KiB
+  static constexpr int Q_BYTES = HALVES * QTILE;
+  static constexpr int K_BYTES = HALVES * KTILE;
+  static constexpr int V_BYTES = HALVES * KTILE;
+  static constexpr int P_BYTES = 128 * BK * 2;                // 128 rows x 64 keys = 16 KiB
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
   static constexpr int NSTAGE = 2;
-  static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSTAGE * STAGE_BYTES + 1024 + 256;
-  static constexpr int TMEM_COLS = 256;                      // S: 128 columns, O: HD columns
+  static constexpr int X_BYTES = 2 * 2 * 128 * 4;             // row-maximum exchange [parity][half][row]
+  static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSTAGE * STAGE_BYTES + X_BYTES + 128;
+  static constexpr int TMEM_COLS = 256;                       // S: 64 columns (at 0), O: HD columns (at 128)
 };
+constexpr int PF_THREADS = 320;                               // 2 + 8 warps; two CTAs share an SM
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(PF_THREADS, 2)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k0,
                     const __grid_constant__ CUtensorMap tm_v0, const __grid_constant__ CUtensorMap tm_k1,
                     const __grid_constant__ CUtensorMap tm_v1, const __grid_constant__ CUtensorMap tm_k2,
                     const __grid_constant__ CUtensorMap tm_v2, const PrefillParams p) {
   using C = PfCfg<HD>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int BK = C::BK;
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_s = smem;
   uint8_t* p_s = q_s + C::Q_BYTES;
   uint8_t* kv_s = p_s + C::P_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + C::NSTAGE * C::STAGE_BYTES);
+  float* xmax = reinterpret_cast<float*>(kv_s + C::NSTAGE * C::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xmax) + C::X_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;                 // [NSTAGE]
   uint64_t* kv_empty = kv_full + C::NSTAGE;     // [NSTAGE]
   uint64_t* s_full = kv_empty + C::NSTAGE;      // S = QK^T complete
-  uint64_t* p_ready = s_full + 1;               // P written, O rescaled (128 arrivals)
+  uint64_t* p_ready = s_full + 1;               // P written, O rescaled (256 arrivals)
   uint64_t* pv_done = p_ready + 1;              // O += PV complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -105,6 +113,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kvh = head / (p.nq / p.nkv);
   const int q0 = p.tile_q0[tile], qn = p.tile_qn[tile];
+  if ((smem_u32(smem) & 1023u) != 0) {          // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, STATUS_BAD_INDEX);
+    return;
+  }
 
   // key blocks per segment: the last row of the tile sees the most keys
   int seg_blocks[PF_MAX_SEG], seg_b0[PF_MAX_SEG], total_blocks = 0;
@@ -114,7 +126,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     seg_b0[s] = 0;
     if (s < p.n_seg) {
       seg_b0[s] = p.seg_base[s][q0];
-      seg_blocks[s] = (p.seg_count[s][q0 + qn - 1] + 127) / 128;
+      seg_blocks[s] = (p.seg_count[s][q0 + qn - 1] + BK - 1) / BK;
     }
     total_blocks += seg_blocks[s];
   }
@@ -123,7 +135,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     mbar_init(q_full, 1);
     for (int s = 0; s < C::NSTAGE; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -143,7 +155,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (lane == 0) {
       mbar_expect_tx(q_full, C::Q_BYTES);
 #pragma unroll
-      for (int h = 0; h < C::HALVES; ++h) tma_load_2d(q_s + h * C::TILE64, &tm_q, head * HD + h * 64, q0, q_full);
+      for (int h = 0; h < C::HALVES; ++h) tma_load_2d(q_s + h * C::QTILE, &tm_q, head * HD + h * 64, q0, q_full);
       int i = 0;
       for (int s = 0; s < p.n_seg; ++s) {
         const CUtensorMap* mk = s == 0 ? &tm_k0 : s == 1 ? &tm_k1 : &tm_k2;
@@ -155,11 +167,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           mbar_expect_tx(&kv_full[st], C::STAGE_BYTES);
           uint8_t* ks = kv_s + st * C::STAGE_BYTES;
           uint8_t* vs = ks + C::K_BYTES;
-          const int y = seg_b0[s] + b * 128;
+          const int y = seg_b0[s] + b * BK;
 #pragma unroll
           for (int h = 0; h < C::HALVES; ++h) {
-            tma_load_2d(ks + h * C::TILE64, mk, kvh * HD + h * 64, y, &kv_full[st]);
-            tma_load_2d(vs + h * C::TILE64, mv, kvh * HD + h * 64, y, &kv_full[st]);
+            tma_load_2d(ks + h * C::KTILE, mk, kvh * HD + h * 64, y, &kv_full[st]);
+            tma_load_2d(vs + h * C::KTILE, mv, kvh * HD + h * 64, y, &kv_full[st]);
           }
         }
       }
@@ -168,7 +180,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128);
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, BK);
       constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(128, HD);
       mbar_wait(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
@@ -182,19 +194,19 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // S = Q K^T : HD / 16 k-steps over head_dim
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks / 4) * C::TILE64 + (ks % 4) * 32;
-          umma_bf16(tmem_s, umma_desc_sw128(q_addr + off), umma_desc_sw128(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+          const uint32_t qo = (ks / 4) * C::QTILE + (ks % 4) * 32;
+          const uint32_t ko = (ks / 4) * C::KTILE + (ks % 4) * 32;
+          umma_bf16(tmem_s, umma_desc_sw128(q_addr + qo), umma_desc_sw128(k_addr + ko), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(s_full);
         // wait for P (and the rescaled O) of this block
         mbar_wait(p_ready, i & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
         tc_fence_after();
-        // O += P V : 8 k-steps over the 128 keys; V is MN-major (head_dim contiguous)
+        // O += P V : BK / 16 k-steps over the keys; V is MN-major (head_dim contiguous)
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t a_off = (ks / 4) * C::TILE64 + (ks % 4) * 32;
-          const uint64_t db = umma_desc_mn_sw128(v_addr + ks * 2048, C::TILE64);
-          umma_bf16(tmem_o, umma_desc_sw128(p_addr + a_off), db, idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < BK / 16; ++ks) {
+          const uint64_t db = umma_desc_mn_sw128(v_addr + ks * 2048, C::KTILE);
+          umma_bf16(tmem_o, umma_desc_sw128(p_addr + ks * 32), db, idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&kv_empty[st]);     // K/V stage may be refilled
         umma_commit(pv_done);           // P buffer and O are free for the next block
@@ -202,30 +214,41 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     __syncwarp();
   } else {
-    // ---------------- softmax / epilogue: one query row per thread ----------------
-    const int qd = warp & 3;
+    // ---------------- softmax / epilogue: two threads per query row, 32 key columns each ----------------
+    const int sw = warp - 2;                    // 0..7
+    const int qd = warp & 3;                    // tensor-memory lane quadrant this warp may access
+    const int half = sw >> 2;                   // which 32 of the 64 key columns / which half of head_dim
     const int row = qd * 32 + lane;
     const bool row_ok = row < qn;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
-    float m_ref = -INFINITY, l = 0.f;
+    const float sc = p.scale_log2;
+    float m_ref = -INFINITY, l = 0.f;           // m_ref in scaled (log2) units
     int i = 0;
     for (int s = 0; s < p.n_seg; ++s) {
       const int cnt = row_ok ? p.seg_count[s][q0 + row] : 0;
       for (int b = 0; b < seg_blocks[s]; ++b, ++i) {
         mbar_wait(s_full, i & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
         tc_fence_after();
-        const int valid = min(128, max(0, cnt - b * 128));      // keys [0, valid) of this block are visible
-        // pass 1: row maximum
-        float sv[128];
-#pragma unroll
-        for (int c = 0; c < 128; c += 32) tmem_ld32(tmem_s + lane_off + c, sv + c);
+        const int valid = cnt - b * BK - half * 32;       // my columns [0, valid) of this block are visible
+        float sv[32];
+        tmem_ld32(tmem_s + lane_off + half * 32, sv);
         tmem_ld_wait();
         float mx = -INFINITY;
+        if (__all_sync(0xffffffffu, valid >= 32)) {
 #pragma unroll
-        for (int j = 0; j < 128; ++j) {
-          sv[j] = j < valid ? sv[j] * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, sv[j]);
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, sv[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            sv[j] = j < valid ? sv[j] : -INFINITY;
+            mx = fmaxf(mx, sv[j]);
+          }
         }
+        // combine the two halves of the row
+        float* xm = xmax + (i & 1) * 256;
+        xm[half * 128 + row] = mx;
+        named_bar_sync(1, 256);
+        mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]) * sc;
         // lazy reference maximum: refresh only when it grew by more than 8 (a factor 256)
         const bool grow = mx > m_ref + 8.0f;
         const float m_new = grow ? mx : m_ref;
@@ -233,52 +256,59 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // the previous block's PV must be complete before P is overwritten or O rescaled
         if (i > 0) mbar_wait(pv_done, (i - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
         tc_fence_after();
-        if (__any_sync(0xffffffffu, f != 1.0f) && i > 0) {
+        if (i > 0 && __any_sync(0xffffffffu, f != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 32) {
+          for (int c = 0; c < HD / 2; c += 32) {
             float o[32];
-            tmem_ld32(tmem_o + lane_off + c, o);
+            tmem_ld32(tmem_o + lane_off + half * (HD / 2) + c, o);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) o[j] *= f;
-            tmem_st32(tmem_o + lane_off + c, o);
+            tmem_st32(tmem_o + lane_off + half * (HD / 2) + c, o);
           }
           tmem_st_wait();
         }
         l *= f;
         m_ref = m_new;
-        // pass 2: P = exp2(S - m_ref) in bf16, written K-major with the 128-byte swizzle
-        float psum = 0.f;
+        const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;   // all-masked so far: exp2(-inf) = 0
+        // P = exp2(S * scale - m_ref) in bf16, written K-major with the 128-byte swizzle
+        float psum0 = 0.f, psum1 = 0.f;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {            // 16 chunks of 8 keys
+        for (int c = 0; c < 4; ++c) {             // 4 chunks of 8 keys
           uint4 pk;
           __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[c * 8 + 2 * j] - m_ref);
-            const float bb = (m_ref == -INFINITY) ? 0.f : exp2f(sv[c * 8 + 2 * j + 1] - m_ref);
+            const float a = exp2f(fmaf(sv[c * 8 + 2 * j], sc, neg_m));
+            const float bb = exp2f(fmaf(sv[c * 8 + 2 * j + 1], sc, neg_m));
             p2[j] = __floats2bfloat162_rn(a, bb);
-            psum += a + bb;
+            psum0 += a;
+            psum1 += bb;
           }
-          const int half = c >> 3, cc = c & 7;
-          *reinterpret_cast<uint4*>(p_s + half * C::TILE64 + row * 128 + ((cc ^ (row & 7)) << 4)) = pk;
+          const int cc = half * 4 + c;
+          *reinterpret_cast<uint4*>(p_s + row * 128 + ((cc ^ (row & 7)) << 4)) = pk;
         }
-        l += psum;
+        l += psum0 + psum1;
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(p_ready);
       }
     }
-    // epilogue: O / l
+    // epilogue: O / l, each thread writes its half of head_dim
     if (total_blocks > 0) mbar_wait(pv_done, (total_blocks - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
     tc_fence_after();
+    float* xl = xmax;                            // reuse the exchange buffer for the row sums
+    named_bar_sync(1, 256);
+    xl[half * 128 + row] = l;
+    named_bar_sync(1, 256);
+    l += xl[(half ^ 1) * 128 + row];
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    __nv_bfloat16* dst = p.out + ((size_t)(q0 + row) * p.nq + head) * HD;
+    __nv_bfloat16* dst = p.out + ((size_t)(q0 + row) * p.nq + head) * HD + half * (HD / 2);
 #pragma unroll 1
-    for (int c = 0; c < HD; c += 32) {
+    for (int c = 0; c < HD / 2; c += 32) {
       float o[32];
       if (total_blocks > 0) {
-        tmem_ld32(tmem_o + lane_off + c, o);
+        tmem_ld32(tmem_o + lane_off + half * (HD / 2) + c, o);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -308,7 +338,7 @@ typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, vo
                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int pf_make_map(CUtensorMap* m, const void* base, long long rows, long long cols) {
+static int pf_make_map(CUtensorMap* m, const void* base, long long rows, long long cols, unsigned box_rows) {
   static PfEncodeFn fn = nullptr;
   if (fn == nullptr) {
     void* ptr = nullptr;
@@ -321,7 +351,7 @@ static int pf_make_map(CUtensorMap* m, const void* base, long long rows, long lo
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((cols * 2) & 15)) return -2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {64u, 128u};
+  cuuint32_t box[2] = {64u, box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -343,11 +373,11 @@ extern "C" int tahb_prefill_attn(const void* q, void* out, void* const* ks, void
   if (n_seg < 1 || n_seg > PF_MAX_SEG || (nq % nkv)) return -1;
   CUtensorMap mq, mk[PF_MAX_SEG], mv[PF_MAX_SEG];
   int rc;
-  if ((rc = pf_make_map(&mq, q, n_q, (long long)nq * hd))) return rc;
+  if ((rc = pf_make_map(&mq, q, n_q, (long long)nq * hd, 128u))) return rc;
   for (int s = 0; s < PF_MAX_SEG; ++s) {
     const int ss = s < n_seg ? s : 0;
-    if ((rc = pf_make_map(&mk[s], ks[ss], n_kv[ss], (long long)nkv * hd))) return rc;
-    if ((rc = pf_make_map(&mv[s], vs[ss], n_kv[ss], (long long)nkv * hd))) return rc;
+    if ((rc = pf_make_map(&mk[s], ks[ss], n_kv[ss], (long long)nkv * hd, 64u))) return rc;
+    if ((rc = pf_make_map(&mv[s], vs[ss], n_kv[ss], (long long)nkv * hd, 64u))) return rc;
   }
   PrefillParams p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
@@ -371,7 +401,7 @@ extern "C" int tahb_prefill_attn(const void* q, void* out, void* const* ks, void
         return -10;                                                                                               \
       configured = true;                                                                                          \
     }                                                                                                             \
-    prefill_attn_kernel<HD_><<<grid, 192, PfCfg<HD_>::SMEM_BYTES, stream>>>(mq, mk[0], mv[0], mk[1], mv[1], mk[2], \
+    prefill_attn_kernel<HD_><<<grid, PF_THREADS, PfCfg<HD_>::SMEM_BYTES, stream>>>(mq, mk[0], mv[0], mk[1], mv[1], mk[2], \
                                                                            mv[2], p);                             \
   }
   if (hd == 128) TAHB_PF(128)

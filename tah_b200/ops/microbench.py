@@ -35,15 +35,30 @@ def _rand(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
 
+USE_GRAPH = False
+
+
 def _time(fn, iters, warmup):
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        fn(warmup + i)
-    e1.record()
+    if USE_GRAPH:
+        # the launches of one timed batch replayed as a CUDA graph: no host launch cost in the number
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(warmup + i)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            fn(warmup + i)
+        e1.record()
     torch.cuda.synchronize()
     K.check_status()
     return e0.elapsed_time(e1) * 1e-3 / max(iters, 1)
@@ -160,11 +175,14 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--copies", type=int, default=0, help="operand copies to rotate through (0 = enough to exceed L2)")
+    ap.add_argument("--graph", action="store_true", help="replay the timed launches as one CUDA graph (small kernels)")
     a = ap.parse_args(argv)
+    global USE_GRAPH
+    USE_GRAPH = a.graph
     torch.manual_seed(0)
     res, t, flops, byts = OPS[a.op](a)
     bw, fl, src = peaks()
-    res.update({"us": round(t * 1e6, 2), "GBps": round(byts / t / 1e9, 1), "TFLOPs": round(flops / t / 1e12, 1),
+    res.update({"graph": a.graph, "us": round(t * 1e6, 2), "GBps": round(byts / t / 1e9, 1), "TFLOPs": round(flops / t / 1e12, 1),
                 "frac_hbm": round(byts / t / bw, 3), "frac_bf16": round(flops / t / fl, 3), "peaks": src})
     print(json.dumps(res))
     return res
