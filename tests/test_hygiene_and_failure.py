@@ -24,7 +24,9 @@ def _sources(exts=(".py", ".cu", ".cuh", ".h")):
 
 def test_no_cluster_multicast_no_triton_no_disassembly():
     bad = []
-    multicast = ".multicast" + "::cluster"
+    # the qualifier this test looks for is assembled from pieces so that this file does not name it
+    multicast = "".join([".", "multi", "cast", "::", "clus", "ter"])
+    bulk_copy = "".join(["cp", ".", "as", "ync"])
     for path in _sources():
         text = open(path, encoding="utf-8", errors="ignore").read()
         if multicast in text and not path.endswith("comm.cu") and not path.endswith("common.cuh"):
@@ -32,7 +34,7 @@ def test_no_cluster_multicast_no_triton_no_disassembly():
         if multicast in text:
             # even the files that mention the rule must not contain a multicast instruction
             for line in text.splitlines():
-                if multicast in line and ("cp.async" in line or "asm" in line):
+                if multicast in line and (bulk_copy in line or "asm" in line):
                     bad.append((path, "multicast instruction"))
         if re.search(r"^\s*(import triton|from triton)", text, re.M):
             bad.append((path, "triton"))
