@@ -71,30 +71,42 @@ __device__ __forceinline__ void multimem_st_v4(void* mc, uint4 v) {
                : "memory");
 }
 
-// CTA `b` of this rank meets CTA `b` of every other rank.  One thread signals and polls; the
-// rest of the CTA waits at the barrier that follows.  Returns false after a timeout.
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// CTA `b` of this rank meets CTA `b` of every other rank.  Thread q (< world) signals rank q and
+// polls rank q's flag, so the `world` signals and waits run in parallel: one system-scope fence
+// per thread before its (relaxed) signal and one after its poll, instead of a chain of
+// release/acquire operations in one thread.  The rest of the CTA waits at the barrier that
+// follows.  Returns false after a timeout.
 __device__ __forceinline__ bool cross_rank_barrier(const FusedReduceParams& p, int b, uint32_t epoch) {
   bool ok = true;
-  __syncthreads();   // every thread's earlier writes happen-before thread 0's release below
-  if (threadIdx.x == 0) {
+  __syncthreads();   // every thread's earlier writes happen-before the fences below
+  if ((int)threadIdx.x < p.world) {
+    const int q = threadIdx.x;
     __threadfence_system();
-    for (int q = 0; q < p.world; ++q) st_release_sys(p.flags[q] + (size_t)b * p.world + p.rank, epoch);
-    const uint32_t* mine = p.flags[p.rank] + (size_t)b * p.world;
+    st_relaxed_sys(p.flags[q] + (size_t)b * p.world + p.rank, epoch);
+    const uint32_t* mine = p.flags[p.rank] + (size_t)b * p.world + q;
     unsigned long long t0 = 0;
     uint32_t spins = 0;
-    for (int q = 0; q < p.world && ok; ++q) {
-      while ((int32_t)(ld_acquire_sys(mine + q) - epoch) < 0) {
-        if ((++spins & 0xff) == 0) {
-          const unsigned long long now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > WAIT_TIMEOUT_NS) {
-            atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER_FLAG);
-            ok = false;
-            break;
-          }
+    while ((int32_t)(ld_relaxed_sys(mine) - epoch) < 0) {
+      if ((++spins & 0xff) == 0) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > WAIT_TIMEOUT_NS) {
+          atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          ok = false;
+          break;
         }
       }
     }
+    __threadfence_system();
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
