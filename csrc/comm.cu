@@ -202,6 +202,155 @@ __global__ void __launch_bounds__(256) fused_reduce_residual_norm_kernel(const F
   cross_rank_barrier(p, b, e0 + 2);                   // every rank's rows have landed everywhere
 }
 
+// ---------------------------------------------------------------------------------------------
+// Push-based variant (decode ticks).  The row-parallel GEMM has already done the reduce-scatter:
+// its epilogue stored every rank's partial rows into the OWNER's slot buffer
+// slot[src][row - row_lo][H] over NVLink and advanced the owner's arrival counter (gemm_tcgen05.cu,
+// push_rows).  This kernel therefore reads local memory only:
+//
+//   wait until the counter shows that all world * (H / 128) tile columns of the owned rows arrived,
+//   sum the `world` slots in rank order, add the residual, RMS-normalise, broadcast the normalised
+//   row to every rank's x buffer (`multimem.st` or peer stores), fence, and advance each peer's
+//   landing flag xflag[peer][this rank] by the rows written.
+//
+// Consumers (the column-parallel GEMM's TMA producer, lora_a_rows) wait on those flags themselves,
+// so the critical path per layer half is two one-way NVLink trips and no kernel-wide barrier.
+// Targets are local state advanced by the last CTA to finish (all CTAs read them at their start).
+// With `final_wait` the kernel also waits for the peers' rows itself, for consumers that cannot.
+// ---------------------------------------------------------------------------------------------
+struct PushReduceParams {
+  const __nv_bfloat16* slot;                      // local [world][rpr][H]
+  uint32_t* cnt;                                  // local arrival counter (peers add rows received)
+  uint32_t* cnt_target;                           // local state: counter value that completes this use
+  __nv_bfloat16* xout[COMM_MAX_RANKS];            // every rank's x buffer [M, H]
+  __nv_bfloat16* mc_xout;                         // multicast address of the x buffer or nullptr
+  uint32_t* xflag[COMM_MAX_RANKS];                // every rank's landing flags [world] (indexed by owner)
+  uint32_t* xtarget;                              // local state [world]: consumers' targets for this use
+  uint32_t* arrive;                               // local CTA arrival counter for the last-CTA update
+  __nv_bfloat16* h;
+  const __nv_bfloat16* ln_w;
+  int* status;
+  int M, H, rank, world, rpr;
+  float eps;
+  int add_residual, final_wait;
+};
+
+template <int VPT>
+__global__ void __launch_bounds__(256) push_reduce_norm_bcast_kernel(const PushReduceParams p) {
+  __shared__ float red[8];
+  __shared__ int s_ok;
+  const int b = blockIdx.x;
+  const int row_lo = p.rank * p.rpr;
+  const int row_hi = min(p.M, row_lo + p.rpr);
+  const int rows_owned = max(0, row_hi - row_lo);
+  if (threadIdx.x == 0) {
+    // all partial tiles of my rows have arrived: world sources x (H / 128) column tiles x rows
+    const uint32_t want = *p.cnt_target + (uint32_t)(p.world * (p.H / 128) * rows_owned);
+    uint32_t tgt[1] = {want};
+    s_ok = wait_peer_rows(p.cnt, tgt, 1, p.status) ? 1 : 0;
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  const int nvec = p.H / 8;
+  int rows_done = 0;
+  for (int row = row_lo + b; ok && row < row_hi; row += gridDim.x) {
+    ++rows_done;
+    const size_t off = (size_t)row * p.H;
+    float v[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nvec) {
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = 0.f;
+        for (int q = 0; q < p.world; ++q) {
+          const uint4 r = ld_relaxed_sys_v4(p.slot + ((size_t)q * p.rpr + (row - row_lo)) * p.H + idx * 8);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); a[2 * j] += f.x; a[2 * j + 1] += f.y; }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = bf16_round(a[j]);
+        uint4 hr = make_uint4(0, 0, 0, 0);
+        if (p.add_residual) hr = *reinterpret_cast<const uint4*>(p.h + off + idx * 8);
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&hr);
+        uint4 ho;
+        __nv_bfloat162* ho2 = reinterpret_cast<__nv_bfloat162*>(&ho);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(hh[j]);
+          const float x0 = bf16_round(a[2 * j] + f.x), x1 = bf16_round(a[2 * j + 1] + f.y);
+          v[i][2 * j] = x0;
+          v[i][2 * j + 1] = x1;
+          ss += x0 * x0 + x1 * x1;
+          ho2[j] = __floats2bfloat162_rn(x0, x1);
+        }
+        *reinterpret_cast<uint4*>(p.h + off + idx * 8) = ho;
+      }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float rstd = rsqrtf(tot / (float)p.H + p.eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nvec) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(p.ln_w + idx * 8);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = __bfloat1622float2(wh[j]);
+          oh[j] = __floats2bfloat162_rn(g.x * bf16_round(v[i][2 * j] * rstd), g.y * bf16_round(v[i][2 * j + 1] * rstd));
+        }
+        if (p.mc_xout != nullptr) {
+          multimem_st_v4(p.mc_xout + off + idx * 8, o);
+        } else {
+          for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.xout[q] + off + idx * 8) = o;
+        }
+      }
+    }
+  }
+  // my rows have been written everywhere: tell every rank how many landed from this owner
+  __syncthreads();
+  if ((int)threadIdx.x < p.world && rows_done > 0) {
+    __threadfence_system();
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.xflag[threadIdx.x] + p.rank), "r"((uint32_t)rows_done)
+                 : "memory");
+  }
+  // the last CTA of this launch advances the local targets for the next use
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(p.arrive, 1u) == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) {
+      *p.cnt_target += (uint32_t)(p.world * (p.H / 128) * rows_owned);
+      *p.arrive = 0;
+    }
+    if ((int)threadIdx.x < p.world) {
+      const int q = threadIdx.x;
+      const int q_rows = max(0, min(p.M, (q + 1) * p.rpr) - q * p.rpr);
+      p.xtarget[q] += (uint32_t)q_rows;
+    }
+    __syncthreads();
+    if (p.final_wait && threadIdx.x == 0) {
+      __threadfence();
+      wait_peer_rows(p.xflag[p.rank], p.xtarget, p.world, p.status);
+    }
+  }
+}
+
 }  // namespace tahb
 
 using namespace tahb;
@@ -238,6 +387,45 @@ extern "C" int tahb_fused_reduce_residual_norm(void* const* partial, void* const
   if (nvec <= 256) fused_reduce_residual_norm_kernel<1><<<grid, 256, 0, stream>>>(p);
   else if (nvec <= 512) fused_reduce_residual_norm_kernel<2><<<grid, 256, 0, stream>>>(p);
   else if (nvec <= 1024) fused_reduce_residual_norm_kernel<4><<<grid, 256, 0, stream>>>(p);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+
+// Push-based reduce + residual + RMSNorm + broadcast (see push_reduce_norm_bcast_kernel).
+// slot / cnt / cnt_target / xtarget / arrive / h are local; xout / xflag are arrays of `world`
+// pointers (peer addresses).  Rows are dealt out in blocks of `rpr`.
+extern "C" int tahb_push_reduce_norm_bcast(const void* slot, void* cnt, void* cnt_target, void* const* xout,
+                                           void* mc_xout, void* const* xflag, void* xtarget, void* arrive, void* h,
+                                           const void* ln_w, int* status, int M, int H, int rank, int world, int rpr,
+                                           float eps, int add_residual, int final_wait, int grid,
+                                           cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (world < 1 || world > COMM_MAX_RANKS || H % 128 || rpr <= 0) return -1;
+  PushReduceParams p;
+  p.slot = reinterpret_cast<const __nv_bfloat16*>(slot);
+  p.cnt = reinterpret_cast<uint32_t*>(cnt);
+  p.cnt_target = reinterpret_cast<uint32_t*>(cnt_target);
+  for (int q = 0; q < COMM_MAX_RANKS; ++q) {
+    const int qq = q < world ? q : 0;
+    p.xout[q] = reinterpret_cast<__nv_bfloat16*>(xout[qq]);
+    p.xflag[q] = reinterpret_cast<uint32_t*>(xflag[qq]);
+  }
+  p.mc_xout = reinterpret_cast<__nv_bfloat16*>(mc_xout);
+  p.xtarget = reinterpret_cast<uint32_t*>(xtarget);
+  p.arrive = reinterpret_cast<uint32_t*>(arrive);
+  p.h = reinterpret_cast<__nv_bfloat16*>(h);
+  p.ln_w = reinterpret_cast<const __nv_bfloat16*>(ln_w);
+  p.status = status;
+  p.M = M; p.H = H; p.rank = rank; p.world = world; p.rpr = rpr;
+  p.eps = eps;
+  p.add_residual = add_residual;
+  p.final_wait = final_wait;
+  const int nvec = H / 8;
+  if (grid < 1) grid = 1;
+  if (nvec <= 256) push_reduce_norm_bcast_kernel<1><<<grid, 256, 0, stream>>>(p);
+  else if (nvec <= 512) push_reduce_norm_bcast_kernel<2><<<grid, 256, 0, stream>>>(p);
+  else if (nvec <= 1024) push_reduce_norm_bcast_kernel<4><<<grid, 256, 0, stream>>>(p);
   else return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -94,6 +94,31 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Bounded wait of ONE thread until flag[q] has reached target[q] (wrap-around safe) for every q <
+// world.  The flags are local device memory that peers advance over NVLink after they have stored
+// rows into this GPU's memory; target[] is local state.  Returns false after a timeout (status set).
+__device__ __forceinline__ bool wait_peer_rows(const uint32_t* flag, const uint32_t* target, int world, int* status) {
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  for (int q = 0; q < world; ++q) {
+    const uint32_t want = target[q];
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag + q) : "memory");
+      if ((int32_t)(v - want) >= 0) break;
+      if ((++spins & 0xff) == 0) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > WAIT_TIMEOUT_NS) {
+          atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          return false;
+        }
+      }
+    }
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (no multicast anywhere in this library)
 // ---------------------------------------------------------------------------------------------

@@ -184,7 +184,9 @@ __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ E, const i
 __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ A,
                                                           __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
-                                                          int K, int R, long long ldx, long long ldt) {
+                                                          int K, int R, long long ldx, long long ldt,
+                                                          const uint32_t* wait_flag, const uint32_t* wait_target,
+                                                          int wait_world, int* status) {
   // grid (rows, ceil(R / 8)): a CTA owns 8 outputs of one row, one per warp, so that a gated row's
   // product is spread over R / 8 CTAs instead of running serially in one
   const int r = blockIdx.x;
@@ -195,6 +197,10 @@ __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* _
   if (gate != nullptr && gate[r] == 0) {
     if (lane == 0) out[j] = __float2bfloat16_rn(0.f);
     return;
+  }
+  if (wait_world > 0) {     // tensor parallel: x rows are broadcast by their owners (see comm.cu)
+    if (lane == 0) wait_peer_rows(wait_flag, wait_target, wait_world, status);
+    __syncwarp();
   }
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
   const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)j * K);
@@ -352,14 +358,28 @@ extern "C" int tahb_embed_gather(const void* E, const int* tok, void* out, int M
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int tahb_lora_a_rows(const void* x, const void* A, void* T, const int* gate, int M, int K, int R,
-                                long long ldx, long long ldt, cudaStream_t stream) {
+static int lora_a_rows_launch(const void* x, const void* A, void* T, const int* gate, int M, int K, int R,
+                              long long ldx, long long ldt, const void* wait_flag, const void* wait_target,
+                              int wait_world, int* status, cudaStream_t stream) {
   if (M <= 0 || R <= 0) return 0;
   if (K % 8) return -1;
-  lora_a_rows_kernel<<<dim3(M, (R + 7) / 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
-                                            reinterpret_cast<const __nv_bfloat16*>(A),
-                                            reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt);
+  lora_a_rows_kernel<<<dim3(M, (R + 7) / 8), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(A),
+      reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt, reinterpret_cast<const uint32_t*>(wait_flag),
+      reinterpret_cast<const uint32_t*>(wait_target), wait_flag ? wait_world : 0, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_lora_a_rows(const void* x, const void* A, void* T, const int* gate, int M, int K, int R,
+                                long long ldx, long long ldt, cudaStream_t stream) {
+  return lora_a_rows_launch(x, A, T, gate, M, K, R, ldx, ldt, nullptr, nullptr, 0, nullptr, stream);
+}
+
+// Tensor-parallel variant: gated rows first wait until the owners' broadcast of x has landed.
+extern "C" int tahb_lora_a_rows_tp(const void* x, const void* A, void* T, const int* gate, int M, int K, int R,
+                                   long long ldx, long long ldt, const void* wait_flag, const void* wait_target,
+                                   int wait_world, int* status, cudaStream_t stream) {
+  return lora_a_rows_launch(x, A, T, gate, M, K, R, ldx, ldt, wait_flag, wait_target, wait_world, status, stream);
 }
 
 extern "C" int tahb_swiglu(const void* gu, void* out, int M, int I, long long ld_in, long long ld_out,

@@ -31,6 +31,8 @@
 
 namespace tahb {
 
+constexpr int GEMM_MAX_RANKS = 8;
+
 struct GemmParams {
   __nv_bfloat16* out;
   const __nv_bfloat16* residual;
@@ -45,6 +47,21 @@ struct GemmParams {
   int tma_out;  // 1: stage the output tile in shared memory and write it with a TMA store
   int* status;
   unsigned long long* trace;   // optional [n_ctas][8] globaltimer stamps (debug aid), else nullptr
+  // Tensor-parallel reduce-scatter by push (row-parallel GEMMs): instead of writing `out`, the tile
+  // is stored into the symmetric slot buffer of the rank that owns its token rows,
+  // slot[owner][(my rank) * rpr + (row - owner * rpr)][f], and the owner's arrival counter is
+  // advanced by the number of rows stored (after a system-scope fence).
+  __nv_bfloat16* push_slot[GEMM_MAX_RANKS];
+  uint32_t* push_cnt[GEMM_MAX_RANKS];
+  int push_world;   // 0 = off
+  int push_rank;
+  int push_rpr;     // token rows per owner
+  // Tensor-parallel all-gather wait (column-parallel GEMMs): X rows arrive from their owners by
+  // peer stores; before the first X load the producer waits until flag[q] has reached target[q]
+  // for every owner q.  Both arrays are local device memory.
+  const uint32_t* wait_flag;
+  const uint32_t* wait_target;
+  int wait_world;   // 0 = off
 };
 
 template <int BN, bool DUAL>
@@ -92,6 +109,32 @@ __device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u,
     if (add_res) y = bf16_round(a) + __bfloat162float(*slot);
   }
   *slot = __float2bfloat16_rn(y);
+}
+
+// Copy `n_tok` staged rows ([token][128 features] bf16 in shared memory, tokens ta..ta+n_tok) into the
+// owners' slot buffers with 16-byte peer stores (128 epilogue threads: 16 lanes per 256-byte row),
+// then fence and advance each touched owner's arrival counter by the rows it received.
+__device__ __forceinline__ void push_rows(const GemmParams& p, const __nv_bfloat16* stg, int ta, int n_tok, int f0) {
+  const int e = threadIdx.x - 64;                 // 0..127
+  const int sub = e & 15, r0 = e >> 4;            // 16-byte piece of the row, first row of this thread
+  const int H = p.F;
+  for (int r = r0; r < n_tok; r += 8) {
+    const int t = ta + r;
+    if (t >= p.M) break;
+    const int owner = t / p.push_rpr;
+    const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 128 + sub * 8);
+    __nv_bfloat16* dst = p.push_slot[owner] + ((size_t)p.push_rank * p.push_rpr + (t - owner * p.push_rpr)) * H + f0 + sub * 8;
+    *reinterpret_cast<uint4*>(dst) = v;
+  }
+  named_bar_sync(1, 128);
+  if (e == 0 && ta < p.M) {
+    __threadfence_system();
+    const int tb = min(p.M, ta + n_tok);
+    for (int owner = ta / p.push_rpr; owner * p.push_rpr < tb; ++owner) {
+      const int lo = max(ta, owner * p.push_rpr), hi = min(tb, (owner + 1) * p.push_rpr);
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.push_cnt[owner]), "r"((uint32_t)(hi - lo)) : "memory");
+    }
+  }
 }
 
 // bytes of the split-K receive area: (S - 1) source blocks of [cols_per_rank][128] floats
@@ -152,6 +195,10 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      if (p.wait_world > 0) {
+        if (!wait_peer_rows(p.wait_flag, p.wait_target, p.wait_world, p.status)) *abort_flag = 1;
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // the TMA loads below see the landed rows
+      }
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % C::NS;
         const uint32_t ph = (i / C::NS) & 1;
@@ -230,7 +277,10 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
-      if (p.tma_out) {
+      if (p.push_world > 0) {
+        named_bar_sync(1, 128);
+        push_rows(p, stg, t0, BN, f0);
+      } else if (p.tma_out) {
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
@@ -330,7 +380,10 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
-      if (p.tma_out) {
+      if (p.push_world > 0) {
+        named_bar_sync(1, 128);
+        push_rows(p, stg, t0 + rank * per, per, f0);
+      } else if (p.tma_out) {
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
@@ -437,11 +490,22 @@ extern "C" void tahb_gemm_set_trace(unsigned long long* trace) { g_gemm_trace = 
 // bn = token-tile width (16/32/64/128/256, 0 = choose from M); splits = split-K cluster size (1,2,4,8).
 // Returns 0 on success, a negative code on a host-side error.  *status (device int) is set non-zero
 // by the kernel if a bounded wait ran out.
-extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* residual, const void* W2,
-                         const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
-                         long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
-                         int* status, cudaStream_t stream) {
+struct GemmTpArgs {
+  void* const* push_slot = nullptr;     // [world] slot buffers (peer pointers), or null
+  void* const* push_cnt = nullptr;      // [world] arrival counters (peer pointers)
+  int push_world = 0, push_rank = 0, push_rpr = 0;
+  const void* wait_flag = nullptr;      // local [world] flags, or null
+  const void* wait_target = nullptr;    // local [world] targets
+  int wait_world = 0;
+};
+
+static int gemm_impl(const void* W, const void* X, void* out, const void* residual, const void* W2,
+                     const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
+                     long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
+                     int* status, cudaStream_t stream, const GemmTpArgs& tp) {
   if (M <= 0 || F <= 0) return 0;
+  const bool push = tp.push_world > 0;
+  if (push && (dual || residual != nullptr || F % 128 || tp.push_world > GEMM_MAX_RANKS || tp.push_rpr <= 0)) return -23;
   if (K % 64 || R % 64 || K <= 0) return -20;
   if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   if (splits < 1) splits = 1;
@@ -461,12 +525,22 @@ extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* re
   }
   // output (and residual) through TMA when their layout allows it, else element-wise stores
   CUtensorMap mo, mr;
-  int tma_out = make_map(&mo, out, M, F, ldo, bn / splits, false) == 0;
+  int tma_out = !push && make_map(&mo, out, M, F, ldo, bn / splits, false) == 0;
   if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F, ldr, bn / splits, false) == 0;
   if (!tma_out) mo = mw;
   if (!tma_out || residual == nullptr) mr = mo;
   GemmParams p;
-  p.tma_out = tma_out;
+  p.tma_out = tma_out || push;          // push mode stages the tile in shared memory as well
+  p.push_world = tp.push_world;
+  p.push_rank = tp.push_rank;
+  p.push_rpr = tp.push_rpr;
+  for (int q = 0; q < GEMM_MAX_RANKS; ++q) {
+    p.push_slot[q] = push && q < tp.push_world ? reinterpret_cast<__nv_bfloat16*>(tp.push_slot[q]) : nullptr;
+    p.push_cnt[q] = push && q < tp.push_world ? reinterpret_cast<uint32_t*>(tp.push_cnt[q]) : nullptr;
+  }
+  p.wait_flag = reinterpret_cast<const uint32_t*>(tp.wait_flag);
+  p.wait_target = reinterpret_cast<const uint32_t*>(tp.wait_target);
+  p.wait_world = tp.wait_flag != nullptr ? tp.wait_world : 0;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ld_out = (int)ldo;
@@ -492,4 +566,29 @@ extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* re
       return -22;
   }
 #undef TAHB_LAUNCH
+}
+
+extern "C" int tahb_gemm(const void* W, const void* X, void* out, const void* residual, const void* W2,
+                         const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
+                         long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
+                         int* status, cudaStream_t stream) {
+  return gemm_impl(W, X, out, residual, W2, X2, M, F, K, R, ldw, ldx, ldo, ldr, ldw2, ldx2, dual, up_off, splits, bn,
+                   status, stream, GemmTpArgs());
+}
+
+// Tensor-parallel variants of the same GEMM (see GemmParams): `push_*` turns the epilogue into a
+// reduce-scatter by peer stores (out is ignored, F must be the full hidden size), `wait_*` makes the
+// producer wait for the X rows that the owners broadcast.
+extern "C" int tahb_gemm_tp(const void* W, const void* X, void* out, const void* residual, const void* W2,
+                            const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
+                            long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
+                            int* status, cudaStream_t stream, void* const* push_slot, void* const* push_cnt,
+                            int push_world, int push_rank, int push_rpr, const void* wait_flag,
+                            const void* wait_target, int wait_world) {
+  GemmTpArgs tp;
+  tp.push_slot = push_slot; tp.push_cnt = push_cnt; tp.push_world = push_slot ? push_world : 0;
+  tp.push_rank = push_rank; tp.push_rpr = push_rpr;
+  tp.wait_flag = wait_flag; tp.wait_target = wait_target; tp.wait_world = wait_world;
+  return gemm_impl(W, X, out, residual, W2, X2, M, F, K, R, ldw, ldx, ldo, ldr, ldw2, ldx2, dual, up_off, splits, bn,
+                   status, stream, tp);
 }

@@ -343,7 +343,7 @@ class TaHEngine:
         s.tensors = tensors
         return s
 
-    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M):
+    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M, push=False, final=False):
         """Row-parallel projection + residual + the RMSNorm that follows it.
 
         One GPU: the GEMM epilogue adds the residual in place and a norm kernel follows.  Tensor
@@ -360,6 +360,14 @@ class TaHEngine:
         if tp is None:
             K.gemm(x, w_, residual=h, out=h, **kw)
             return K.rms_norm(h, ln_w, cfg.rms_norm_eps, out=xn_out)
+        desc = tp.push_desc(M) if push else None
+        if desc is not None:
+            # reduce-scatter inside the GEMM epilogue (peer stores), then sum + norm + broadcast on
+            # the owners; the consumers of xn wait for the broadcast rows themselves (self._xn_wait)
+            K.gemm(x, w_, tp_push=desc, **kw)
+            self._xn_wait = None if final else tp.wait_desc
+            return tp.push_reduce_norm(M, h, ln_w, cfg.rms_norm_eps, add_residual=True, final_wait=final)
+        self._xn_wait = None
         K.gemm(x, w_, out=tp.partial[:M], **kw)
         return tp.fused_reduce_norm(M, h, ln_w, cfg.rms_norm_eps, add_residual=True)
 
@@ -377,27 +385,30 @@ class TaHEngine:
         s.h.copy_(s.x_in)
         pools = [[kv.layer_pool(d, li) for d in range(kv.n_depths)] for li in range(nL)]
         xn = K.rms_norm(s.h, w.layers[0].ln1, cfg.rms_norm_eps, out=s.xn)
+        self._xn_wait = None       # set by _row_parallel when xn is a tensor-parallel broadcast in flight
+        push = tp is not None and os.environ.get("TAH_B200_TP_PULL", "0") != "1"
         for li, L in enumerate(w.layers):
             if li in tl:
                 j = tl.index(li)
                 s.taps[:, j * H:(j + 1) * H].copy_(s.h if tp is None else tp.gather_rows(s.h, B))
             if lora:
-                K.lora_a_rows(xn, L.a_qkv, s.gate, out=s.t_qkv)
-                K.gemm(xn, L.w_qkv, x2=s.t_qkv, w2=L.b_qkv, out=s.qkv)
+                K.lora_a_rows(xn, L.a_qkv, s.gate, out=s.t_qkv, tp_wait=self._xn_wait)
+                K.gemm(xn, L.w_qkv, x2=s.t_qkv, w2=L.b_qkv, out=s.qkv, tp_wait=self._xn_wait)
             else:
-                K.gemm(xn, L.w_qkv, out=s.qkv)
+                K.gemm(xn, L.w_qkv, out=s.qkv, tp_wait=self._xn_wait)
             K.qk_norm_rope_kv(s.qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
                               q_out=s.q, caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size)
             K.decode_attn(s.q, pools[li], kv.page_table, kv.len, s.depth, nq, nkv, hd, self.page_size, scale, out=s.o)
-            xn = self._row_parallel(s.o, L.w_o, L.a_o if lora else None, L.b_o, s.t_o, s.gate, s.h, L.ln2, s.xn, B)
+            xn = self._row_parallel(s.o, L.w_o, L.a_o if lora else None, L.b_o, s.t_o, s.gate, s.h, L.ln2, s.xn, B,
+                                    push=push)
             if lora:
-                K.lora_a_rows(xn, L.a_gu, s.gate, out=s.t_gu)
-                K.gemm(xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act)
+                K.lora_a_rows(xn, L.a_gu, s.gate, out=s.t_gu, tp_wait=self._xn_wait)
+                K.gemm(xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
             else:
-                K.gemm(xn, L.w_gu, swiglu=True, out=s.act)
+                K.gemm(xn, L.w_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
             next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
             xn = self._row_parallel(s.act, L.w_down, L.a_down if lora else None, L.b_down, s.t_down, s.gate, s.h,
-                                    next_ln, s.xn, B)
+                                    next_ln, s.xn, B, push=push, final=li + 1 == nL)
         # xn is now the final-norm output of every row
         if cfg.num_hidden_layers in tl:
             j = tl.index(cfg.num_hidden_layers)

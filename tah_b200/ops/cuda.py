@@ -145,9 +145,14 @@ def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
-         bn: int = 0) -> torch.Tensor:
+         bn: int = 0, tp_push=None, tp_wait=None) -> torch.Tensor:
     """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
-    weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``."""
+    weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
+
+    Tensor parallel (see :class:`tah_b200.parallel.tp.TensorParallel`): ``tp_push =
+    (slot_ptrs, cnt_ptrs, rank, rows_per_rank)`` replaces the output by peer stores of the tile
+    rows into their owners' slot buffers (reduce-scatter by push, ``out`` is not written);
+    ``tp_wait = (flags, targets)`` makes the kernel wait for the broadcast rows of ``x``."""
     _check_bf16_2d(x, "x")
     _check_bf16_2d(w, "w")
     M, K = x.shape
@@ -161,7 +166,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         R = x2.shape[1]
         if w2.shape[1] != R or w2.shape[0] != w.shape[0] or x2.shape[0] != M:
             raise ValueError("K-extension operands do not match")
-    if out is None:
+    if tp_push is not None:
+        out = x.new_empty(0, F) if out is None else out
+    elif out is None:
         out = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
     else:
         _check_bf16_2d(out, "out")
@@ -171,12 +178,27 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         bn, splits = plan_gemm(M, F, K, R, swiglu)
     elif splits is None:
         splits = 1
-    rc = lib().tahb_gemm(_p(w), _p(x), _p(out), _p(residual), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R),
-                         c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
-                         c_ll(residual.stride(0) if residual is not None else 0),
-                         c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
-                         c_int(1 if swiglu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
-                         _p(status_word(x.device)), _stream())
+    args = (_p(w), _p(x), _p(out), _p(residual), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R),
+            c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
+            c_ll(residual.stride(0) if residual is not None else 0),
+            c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
+            c_int(1 if swiglu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+            _p(status_word(x.device)), _stream())
+    if tp_push is None and tp_wait is None:
+        rc = lib().tahb_gemm(*args)
+    else:
+        if tp_push is not None:
+            slot_ptrs, cnt_ptrs, rank, rpr = tp_push
+            n = len(slot_ptrs)
+            push = ((c_void_p * n)(*slot_ptrs), (c_void_p * n)(*cnt_ptrs), c_int(n), c_int(rank), c_int(rpr))
+        else:
+            push = (None, None, c_int(0), c_int(0), c_int(0))
+        if tp_wait is not None:
+            flags, targets = tp_wait
+            wait = (_p(flags), _p(targets), c_int(flags.numel()))
+        else:
+            wait = (None, None, c_int(0))
+        rc = lib().tahb_gemm_tp(*args, *push, *wait)
     _rc(rc, "tahb_gemm")
     return out
 
@@ -226,14 +248,22 @@ def embed_gather(E, tok, out=None):
     return out
 
 
-def lora_a_rows(x, A, gate=None, out=None):
+def lora_a_rows(x, A, gate=None, out=None, tp_wait=None):
+    """``out[r] = gate[r] ? x[r] @ A^T : 0`` for the few gated rows of a decode tick.  ``tp_wait =
+    (flags, targets)``: gated rows first wait for the tensor-parallel broadcast of ``x``."""
     _check_bf16_2d(x, "x")
     M, K = x.shape
     R = A.shape[0]
     if out is None:
         out = torch.empty(M, R, dtype=torch.bfloat16, device=x.device)
-    _rc(lib().tahb_lora_a_rows(_p(x), _p(A), _p(out), _p(gate), c_int(M), c_int(K), c_int(R), c_ll(x.stride(0)),
-                               c_ll(out.stride(0)), _stream()), "tahb_lora_a_rows")
+    if tp_wait is None:
+        _rc(lib().tahb_lora_a_rows(_p(x), _p(A), _p(out), _p(gate), c_int(M), c_int(K), c_int(R), c_ll(x.stride(0)),
+                                   c_ll(out.stride(0)), _stream()), "tahb_lora_a_rows")
+    else:
+        flags, targets = tp_wait
+        _rc(lib().tahb_lora_a_rows_tp(_p(x), _p(A), _p(out), _p(gate), c_int(M), c_int(K), c_int(R),
+                                      c_ll(x.stride(0)), c_ll(out.stride(0)), _p(flags), _p(targets),
+                                      c_int(flags.numel()), _p(status_word(x.device)), _stream()), "tahb_lora_a_rows_tp")
     return out
 
 
@@ -373,6 +403,21 @@ def fused_reduce_residual_norm(partial_ptrs, xout_ptrs, mc_partial: int, mc_xout
                                               _p(status_word(h.device)), c_int(M), c_int(H), c_int(rank),
                                               c_int(world), c_float(eps), c_int(1 if add_residual else 0),
                                               c_int(grid), _stream()), "tahb_fused_reduce_residual_norm")
+
+
+def push_reduce_norm_bcast(slot, cnt, cnt_target, xout_ptrs, mc_xout: int, xflag_ptrs, xtarget, arrive, h, ln_w,
+                           M: int, H: int, rank: int, world: int, rpr: int, eps: float, add_residual: bool,
+                           final_wait: bool, grid: int):
+    """Owner side of the push-based row-parallel epilogue: sum the slots that the peers' GEMMs
+    filled, residual add, RMSNorm, broadcast, flag (see ``push_reduce_norm_bcast_kernel``)."""
+    n = len(xout_ptrs)
+    arr = lambda ptrs: (c_void_p * n)(*ptrs)
+    _rc(lib().tahb_push_reduce_norm_bcast(_p(slot), _p(cnt), _p(cnt_target), arr(xout_ptrs), c_void_p(mc_xout),
+                                          arr(xflag_ptrs), _p(xtarget), _p(arrive), _p(h), _p(ln_w),
+                                          _p(status_word(h.device)), c_int(M), c_int(H), c_int(rank), c_int(world),
+                                          c_int(rpr), c_float(eps), c_int(1 if add_residual else 0),
+                                          c_int(1 if final_wait else 0), c_int(grid), _stream()),
+        "tahb_push_reduce_norm_bcast")
 
 
 class TickStateBinding:

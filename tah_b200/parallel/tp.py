@@ -80,6 +80,21 @@ class TensorParallel:
         self.partial = self._partial_flat.view(max_tokens, hidden_size)
         self.xout = self._xout_flat.view(max_tokens, hidden_size)
         self.epoch = torch.zeros(MAX_GRID, dtype=torch.int32, device=self.device)
+        # push path (decode ticks): slots [world][rows_per_rank][H] filled by the peers' GEMM epilogues,
+        # an arrival counter (word 0) and per-owner landing flags (words 8..8+world) in symmetric memory,
+        # and local targets: word 0 = counter target, word 1 = CTA arrivals, words 8.. = flag targets
+        self._slot_flat = mk(max_tokens * hidden_size, torch.bfloat16)
+        self._pushflags = mk(16, torch.int32)
+        self._pushflags.zero_()
+        hs = symm_mem.rendezvous(self._slot_flat, self.group)
+        hq = symm_mem.rendezvous(self._pushflags, self.group)
+        self._handles = self._handles + (hs, hq)
+        self.slot_ptrs = [int(p) for p in hs.buffer_ptrs]
+        self.cnt_ptrs = [int(p) for p in hq.buffer_ptrs]
+        self.xflag_ptrs = [int(p) + 8 * 4 for p in hq.buffer_ptrs]
+        self._pstate = torch.zeros(16, dtype=torch.int32, device=self.device)
+        self.xflag_local = self._pushflags[8:8 + self.world_size]
+        self.xtarget = self._pstate[8:8 + self.world_size]
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
@@ -99,6 +114,31 @@ class TensorParallel:
         K.fused_reduce_residual_norm(self.partial_ptrs, self.xout_ptrs, self.mc_partial, self.mc_xout, h, ln_w,
                                      self.flag_ptrs, self.epoch, M, self.hidden, self.rank, self.world_size, eps,
                                      add_residual, grid)
+        return self.xout[:M]
+
+    # ---- push path: GEMM epilogue = reduce-scatter, owner kernel = sum + norm + broadcast ------------
+    def push_desc(self, M: int):
+        """Arguments that turn a row-parallel GEMM's epilogue into peer stores into the owners'
+        slots, or None when ``M`` rows cannot be dealt out in 16-row blocks."""
+        if self.hidden % 128 or M % (16 * self.world_size) or M > self.max_tokens:
+            return None
+        return (self.slot_ptrs, self.cnt_ptrs, self.rank, M // self.world_size)
+
+    @property
+    def wait_desc(self):
+        """(flags, targets) that consumers of ``xout`` pass as ``tp_wait`` after :meth:`push_reduce_norm`."""
+        return (self.xflag_local, self.xtarget)
+
+    def push_reduce_norm(self, M: int, h: torch.Tensor, ln_w: torch.Tensor, eps: float, add_residual: bool = True,
+                         final_wait: bool = False) -> torch.Tensor:
+        """Owner side after a ``tp_push`` GEMM on every rank.  The returned ``xout[:M]`` is complete
+        on this rank only once the flags in :attr:`wait_desc` have reached their targets: consumers
+        either wait themselves (``tp_wait``) or ask for ``final_wait``."""
+        rpr = M // self.world_size
+        grid = max(1, min(MAX_GRID, rpr))
+        K.push_reduce_norm_bcast(self._slot_flat, self._pushflags[0:1], self._pstate[0:1], self.xout_ptrs,
+                                 self.mc_xout, self.xflag_ptrs, self.xtarget, self._pstate[1:2], h, ln_w, M,
+                                 self.hidden, self.rank, self.world_size, rpr, eps, add_residual, final_wait, grid)
         return self.xout[:M]
 
     # ---- cold paths: NCCL -----------------------------------------------------------------------

@@ -58,6 +58,47 @@ def main():
                 print(f"fused_reduce_norm multicast={use_mc} iter={it}: max err h {e1:.4f} xn {e2:.4f} {'ok' if good else 'BAD'}")
         dist.barrier()
 
+    # ---- push path: GEMM epilogue = reduce-scatter by peer stores, owner kernel, flag-waiting consumer ----
+    for use_mc in (False, True):
+        tp = TensorParallel(dist.group.WORLD, dev, use_multicast=use_mc)
+        H, M, Kr = 512, 32 * world, 256
+        tp.allocate(H, M)
+        if use_mc and tp.mc_xout == 0:
+            continue
+        gw = torch.Generator(device=dev).manual_seed(11)
+        w2 = (torch.randn(384, H, generator=gw, device=dev) * H ** -0.5).to(torch.bfloat16)
+        ln = (torch.randn(H, generator=gw, device=dev) * 0.1 + 1).to(torch.bfloat16)
+        for it in range(4):
+            g = torch.Generator(device=dev).manual_seed(1000 * it + rank)
+            x = torch.randn(M, Kr, generator=g, device=dev).to(torch.bfloat16)
+            w = (torch.randn(H, Kr, generator=g, device=dev) * Kr ** -0.5).to(torch.bfloat16)
+            gh = torch.Generator(device=dev).manual_seed(77 + it)
+            h_full = torch.randn(M, H, generator=gh, device=dev).to(torch.bfloat16)
+            h = h_full.clone()
+            desc = tp.push_desc(M)
+            assert desc is not None
+            K.gemm(x, w, tp_push=desc, splits=(1 if it % 2 == 0 else None))
+            last = it == 3
+            xn = tp.push_reduce_norm(M, h, ln, 1e-6, add_residual=True, final_wait=last)
+            y2 = K.gemm(xn, w2, tp_wait=None if last else tp.wait_desc)      # consumer waits for the broadcast rows
+            xn_seen = xn.clone() if last else None
+            torch.cuda.synchronize()
+            K.check_status(dev)
+            part = (x.float() @ w.float().t()).to(torch.bfloat16).float()
+            dist.all_reduce(part)
+            h_ref = (h_full.float() + part.to(torch.bfloat16).float()).to(torch.bfloat16)
+            xn_ref = torch_ref.rms_norm(h_ref, ln, 1e-6)
+            y2_ref = (xn_ref.float() @ w2.float().t())
+            lo, hi = tp.rows_of(M)
+            e1 = (h[lo:hi].float() - h_ref[lo:hi].float()).abs().max().item()
+            e2 = (y2.float() - y2_ref).abs().max().item()
+            e3 = (xn_seen.float() - xn_ref.float()).abs().max().item() if last else 0.0
+            good = e1 < 0.07 and e2 < 0.15 and e3 < 0.07
+            ok = ok and good
+            if rank == 0:
+                print(f"push path multicast={use_mc} iter={it}: max err h {e1:.4f} consumer {e2:.4f} xn {e3:.4f} {'ok' if good else 'BAD'}")
+            dist.barrier()
+
     # ---- ZeRO optimizer: fused reduce-scatter + AdamW + parameter broadcast over peer memory -----
     from tah_b200.parallel.zero import ZeroAdamW
     for use_mc in (False, True):
@@ -94,7 +135,7 @@ def main():
     # ---- engine parity: TP vs single GPU -------------------------------------------------------
     from tests.helpers import tiny_tah
     from tah_b200.engine import TaHEngine
-    B, T, n_new = 4, 20, 16
+    B, T, n_new = 16 * world, 20, 16      # a multiple of 16 rows per rank: the push path runs
     model = tiny_tah(max_iter=2, dtype=torch.bfloat16).to(dev).eval()
     gen = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 1024, (B, T), generator=gen).to(dev)
