@@ -58,6 +58,8 @@ __device__ __forceinline__ void locate_page(int i, const int* seg_pages, int& c,
 
 template <int HD, int G>
 __global__ void __launch_bounds__(160, (HD * G <= 256) ? 4 : 2) decode_attn_kernel(const DecodeAttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   using C = AttCfg<HD>;
   constexpr int VEC = HD / 64;       // 16-byte chunks per lane per row: lane gl owns chunks gl, gl + 8, ...
   constexpr int DPL = VEC * 8;       // dims per lane
@@ -270,6 +272,8 @@ __global__ void __launch_bounds__(160, (HD * G <= 256) ? 4 : 2) decode_attn_kern
 
 template <int HD>
 __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int n_split) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int rh = blockIdx.x;   // row * nq + head
   const float* w = ws + (size_t)rh * n_split * (HD + 2);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
@@ -351,9 +355,10 @@ static int launch_decode(const DecodeAttnParams& p, cudaStream_t stream) {
       return -10;
     configured = true;
   }
-  decode_attn_kernel<HD, G><<<grid, 160, AttCfg<HD>::SMEM_BYTES, stream>>>(p);
-  if (p.n_split > 1) decode_attn_merge_kernel<HD><<<p.rows * p.nq, HD, 0, stream>>>(p.ws, p.out, p.n_split);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  cudaError_t e = launch_chain(decode_attn_kernel<HD, G>, grid, dim3(160), AttCfg<HD>::SMEM_BYTES, stream, p);
+  if (e == cudaSuccess && p.n_split > 1)
+    e = launch_chain(decode_attn_merge_kernel<HD>, dim3(p.rows * p.nq), dim3(HD), 0, stream, p.ws, p.out, p.n_split);
+  return e == cudaSuccess ? 0 : -3;
 }
 
 }  // namespace tahb

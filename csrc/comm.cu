@@ -113,6 +113,8 @@ __device__ __forceinline__ bool cross_rank_barrier(const FusedReduceParams& p, i
 
 template <int VPT>
 __global__ void __launch_bounds__(256) fused_reduce_residual_norm_kernel(const FusedReduceParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x;
   __shared__ uint32_t s_epoch;
   __shared__ float red[8];
@@ -237,6 +239,8 @@ struct PushReduceParams {
 
 template <int VPT>
 __global__ void __launch_bounds__(256) push_reduce_norm_bcast_kernel(const PushReduceParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[8];
   __shared__ int s_ok;
   const int b = blockIdx.x;
@@ -384,11 +388,12 @@ extern "C" int tahb_fused_reduce_residual_norm(void* const* partial, void* const
   p.add_residual = add_residual;
   const int nvec = H / 8;
   if (grid < 1) grid = 1;
-  if (nvec <= 256) fused_reduce_residual_norm_kernel<1><<<grid, 256, 0, stream>>>(p);
-  else if (nvec <= 512) fused_reduce_residual_norm_kernel<2><<<grid, 256, 0, stream>>>(p);
-  else if (nvec <= 1024) fused_reduce_residual_norm_kernel<4><<<grid, 256, 0, stream>>>(p);
+  cudaError_t e;
+  if (nvec <= 256) e = launch_chain(fused_reduce_residual_norm_kernel<1>, dim3(grid), dim3(256), 0, stream, p);
+  else if (nvec <= 512) e = launch_chain(fused_reduce_residual_norm_kernel<2>, dim3(grid), dim3(256), 0, stream, p);
+  else if (nvec <= 1024) e = launch_chain(fused_reduce_residual_norm_kernel<4>, dim3(grid), dim3(256), 0, stream, p);
   else return -2;
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return e == cudaSuccess ? 0 : -3;
 }
 
 
@@ -423,9 +428,10 @@ extern "C" int tahb_push_reduce_norm_bcast(const void* slot, void* cnt, void* cn
   p.final_wait = final_wait;
   const int nvec = H / 8;
   if (grid < 1) grid = 1;
-  if (nvec <= 256) push_reduce_norm_bcast_kernel<1><<<grid, 256, 0, stream>>>(p);
-  else if (nvec <= 512) push_reduce_norm_bcast_kernel<2><<<grid, 256, 0, stream>>>(p);
-  else if (nvec <= 1024) push_reduce_norm_bcast_kernel<4><<<grid, 256, 0, stream>>>(p);
+  cudaError_t e;
+  if (nvec <= 256) e = launch_chain(push_reduce_norm_bcast_kernel<1>, dim3(grid), dim3(256), 0, stream, p);
+  else if (nvec <= 512) e = launch_chain(push_reduce_norm_bcast_kernel<2>, dim3(grid), dim3(256), 0, stream, p);
+  else if (nvec <= 1024) e = launch_chain(push_reduce_norm_bcast_kernel<4>, dim3(grid), dim3(256), 0, stream, p);
   else return -2;
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return e == cudaSuccess ? 0 : -3;
 }

@@ -25,6 +25,39 @@ enum Status : int {
   STATUS_BAD_INDEX = 5,
 };
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  The kernels of the per-layer decode chain are launched with the
+// programmatic-stream-serialization attribute: a kernel tells the scheduler at its very start that
+// its successor may be launched (pdl_launch_dependents), does the set-up that touches no global
+// memory, and then waits until its predecessor has completed and flushed (pdl_wait) before its
+// first global access.  Launch latency, CTA scheduling and set-up of kernel N+1 thus overlap the
+// tail of kernel N.  Every such kernel executes pdl_wait on every path, so completion of a kernel
+// implies completion of all kernels before it.  Both instructions are no-ops in a kernel launched
+// without the attribute.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// 1 unless the environment variable TAH_B200_PDL is "0" (defined in elementwise.cu)
+int pdl_enabled();
+
+// Launch `kern` with (or without) the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -5,6 +5,8 @@
 // Rounding follows what a bf16 PyTorch module stack produces (norm output rounded before the
 // weight multiply, RoPE products rounded before the add), so that greedy token streams agree
 // with an eager bf16 run of the same model.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace tahb {
@@ -18,6 +20,8 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const __nv_bfloat16* __res
                                                       const __nv_bfloat16* __restrict__ w,
                                                       __nv_bfloat16* __restrict__ y, int H, long long ldx,
                                                       long long ldy, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int nvec = H / 8;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
@@ -91,6 +95,8 @@ struct QkvRopeParams {
 
 template <int HD>
 __global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(const QkvRopeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int EPL = HD / 32;  // elements per lane
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -181,7 +187,7 @@ __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ E, const i
 // Rows whose gate is 0 only clear their output.  Meant for decode ticks where a handful of rows
 // are at depth >= 1; dense passes use the tensor-core GEMM instead.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256) lora_a_rows_dense_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ A,
                                                           __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
                                                           int K, int R, long long ldx, long long ldt,
@@ -189,6 +195,8 @@ __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* _
                                                           int wait_world, int* status) {
   // grid (rows, ceil(R / 8)): a CTA owns 8 outputs of one row, one per warp, so that a gated row's
   // product is spread over R / 8 CTAs instead of running serially in one
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.y * 8 + warp;
@@ -217,6 +225,88 @@ __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* _
   }
   acc = warp_sum(acc);
   if (lane == 0) out[j] = __float2bfloat16_rn(acc);
+}
+
+// Decode-tick form (gate given, M <= 1024): only a handful of rows are gated on, so the grid is
+// (LORA_SLOTS, ceil(R / 8)) instead of one CTA per (row, 8 outputs).  Every CTA compacts the gate
+// vector into a list of gated rows in shared memory; CTA x handles list entries x, x + LORA_SLOTS,
+// ... for its 8 outputs (one per warp); the x == 0 CTAs also clear their 8 columns of the rows that
+// are gated off.
+constexpr int LORA_SLOTS = 32;
+__global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ A,
+                                                          __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
+                                                          int M, int K, int R, long long ldx, long long ldt,
+                                                          const uint32_t* wait_flag, const uint32_t* wait_target,
+                                                          int wait_world, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int s_rows[1024];
+  __shared__ int s_warp[8];
+  __shared__ int s_n;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int jb = blockIdx.y;
+  // compact the gated rows: thread t looks at rows 4t .. 4t+3
+  int g[4], cnt = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = tid * 4 + i;
+    g[i] = (r < M && gate[r] != 0) ? 1 : 0;
+    cnt += g[i];
+  }
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int base = 0;
+  for (int w = 0; w < warp; ++w) base += s_warp[w];
+  int pos = base + incl - cnt;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (g[i]) s_rows[pos++] = tid * 4 + i;
+  if (tid == 255) s_n = base + incl;
+  __syncthreads();
+  const int n = s_n;
+  if (blockIdx.x == 0) {      // clear this CTA's 8 columns of the rows that are gated off
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = tid * 4 + i;
+      if (r < M && !g[i]) {
+        __nv_bfloat16* o = T + (size_t)r * ldt + jb * 8;
+        if (jb * 8 + 8 <= R && (ldt % 8) == 0) *reinterpret_cast<uint4*>(o) = make_uint4(0, 0, 0, 0);
+        else for (int c = 0; c < 8 && jb * 8 + c < R; ++c) o[c] = __float2bfloat16_rn(0.f);
+      }
+    }
+  }
+  if ((int)blockIdx.x >= n) return;
+  if (wait_world > 0) {       // tensor parallel: x rows are broadcast by their owners (see comm.cu)
+    if (tid == 0) wait_peer_rows(wait_flag, wait_target, wait_world, status);
+    __syncthreads();
+  }
+  const int j = jb * 8 + warp;
+  if (j >= R) return;
+  const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)j * K);
+  for (int k = blockIdx.x; k < n; k += gridDim.x) {
+    const int r = s_rows[k];
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
+    float acc = 0.f;
+    for (int i = lane; i < K / 8; i += 32) {
+      uint4 xv = xr[i], av = ar[i];
+      const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 a = __bfloat1622float2(xh[q]), b = __bfloat1622float2(ah[q]);
+        acc += a.x * b.x + a.y * b.y;
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) T[(size_t)r * ldt + j] = __float2bfloat16_rn(acc);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -301,6 +391,15 @@ __global__ void __launch_bounds__(1024) logits_post_kernel(const __nv_bfloat16* 
   }
 }
 
+int pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("TAH_B200_PDL");
+    on = (v != nullptr && v[0] == '0') ? 0 : 1;
+  }
+  return on;
+}
+
 }  // namespace tahb
 
 using namespace tahb;
@@ -313,12 +412,13 @@ extern "C" int tahb_rmsnorm(const void* x, const void* w, void* y, int M, int H,
   auto X = reinterpret_cast<const __nv_bfloat16*>(x);
   auto W = reinterpret_cast<const __nv_bfloat16*>(w);
   auto Y = reinterpret_cast<__nv_bfloat16*>(y);
-  if (nvec <= 128) rmsnorm_kernel<1><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
-  else if (nvec <= 256) rmsnorm_kernel<2><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
-  else if (nvec <= 512) rmsnorm_kernel<4><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
-  else if (nvec <= 1024) rmsnorm_kernel<8><<<M, 128, 0, stream>>>(X, W, Y, H, ldx, ldy, eps);
+  cudaError_t e;
+  if (nvec <= 128) e = launch_chain(rmsnorm_kernel<1>, dim3(M), dim3(128), 0, stream, X, W, Y, H, ldx, ldy, eps);
+  else if (nvec <= 256) e = launch_chain(rmsnorm_kernel<2>, dim3(M), dim3(128), 0, stream, X, W, Y, H, ldx, ldy, eps);
+  else if (nvec <= 512) e = launch_chain(rmsnorm_kernel<4>, dim3(M), dim3(128), 0, stream, X, W, Y, H, ldx, ldy, eps);
+  else if (nvec <= 1024) e = launch_chain(rmsnorm_kernel<8>, dim3(M), dim3(128), 0, stream, X, W, Y, H, ldx, ldy, eps);
   else return -2;
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return e == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int tahb_qk_norm_rope_kv(const void* qkv, const void* q_w, const void* k_w, void* q_out, void* k_dense,
@@ -344,10 +444,11 @@ extern "C" int tahb_qk_norm_rope_kv(const void* qkv, const void* q_w, const void
   p.log2_theta = log2f(theta);
   const long long warps = (long long)M * (nq + 2 * nkv);
   const int blocks = (int)((warps + 3) / 4);
-  if (hd == 128) qk_norm_rope_kv_kernel<128><<<blocks, 128, 0, stream>>>(p);
-  else if (hd == 64) qk_norm_rope_kv_kernel<64><<<blocks, 128, 0, stream>>>(p);
+  cudaError_t e = cudaSuccess;
+  if (hd == 128) e = launch_chain(qk_norm_rope_kv_kernel<128>, dim3(blocks), dim3(128), 0, stream, p);
+  else if (hd == 64) e = launch_chain(qk_norm_rope_kv_kernel<64>, dim3(blocks), dim3(128), 0, stream, p);
   else return -2;
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return e == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int tahb_embed_gather(const void* E, const int* tok, void* out, int M, int H, long long ld_out,
@@ -363,11 +464,20 @@ static int lora_a_rows_launch(const void* x, const void* A, void* T, const int* 
                               int wait_world, int* status, cudaStream_t stream) {
   if (M <= 0 || R <= 0) return 0;
   if (K % 8) return -1;
-  lora_a_rows_kernel<<<dim3(M, (R + 7) / 8), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(A),
-      reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt, reinterpret_cast<const uint32_t*>(wait_flag),
-      reinterpret_cast<const uint32_t*>(wait_target), wait_flag ? wait_world : 0, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  cudaError_t e;
+  if (gate != nullptr && M <= 1024)
+    e = launch_chain(lora_a_rows_kernel, dim3(M < LORA_SLOTS ? M : LORA_SLOTS, (R + 7) / 8), dim3(256), 0, stream,
+                     reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(A),
+                     reinterpret_cast<__nv_bfloat16*>(T), gate, M, K, R, ldx, ldt,
+                     reinterpret_cast<const uint32_t*>(wait_flag), reinterpret_cast<const uint32_t*>(wait_target),
+                     wait_flag ? wait_world : 0, status);
+  else
+    e = launch_chain(lora_a_rows_dense_kernel, dim3(M, (R + 7) / 8), dim3(256), 0, stream,
+                     reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(A),
+                     reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt,
+                     reinterpret_cast<const uint32_t*>(wait_flag), reinterpret_cast<const uint32_t*>(wait_target),
+                     wait_flag ? wait_world : 0, status);
+  return e == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int tahb_lora_a_rows(const void* x, const void* A, void* T, const int* gate, int M, int K, int R,

@@ -149,6 +149,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
                const GemmParams p) {
   using C = GemmCfg<BN, DUAL>;
+  pdl_launch_dependents();      // the next kernel of the chain may be scheduled behind this one
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::NS * C::STAGE_BYTES);
@@ -188,6 +189,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();                   // set-up above touched no global memory; operands may be read from here on
   const uint32_t tmem_base = *tmem_slot;
   const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
   if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 0] = globaltimer_ns();
@@ -465,13 +467,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = p.splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, mw2, mx2, mo, mr, p);
   return e == cudaSuccess ? 0 : -12;
 }

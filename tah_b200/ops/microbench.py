@@ -77,11 +77,12 @@ def bench_gemm(a):
     w2 = _rand(wrows, R, scale=0.05) if R else None
     x2 = _rand(M, R) if R else None
     out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
-    fn = lambda i: K.gemm(xs[i % n], ws[i % n], out=out, x2=x2, w2=w2, swiglu=a.swiglu)
+    plan = dict(bn=a.bn, splits=a.splits) if a.bn else {}
+    fn = lambda i: K.gemm(xs[i % n], ws[i % n], out=out, x2=x2, w2=w2, swiglu=a.swiglu, **plan)
     t = _time(fn, a.iters, a.warmup)
     flops = 2.0 * M * wrows * (Kd + R)
     byts = (wrows * (Kd + R) + M * (Kd + R) + M * F) * 2
-    res = {"op": "gemm", "M": M, "F": F, "K": Kd, "R": R, "swiglu": a.swiglu, "plan_bn_splits": K.plan_gemm(M, F, Kd, R, a.swiglu)}
+    res = {"op": "gemm", "M": M, "F": F, "K": Kd, "R": R, "swiglu": a.swiglu, "plan_bn_splits": [a.bn, a.splits] if a.bn else K.plan_gemm(M, F, Kd, R, a.swiglu)}
     if a.cublas:
         ref = lambda i: torch.matmul(xs[i % n], ws[i % n].t())
         res["cublas_us"] = round(_time(ref, a.iters, a.warmup) * 1e6, 2)
@@ -164,6 +165,8 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--r", type=int, default=0, help="LoRA K-extension width")
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--bn", type=int, default=0, help="force the token-tile width (with --splits) instead of the planner")
+    ap.add_argument("--splits", type=int, default=1, help="split-K cluster size used with --bn")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on the same operands")
     ap.add_argument("--rows", type=int, default=256, help="decode rows / prefill sequences / top-k rows")
     ap.add_argument("--ctx", type=int, default=1024, help="context (decode) or sequence length (prefill)")

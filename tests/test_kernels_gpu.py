@@ -306,6 +306,16 @@ def test_lora_a_rows_and_swiglu():
     t = Kc.lora_a_rows(x, A, gate)
     ref = (x.float() @ A.float().t()) * gate[:, None]
     _close(t, ref, atol=2e-2, rtol=2e-2)
+    # more gated rows than compaction slots, a row count that is not a multiple of 4, dirty output
+    x2 = _rand(203, 1024, seed=4)
+    A2 = _rand(72, 1024, scale=1024 ** -0.5, seed=5)
+    gate2 = (torch.rand(203, device="cuda") < 0.4).to(torch.int32)
+    out2 = torch.full((203, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    Kc.lora_a_rows(x2, A2, gate2, out=out2[:, :72])
+    _close(out2[:, :72], (x2.float() @ A2.float().t()) * gate2[:, None], atol=2e-2, rtol=2e-2)
+    assert (out2[:, 72:] == 7.0).all()
+    # no gate: every row (dense kernel)
+    _close(Kc.lora_a_rows(x2, A2), x2.float() @ A2.float().t(), atol=2e-2, rtol=2e-2)
     gu = _rand(11, 2 * 768, seed=3)
     from tah_b200.ops import torch_ref
     _close(Kc.swiglu(gu), torch_ref.swiglu(gu), atol=1e-2, rtol=1e-2)

@@ -136,7 +136,11 @@ def main():
     from tests.helpers import tiny_tah
     from tah_b200.engine import TaHEngine
     B, T, n_new = 16 * world, 20, 16      # a multiple of 16 rows per rank: the push path runs
-    model = tiny_tah(max_iter=2, dtype=torch.bfloat16).to(dev).eval()
+    # the tiny preset has 4 query / 2 KV heads; wider groups get a tiny model whose heads, KV heads and
+    # MLP channels divide by the group size
+    over = {} if world <= 2 else dict(num_attention_heads=world, num_key_value_heads=world, head_dim=64,
+                                      intermediate_size=128 * world)
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16, **over).to(dev).eval()
     gen = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 1024, (B, T), generator=gen).to(dev)
     tp = TensorParallel(dist.group.WORLD, dev, use_multicast=os.environ.get("TAH_B200_NVLS", "1") != "0")
