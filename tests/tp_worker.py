@@ -52,7 +52,10 @@ def main():
             lo, hi = tp.rows_of(M)
             e1 = (h[lo:hi].float() - h_ref[lo:hi].float()).abs().max().item()
             e2 = (xn.float() - xn_ref.float()).abs().max().item()
-            good = e1 < 0.07 and e2 < 0.07
+            # the sum of `world` N(0,1) partials reaches ~4 sqrt(world): allow two bf16 ulps at that size
+            # (the in-switch reduction does not promise the reference's summation order)
+            tol = 0.07 if world <= 2 else 0.26
+            good = e1 < tol and e2 < tol
             ok = ok and good
             if rank == 0:
                 print(f"fused_reduce_norm multicast={use_mc} iter={it}: max err h {e1:.4f} xn {e2:.4f} {'ok' if good else 'BAD'}")
