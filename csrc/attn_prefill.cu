@@ -21,11 +21,9 @@
 // warps 2..5 take key columns 0..31 and the lower half of head_dim, warps 6..9 the rest).
 #include <cuda.h>
 
-#include "common.cuh"
+#include "attn_common.cuh"
 
 namespace tahb {
-
-constexpr int PF_MAX_SEG = 3;
 
 struct PrefillParams {
   __nv_bfloat16* out;            // [n_q, nq * HD]
@@ -35,6 +33,7 @@ struct PrefillParams {
   const int* seg_count[PF_MAX_SEG];  // [n_q] number of visible KV rows (non-decreasing inside a tile)
   int n_seg, nq, nkv;
   float scale_log2;
+  float* lse;                    // optional [n_q, nq]: log2-domain log-sum-exp of the scaled scores (for backward)
   int* status;
 };
 
@@ -51,22 +50,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// MN-major bf16 operand (the N/M dimension is contiguous): rows of 64 elements (128 B) per K index,
-// 128-byte swizzle, 8 K-rows per 1024-byte group (SBO), next 64 MN elements `lbo_bytes` further.
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= static_cast<uint64_t>(64) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-// bf16 x bf16 -> fp32, A K-major, B MN-major
-__host__ __device__ constexpr uint32_t umma_idesc_bf16_bmn(int m, int n) {
-  return umma_idesc_bf16(m, n) | (1u << 16);
-}
 
 template <int HD>
 struct PfCfg {
@@ -303,6 +286,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     named_bar_sync(1, 256);
     l += xl[(half ^ 1) * 128 + row];
     const float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (p.lse != nullptr && half == 0 && row_ok)
+      p.lse[(size_t)(q0 + row) * p.nq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
     __nv_bfloat16* dst = p.out + ((size_t)(q0 + row) * p.nq + head) * HD + half * (HD / 2);
 #pragma unroll 1
     for (int c = 0; c < HD / 2; c += 32) {
@@ -334,31 +319,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
 }
 
-typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static int pf_make_map(CUtensorMap* m, const void* base, long long rows, long long cols, unsigned box_rows) {
-  static PfEncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return -1;
-    fn = reinterpret_cast<PfEncodeFn>(ptr);
-  }
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((cols * 2) & 15)) return -2;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {64u, box_rows};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
-}
-
 }  // namespace tahb
 
 using namespace tahb;
@@ -368,7 +328,7 @@ using namespace tahb;
 extern "C" int tahb_prefill_attn(const void* q, void* out, void* const* ks, void* const* vs, const long long* n_kv,
                                  const int* const* bases, const int* const* counts, int n_seg, const int* tile_q0,
                                  const int* tile_qn, int n_tiles, long long n_q, int nq, int nkv, int hd, float scale,
-                                 int* status, cudaStream_t stream) {
+                                 float* lse, int* status, cudaStream_t stream) {
   if (n_tiles <= 0 || n_q <= 0) return 0;
   if (n_seg < 1 || n_seg > PF_MAX_SEG || (nq % nkv)) return -1;
   CUtensorMap mq, mk[PF_MAX_SEG], mv[PF_MAX_SEG];
@@ -390,6 +350,7 @@ extern "C" int tahb_prefill_attn(const void* q, void* out, void* const* ks, void
   }
   p.n_seg = n_seg; p.nq = nq; p.nkv = nkv;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse;
   p.status = status;
   dim3 grid(n_tiles, nq);
 #define TAHB_PF(HD_)                                                                                              \

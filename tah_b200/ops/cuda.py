@@ -330,10 +330,11 @@ def attn_tiles(seq_counts: torch.Tensor, tile: int = 128):
     return q0.to(torch.int32).contiguous(), qn.to(torch.int32).contiguous()
 
 
-def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, out=None):
+def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, out=None, lse=None):
     """Packed duo-causal attention on the tensor cores (``csrc/attn_prefill.cu``).  Same contract as
     :func:`varlen_attn_naive` plus the query tiling of :func:`attn_tiles`: the tokens of a tile belong
-    to one sequence, share ``bases[s]`` and have non-decreasing ``counts[s]``."""
+    to one sequence, share ``bases[s]`` and have non-decreasing ``counts[s]``.  ``lse`` (optional fp32
+    ``[n_q, nq]``) receives the base-2 log-sum-exp of the scaled scores, which the backward kernels take."""
     if out is None:
         out = torch.empty_like(q)
     n = len(ks)
@@ -343,9 +344,59 @@ def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale,
     n_kv = (c_ll * n)(*[k.shape[0] for k in ks])
     _rc(lib().tahb_prefill_attn(_p(q), _p(out), _ptr_array(ks), _ptr_array(vs), n_kv, _ptr_array(bases),
                                 _ptr_array(counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
-                                c_ll(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale),
+                                c_ll(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse),
                                 _p(status_word(q.device)), _stream()), "tahb_prefill_attn")
     return out
+
+
+def attn_kv_items(seq_kv_counts: torch.Tensor, seq_kv_base: torch.Tensor, seq_q_counts: torch.Tensor, block: int = 128):
+    """Work items of :func:`attn_bwd_dkv` for one KV segment: every sequence's ``seq_kv_counts[b]`` keys
+    (stored from row ``seq_kv_base[b]`` of the segment's K/V matrices) are cut into blocks of ``block``.
+    Returns int32 ``(row0, nkeys, kidx0, qa, qb)``; ``qa:qb`` are the sequence's packed query rows
+    (sequences laid out back to back, ``seq_q_counts[b]`` rows each)."""
+    cnt = seq_kv_counts.to(torch.int64)
+    per = (cnt + block - 1) // block
+    n = int(per.sum())
+    dev = cnt.device
+    seq_of = torch.repeat_interleave(torch.arange(cnt.numel(), device=dev), per, output_size=n)
+    rank = torch.arange(n, device=dev) - (torch.cumsum(per, 0) - per)[seq_of]
+    kidx0 = block * rank
+    row0 = seq_kv_base.to(torch.int64)[seq_of] + kidx0
+    nkeys = torch.clamp(cnt[seq_of] - kidx0, max=block)
+    qc = seq_q_counts.to(torch.int64)
+    qstart = torch.cumsum(qc, 0) - qc
+    qa = qstart[seq_of]
+    qb = qa + qc[seq_of]
+    i32 = lambda t: t.to(torch.int32).contiguous()
+    return i32(row0), i32(nkeys), i32(kidx0), i32(qa), i32(qb)
+
+
+def attn_bwd_dq(q, dout, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, lse, dsum, out=None):
+    """dQ of :func:`prefill_attn` (``csrc/attn_prefill_bwd.cu``); ``dsum = rowsum(dO * O)`` per (query, head)."""
+    if out is None:
+        out = torch.empty_like(q)
+    n = len(ks)
+    n_kv = (c_ll * n)(*[k.shape[0] for k in ks])
+    _rc(lib().tahb_attn_bwd_dq(_p(q), _p(dout), _p(out), _ptr_array(ks), _ptr_array(vs), n_kv, _ptr_array(bases),
+                               _ptr_array(counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
+                               c_ll(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse), _p(dsum),
+                               _p(status_word(q.device)), _stream()), "tahb_attn_bwd_dq")
+    return out
+
+
+def attn_bwd_dkv(q, dout, k, v, count, items, nq, nkv, hd, scale, lse, dsum, dk=None, dv=None):
+    """dK, dV of one KV segment of :func:`prefill_attn`; ``items`` from :func:`attn_kv_items`, ``count`` the
+    segment's visible-key counts per packed query.  Keys outside every item keep a zero gradient."""
+    if dk is None:
+        dk = torch.zeros_like(k)
+    if dv is None:
+        dv = torch.zeros_like(v)
+    row0, nkeys, kidx0, qa, qb = items
+    _rc(lib().tahb_attn_bwd_dkv(_p(q), _p(dout), _p(k), _p(v), _p(dk), _p(dv), c_ll(k.shape[0]), _p(count), _p(row0),
+                                _p(nkeys), _p(kidx0), _p(qa), _p(qb), c_int(row0.numel()), c_ll(q.shape[0]),
+                                c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse), _p(dsum),
+                                _p(status_word(q.device)), _stream()), "tahb_attn_bwd_dkv")
+    return dk, dv
 
 
 # -------------------------------------------------------------------------------------------

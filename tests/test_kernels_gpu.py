@@ -244,6 +244,76 @@ def test_prefill_attention_tcgen05_duo_segments(hd):
     _close(out, naive.float(), atol=2e-2, rtol=2e-2)
 
 
+def _ref_attention_autograd(q, ks, vs, bases, counts, nq, nkv, hd, dout):
+    """fp32 masked-softmax attention with autograd: returns out, dq, [dk], [dv]."""
+    G = nq // nkv
+    qf = q.float().view(-1, nq, hd).requires_grad_(True)
+    kf = [k.float().view(-1, nkv, hd).requires_grad_(True) for k in ks]
+    vf = [v.float().view(-1, nkv, hd).requires_grad_(True) for v in vs]
+    n = qf.shape[0]
+    kk = torch.cat(kf).repeat_interleave(G, 1)
+    vv = torch.cat(vf).repeat_interleave(G, 1)
+    offs = [0]
+    for k in kf:
+        offs.append(offs[-1] + k.shape[0])
+    mask = torch.zeros(n, kk.shape[0], dtype=torch.bool, device=q.device)
+    for s, (b, c) in enumerate(zip(bases, counts)):
+        idx = torch.arange(kf[s].shape[0], device=q.device)[None]
+        b_t = torch.tensor(b, device=q.device)[:, None]
+        c_t = torch.tensor(c, device=q.device)[:, None]
+        mask[:, offs[s]:offs[s + 1]] = (idx >= b_t) & (idx < b_t + c_t)
+    sc = torch.einsum("qhd,khd->hqk", qf, kk) * hd ** -0.5
+    sc = sc.masked_fill(~mask[None], float("-inf"))
+    out = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), vv)
+    out.backward(dout.float().view(n, nq, hd))
+    return out.detach(), qf.grad, [k.grad for k in kf], [v.grad for v in vf]
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_prefill_attention_backward_tcgen05(hd):
+    """dQ / dK / dV kernels (two segments, several key blocks and query tiles, GQA) against fp32 autograd."""
+    Kc = _cuda()
+    nq, nkv = 4, 2
+    seqlens = [300, 70, 5]
+    starts = [0, 300, 370]
+    n0 = sum(seqlens)
+    g = torch.Generator().manual_seed(7)
+    hard = [sorted(torch.randperm(L, generator=g)[: max(1, (L * 3) // 5)].tolist()) for L in seqlens]
+    n1s = [len(h) for h in hard]
+    n1 = sum(n1s)
+    k0, v0 = _rand(n0, nkv * hd, seed=1), _rand(n0, nkv * hd, seed=2)
+    k1, v1 = _rand(n1, nkv * hd, seed=3), _rand(n1, nkv * hd, seed=4)
+    b0, c0, b1, c1 = [], [], [], []
+    off1 = 0
+    for s, hs in enumerate(hard):
+        for j, p in enumerate(hs):
+            b0.append(starts[s]); c0.append(p + 1); b1.append(off1); c1.append(j + 1)
+        off1 += len(hs)
+    q = _rand(n1, nq * hd, seed=5)
+    dout = _rand(n1, nq * hd, seed=6)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    qcnt = torch.tensor(n1s, device="cuda")
+    tq0, tqn = Kc.attn_tiles(qcnt)
+    bases, counts = [i32(b0), i32(b1)], [i32(c0), i32(c1)]
+    lse = torch.empty(n1, nq, dtype=torch.float32, device="cuda")
+    out = Kc.prefill_attn(q, [k0, k1], [v0, v1], bases, counts, tq0, tqn, nq, nkv, hd, hd ** -0.5, lse=lse)
+    ref_out, ref_dq, ref_dk, ref_dv = _ref_attention_autograd(q, [k0, k1], [v0, v1], [b0, b1], [c0, c1], nq, nkv, hd, dout)
+    _close(out.view(n1, nq, hd), ref_out, atol=2e-2, rtol=2e-2)
+    dsum = (dout.float() * out.float()).view(n1, nq, hd).sum(-1).contiguous()
+    dq = Kc.attn_bwd_dq(q, dout, [k0, k1], [v0, v1], bases, counts, tq0, tqn, nq, nkv, hd, hd ** -0.5, lse, dsum)
+    Kc.check_status()
+    _close(dq.view(n1, nq, hd), ref_dq, atol=3e-2, rtol=3e-2)
+    # segment 0: every sequence's depth-0 keys; segment 1: its depth-1 keys
+    items0 = Kc.attn_kv_items(torch.tensor(seqlens, device="cuda"), torch.tensor(starts, device="cuda"), qcnt)
+    start1 = [sum(n1s[:i]) for i in range(len(n1s))]
+    items1 = Kc.attn_kv_items(qcnt, torch.tensor(start1, device="cuda"), qcnt)
+    dk0, dv0 = Kc.attn_bwd_dkv(q, dout, k0, v0, counts[0], items0, nq, nkv, hd, hd ** -0.5, lse, dsum)
+    dk1, dv1 = Kc.attn_bwd_dkv(q, dout, k1, v1, counts[1], items1, nq, nkv, hd, hd ** -0.5, lse, dsum)
+    Kc.check_status()
+    for got, ref in ((dk0, ref_dk[0]), (dv0, ref_dv[0]), (dk1, ref_dk[1]), (dv1, ref_dv[1])):
+        _close(got.view(-1, nkv, hd), ref, atol=4e-2, rtol=4e-2)
+
+
 @pytest.mark.parametrize("V,K", [(1024, 100), (151936, 100), (151936, 20), (5000, 1)])
 def test_topk_rows_sorted(V, K):
     Kc = _cuda()
