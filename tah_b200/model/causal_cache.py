@@ -38,6 +38,8 @@ class TaHCache(PassKV):
         self.valid_mask_to_cache: Optional[torch.Tensor] = None
         self.batch_size: Optional[int] = None
         self._store_pass: bool = True
+        self._seg_meta = None
+        self._appended = False         # a slot has been extended by a later forward (decode with this cache)
         self._device = torch.device("cpu")
         self._dtype = torch.bfloat16
 
@@ -47,10 +49,47 @@ class TaHCache(PassKV):
         self.position_ids_to_cache = position_ids
         self.valid_mask_to_cache = valid_mask
         self._store_pass = store
+        self._seg_meta = None          # index arrays of the tensor-core attention path, built once per pass
+
+    def _segments(self, layer_idx: int, k, v):
+        """Per-depth K/V, positions and validity visible to this pass (this pass's own last)."""
+        d = self.current_iter_depth
+        ks, vs, ps, ms = [], [], [], []
+        for i in range(d + 1):
+            if (layer_idx, i) in self._k and not (i == d and self._store_pass):
+                ks.append(self._k[(layer_idx, i)]); vs.append(self._v[(layer_idx, i)])
+                ps.append(self._pos[(layer_idx, i)]); ms.append(self._valid[(layer_idx, i)])
+        own_new = self._store_pass and (layer_idx, d) in self._k
+        if own_new or (not self._store_pass and ks and (layer_idx, d) in self._k):
+            return None                  # slot d already holds earlier tokens: not a from-scratch pass
+        ks.append(k); vs.append(v)
+        ps.append(self.position_ids_to_cache); ms.append(self.valid_mask_to_cache)
+        return ks, vs, ps, ms
+
+    def _attend_segments(self, layer_idx: int, q, k, v):
+        """Tensor-core path (CUDA, bf16, from-scratch forward: every slot holds one pass's tokens, whose
+        valid entries are contiguous and in position order).  Returns None when it does not apply."""
+        import os
+        from tah_b200.ops import autograd_ops
+        if not q.is_cuda or os.environ.get("TAH_B200_FORCE_TORCH", "0") == "1" or self._appended:
+            return None
+        seg = self._segments(layer_idx, k, v)
+        if seg is None or not autograd_ops.segment_attention_ok(q, len(seg[0])):
+            return None
+        ks, vs, ps, ms = seg
+        if self._seg_meta is None:
+            self._seg_meta = autograd_ops.SegmentMeta(self.position_ids_to_cache, ps, ms)
+        out = autograd_ops.segment_attention(q, ks, vs, self._seg_meta)
+        if self._store_pass:
+            self.update(k, v, layer_idx)
+        return out
 
     def attend(self, layer_idx: int, q, k, v):
         d = self.current_iter_depth
         pos_new, valid_new = self.position_ids_to_cache, self.valid_mask_to_cache
+        fast = self._attend_segments(layer_idx, q, k, v)
+        if fast is not None:
+            return fast
         if self._store_pass:
             ks, vs = self.update(k, v, layer_idx)
             kv_pos = self.get_position_id_upto_iter(layer_idx, d, init_batch_size=q.shape[0])
@@ -78,6 +117,7 @@ class TaHCache(PassKV):
         self._device, self._dtype = key_states.device, key_states.dtype
         slot = (layer_idx, self.current_iter_depth)
         if slot in self._k:
+            self._appended = True
             self._k[slot] = torch.cat([self._k[slot], key_states], dim=1)
             self._v[slot] = torch.cat([self._v[slot], value_states], dim=1)
             self._pos[slot] = torch.cat([self._pos[slot], self.position_ids_to_cache], dim=-1)

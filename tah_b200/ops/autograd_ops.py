@@ -95,3 +95,89 @@ def swiglu(gate_up):
 
 def duo_attention(q, k, v, q_pos, kv_pos, kv_valid, q_depth=None, kv_depth=None):
     return torch_ref.duo_attention(q, k, v, q_pos, kv_pos, kv_valid, q_depth, kv_depth)
+
+
+# ---------------------------------------------------------------------------------------------
+# Duo-causal attention over per-depth KV segments on the tensor-core kernels (forward + backward)
+# ---------------------------------------------------------------------------------------------
+class SegmentMeta:
+    """Index arrays that the packed attention kernels take, built once per backbone pass.
+
+    Queries are the ``[B, Tq]`` tokens of the pass (row ``b * Tq + i``); segment ``s`` is the
+    ``[B, Ts]`` K/V of iteration depth ``s``.  A query sees, in every segment, the valid entries of
+    its own sample whose position is ``<=`` its own: with the valid entries of a sample stored
+    contiguously in position order that is a prefix, described by ``base`` (row of the sample's
+    first valid entry) and ``count`` (prefix length).
+    """
+
+    def __init__(self, q_pos: torch.Tensor, seg_pos: Sequence[torch.Tensor], seg_valid: Sequence[torch.Tensor]):
+        B, Tq = q_pos.shape
+        dev = q_pos.device
+        self.B, self.Tq = B, Tq
+        self.tile_q0, self.tile_qn = K.attn_tiles(torch.full((B,), Tq, device=dev))
+        self.bases, self.counts, self.items, self.seg_T = [], [], [], []
+        q_rows = torch.full((B,), Tq, device=dev)
+        big = torch.iinfo(torch.int64).max
+        for pos, valid in zip(seg_pos, seg_valid):
+            Ts = pos.shape[1]
+            v = valid.to(torch.bool)
+            n_valid = v.sum(-1)
+            first = torch.where(n_valid > 0, v.to(torch.int64).argmax(-1), torch.zeros_like(n_valid))
+            keyed = torch.where(v, pos.to(torch.int64), torch.full_like(pos, big, dtype=torch.int64))
+            keyed, _ = keyed.sort(dim=-1)
+            cnt = torch.searchsorted(keyed, q_pos.to(torch.int64).contiguous(), right=True)
+            cnt = torch.minimum(cnt, n_valid[:, None])
+            base = (torch.arange(B, device=dev) * Ts + first)
+            self.bases.append(base[:, None].expand(B, Tq).reshape(-1).to(torch.int32).contiguous())
+            self.counts.append(cnt.reshape(-1).to(torch.int32).contiguous())
+            self.items.append(K.attn_kv_items(n_valid, base, q_rows))
+            self.seg_T.append(Ts)
+
+
+class _SegmentAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, meta: SegmentMeta, *kv):
+        B, Tq, nq, hd = q.shape
+        n_seg = len(kv) // 2
+        nkv = kv[0].shape[2]
+        q2 = q.reshape(B * Tq, nq * hd).contiguous()
+        ks = [kv[2 * s].reshape(-1, nkv * hd).contiguous() for s in range(n_seg)]
+        vs = [kv[2 * s + 1].reshape(-1, nkv * hd).contiguous() for s in range(n_seg)]
+        lse = torch.empty(B * Tq, nq, dtype=torch.float32, device=q.device)
+        out = K.prefill_attn(q2, ks, vs, meta.bases, meta.counts, meta.tile_q0, meta.tile_qn, nq, nkv, hd, hd ** -0.5,
+                             lse=lse)
+        ctx.meta, ctx.dims = meta, (B, Tq, nq, nkv, hd, n_seg)
+        ctx.save_for_backward(q2, out, lse, *ks, *vs)
+        return out.view(B, Tq, nq, hd)
+
+    @staticmethod
+    def backward(ctx, dout):
+        B, Tq, nq, nkv, hd, n_seg = ctx.dims
+        meta = ctx.meta
+        q2, out, lse = ctx.saved_tensors[:3]
+        ks = list(ctx.saved_tensors[3:3 + n_seg])
+        vs = list(ctx.saved_tensors[3 + n_seg:])
+        do2 = dout.reshape(B * Tq, nq * hd).contiguous()
+        dsum = (do2.float() * out.float()).view(B * Tq, nq, hd).sum(-1).contiguous()
+        scale = hd ** -0.5
+        dq = K.attn_bwd_dq(q2, do2, ks, vs, meta.bases, meta.counts, meta.tile_q0, meta.tile_qn, nq, nkv, hd, scale,
+                           lse, dsum)
+        grads = []
+        for s in range(n_seg):
+            dk, dv = K.attn_bwd_dkv(q2, do2, ks[s], vs[s], meta.counts[s], meta.items[s], nq, nkv, hd, scale, lse, dsum)
+            grads += [dk.view(B, meta.seg_T[s], nkv, hd), dv.view(B, meta.seg_T[s], nkv, hd)]
+        return (dq.view(B, Tq, nq, hd), None, *grads)
+
+
+def segment_attention_ok(q: torch.Tensor, n_seg: int) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and 1 <= n_seg <= 3
+            and q.shape[1] >= 16)
+
+
+def segment_attention(q, k_list, v_list, meta: SegmentMeta):
+    """Attention of the pass's queries ``[B, Tq, nq, hd]`` over the per-depth K/V segments
+    (``[B, Ts, nkv, hd]`` each) on the tcgen05 kernels, differentiable in q and every K/V."""
+    kv = []
+    for k, v in zip(k_list, v_list):
+        kv += [k, v]
+    return _SegmentAttention.apply(q, meta, *kv)
