@@ -268,8 +268,9 @@ struct BwdKVCfg {
   static constexpr int STAGE_BYTES = 2 * Q_BYTES;
   static constexpr int NSTAGE = 2;
   static constexpr int PT_BYTES = 128 * BQ * 2;                // P^T and dS^T tiles
-  static constexpr int SMEM_BYTES = 2 * K_BYTES + NSTAGE * STAGE_BYTES + 2 * PT_BYTES + 128;
-  static constexpr int TMEM_COLS = 512;                        // S^T at 0, dP^T at 64, dK at 128, dV at 256
+  static constexpr int META_BYTES = 2 * 3 * BQ * 4;            // [2 buffers][lse | dsum | count][64 queries]
+  static constexpr int SMEM_BYTES = 2 * K_BYTES + NSTAGE * STAGE_BYTES + 2 * PT_BYTES + META_BYTES + 128;
+  static constexpr int TMEM_COLS = 512;                        // scores at 0 / 384 (S^T, dP^T), dK at 128, dV at 256
 };
 
 template <int HD>
@@ -285,12 +286,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   uint8_t* qd_s = v_s + C::K_BYTES;                             // stages: [Q | dO]
   uint8_t* pt_s = qd_s + C::NSTAGE * C::STAGE_BYTES;
   uint8_t* dst_s = pt_s + C::PT_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dst_s + C::PT_BYTES);
+  float* meta_s = reinterpret_cast<float*>(dst_s + C::PT_BYTES);  // per-query lse, dsum, count of the sub-tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dst_s + C::PT_BYTES + C::META_BYTES);
   uint64_t* kv_full = bars;
   uint64_t* qd_full = bars + 1;                                 // [NSTAGE]
   uint64_t* qd_empty = qd_full + C::NSTAGE;                     // [NSTAGE]
-  uint64_t* s_full = qd_empty + C::NSTAGE;
-  uint64_t* p_ready = s_full + 1;
+  uint64_t* s_full = qd_empty + C::NSTAGE;                      // [2]: one per score buffer
+  uint64_t* p_ready = s_full + 2;
   uint64_t* acc_done = p_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -319,7 +321,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::NSTAGE; ++s) { mbar_init(&qd_full[s], 1); mbar_init(&qd_empty[s], 1); }
-    mbar_init(s_full, 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -333,7 +336,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_st = tmem_base, tmem_dpt = tmem_base + 64, tmem_dk = tmem_base + 128, tmem_dv = tmem_base + 256;
+  // two score buffers (S^T at +0, dP^T at +64 inside each) so that the scores of iteration it+1 are
+  // computed while the threads still work on iteration it
+  const uint32_t tmem_sc[2] = {tmem_base, tmem_base + 384};
+  const uint32_t tmem_dk = tmem_base + 128, tmem_dv = tmem_base + 256;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -367,21 +373,30 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       mbar_wait(kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
       const uint32_t pt_addr = smem_u32(pt_s), dst_addr = smem_u32(dst_s);
-      for (int it = 0; it < n_iter; ++it) {
-        const int st = it % C::NSTAGE;
-        const uint32_t ph = (it / C::NSTAGE) & 1;
-        mbar_wait(&qd_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
+      // scores of iteration `j`: S^T = K Q^T, dP^T = V dO^T over head_dim, into score buffer j & 1
+      auto issue_scores = [&](int j) {
+        const int st = j % C::NSTAGE;
+        mbar_wait(&qd_full[st], (j / C::NSTAGE) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
         tc_fence_after();
         const uint32_t q_addr = smem_u32(qd_s + st * C::STAGE_BYTES);
         const uint32_t do_addr = q_addr + C::Q_BYTES;
+        const uint32_t t_s = tmem_sc[j & 1];
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {      // S^T = K Q^T, dP^T = V dO^T over head_dim
+        for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t ko = (ks / 4) * C::KTILE + (ks % 4) * 32;
           const uint32_t qo = (ks / 4) * C::QTILE + (ks % 4) * 32;
-          umma_bf16(tmem_st, umma_desc_sw128(k_addr + ko), umma_desc_sw128(q_addr + qo), idesc_s, ks > 0 ? 1u : 0u);
-          umma_bf16(tmem_dpt, umma_desc_sw128(v_addr + ko), umma_desc_sw128(do_addr + qo), idesc_s, ks > 0 ? 1u : 0u);
+          umma_bf16(t_s, umma_desc_sw128(k_addr + ko), umma_desc_sw128(q_addr + qo), idesc_s, ks > 0 ? 1u : 0u);
+          umma_bf16(t_s + 64, umma_desc_sw128(v_addr + ko), umma_desc_sw128(do_addr + qo), idesc_s, ks > 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
+        umma_commit(&s_full[j & 1]);
+      };
+      if (n_iter > 0) issue_scores(0);
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it % C::NSTAGE;
+        const uint32_t q_addr = smem_u32(qd_s + st * C::STAGE_BYTES);
+        const uint32_t do_addr = q_addr + C::Q_BYTES;
+        // the other score buffer was last read for iteration it-1, whose p_ready has been waited for
+        if (it + 1 < n_iter) issue_scores(it + 1);
         mbar_wait(p_ready, it & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
         tc_fence_after();
 #pragma unroll
@@ -406,14 +421,43 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int kidx = kidx0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float sc = p.scale_log2;
+    // Per-query lse, dsum and visible-key count of a sub-tile are fetched by 64 threads (one query
+    // each, in parallel) one iteration ahead and handed over through shared memory; every thread then
+    // reads its 32 columns' values with broadcast vector loads.
+    const int mt = threadIdx.x - 64;               // 0..255 among the math threads
+    float m_l = 0.f, m_d = 0.f;
+    int m_c = 0;
+    auto fetch_meta = [&](int j) {
+      m_l = 0.f; m_d = 0.f; m_c = 0;
+      if (mt < BQ && j < n_iter) {
+        const int qr = qa + (sub0 + j / G) * BQ + mt;
+        if (qr < qb) {
+          const int hh = kvh * G + j % G;
+          m_c = p.kv_count[qr];
+          m_l = p.lse[(size_t)qr * p.nq + hh];
+          m_d = p.dsum[(size_t)qr * p.nq + hh];
+        }
+      }
+    };
+    auto store_meta = [&](int j) {
+      if (mt < BQ) {
+        float* mb = meta_s + (j & 1) * 3 * BQ;
+        mb[mt] = m_l;
+        mb[BQ + mt] = m_d;
+        reinterpret_cast<int*>(mb)[2 * BQ + mt] = m_c;
+      }
+    };
+    fetch_meta(0);
+    store_meta(0);
+    named_bar_sync(2, 256);
     for (int it = 0; it < n_iter; ++it) {
-      const int sub = sub0 + it / G, head = kvh * G + it % G;
-      const int qrow0 = qa + sub * BQ + half * 32;
-      mbar_wait(s_full, it & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
+      fetch_meta(it + 1);                          // in flight while this iteration computes
+      const float* mb = meta_s + (it & 1) * 3 * BQ + half * 32;
+      mbar_wait(&s_full[it & 1], (it >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
       tc_fence_after();
       float sv[32], dp[32];
-      tmem_ld32(tmem_st + lane_off + half * 32, sv);
-      tmem_ld32(tmem_dpt + lane_off + half * 32, dp);
+      tmem_ld32(tmem_sc[it & 1] + lane_off + half * 32, sv);
+      tmem_ld32(tmem_sc[it & 1] + 64 + lane_off + half * 32, dp);
       tmem_ld_wait();
       if (it > 0) mbar_wait(acc_done, (it - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
 #pragma unroll
@@ -421,24 +465,24 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         uint4 pk, dk;
         __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
         __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(&dk);
+        float lv[8], dv8[8];
+        int cv[8];
+        *reinterpret_cast<float4*>(lv) = *reinterpret_cast<const float4*>(mb + c * 8);
+        *reinterpret_cast<float4*>(lv + 4) = *reinterpret_cast<const float4*>(mb + c * 8 + 4);
+        *reinterpret_cast<float4*>(dv8) = *reinterpret_cast<const float4*>(mb + BQ + c * 8);
+        *reinterpret_cast<float4*>(dv8 + 4) = *reinterpret_cast<const float4*>(mb + BQ + c * 8 + 4);
+        *reinterpret_cast<int4*>(cv) = *reinterpret_cast<const int4*>(mb + 2 * BQ + c * 8);
+        *reinterpret_cast<int4*>(cv + 4) = *reinterpret_cast<const int4*>(mb + 2 * BQ + c * 8 + 4);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float pv[2], dsv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = c * 8 + 2 * j + e;
-            const int qr = qrow0 + col;              // packed query row (same for every lane: broadcast loads)
-            float pe = 0.f, de = 0.f;
-            if (qr < qb) {
-              const int cnt = p.kv_count[qr];
-              if (key_ok && kidx < cnt) {
-                const float l = p.lse[(size_t)qr * p.nq + head];
-                pe = exp2f(fmaf(sv[col], sc, -l));
-                de = pe * (dp[col] - p.dsum[(size_t)qr * p.nq + head]) * p.scale;
-              }
-            }
+            const int cl = 2 * j + e, col = c * 8 + cl;
+            const bool vis = key_ok && kidx < cv[cl];
+            const float pe = vis ? exp2f(fmaf(sv[col], sc, -lv[cl])) : 0.f;
             pv[e] = pe;
-            dsv[e] = de;
+            dsv[e] = pe * (dp[col] - dv8[cl]) * p.scale;
           }
           p2[j] = __floats2bfloat162_rn(pv[0], pv[1]);
           d2[j] = __floats2bfloat162_rn(dsv[0], dsv[1]);
@@ -451,6 +495,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
+      store_meta(it + 1);
+      named_bar_sync(2, 256);                      // next iteration's values visible; this buffer free again
     }
     if (n_iter > 0) mbar_wait(acc_done, (n_iter - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
     tc_fence_after();

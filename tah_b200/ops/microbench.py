@@ -131,6 +131,32 @@ def bench_prefill_attn(a):
     return {"op": "prefill_attn", "seqs": B, "len": L, "nq": nq, "nkv": nkv, "hd": hd, "flops_counted": "causal half"}, t, flops, byts
 
 
+def bench_attn_bwd(a):
+    """Backward of the packed causal attention: dQ kernel + dK/dV kernel (the forward supplies lse)."""
+    nq, nkv, hd = a.nq, a.nkv, a.hd
+    B, L = a.rows, a.ctx
+    ntok = B * L
+    q, k, v, do = _rand(ntok, nq * hd), _rand(ntok, nkv * hd), _rand(ntok, nkv * hd), _rand(ntok, nq * hd)
+    lens = torch.full((B,), L, device="cuda")
+    base = (torch.arange(B, device="cuda") * L).repeat_interleave(L).to(torch.int32)
+    cnt = (torch.arange(L, device="cuda") + 1).repeat(B).to(torch.int32)
+    tq0, tqn = K.attn_tiles(lens)
+    items = K.attn_kv_items(lens, torch.arange(B, device="cuda") * L, lens)
+    lse = torch.empty(ntok, nq, dtype=torch.float32, device="cuda")
+    out = K.prefill_attn(q, [k], [v], [base], [cnt], tq0, tqn, nq, nkv, hd, hd ** -0.5, lse=lse)
+    dsum = (do.float() * out.float()).view(ntok, nq, hd).sum(-1).contiguous()
+    dq = torch.empty_like(q)
+    dk, dv = torch.zeros_like(k), torch.zeros_like(v)
+    f_dq = lambda i: K.attn_bwd_dq(q, do, [k], [v], [base], [cnt], tq0, tqn, nq, nkv, hd, hd ** -0.5, lse, dsum, out=dq)
+    f_kv = lambda i: K.attn_bwd_dkv(q, do, k, v, cnt, items, nq, nkv, hd, hd ** -0.5, lse, dsum, dk=dk, dv=dv)
+    t_dq = _time(f_dq, a.iters, a.warmup)
+    t_kv = _time(f_kv, a.iters, a.warmup)
+    fwd = 4.0 * B * nq * hd * L * (L + 1) / 2
+    res = {"op": "attn_bwd", "seqs": B, "len": L, "nq": nq, "nkv": nkv, "hd": hd, "dq_us": round(t_dq * 1e6, 1),
+           "dkv_us": round(t_kv * 1e6, 1), "flops_counted": "2.5 x causal forward"}
+    return res, t_dq + t_kv, 2.5 * fwd, ntok * (2 * nq + 2 * nkv) * hd * 2 * 2
+
+
 def bench_topk(a):
     rows, V, k = a.rows, a.v, a.topk
     n = _copies(rows * V * 2, a.copies)
@@ -153,7 +179,7 @@ def bench_rmsnorm(a):
     return {"op": "rms_norm", "M": M, "H": H}, t, 0.0, 2 * M * H * 2
 
 
-OPS = {"gemm": bench_gemm, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn, "topk": bench_topk,
+OPS = {"attn_bwd": bench_attn_bwd, "gemm": bench_gemm, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn, "topk": bench_topk,
        "rmsnorm": bench_rmsnorm}
 
 
