@@ -13,7 +13,7 @@ import os
 import torch
 
 from tah_b200.ops import torch_ref
-from tah_b200.ops.torch_ref import duo_mask, sample, topk_softmax_embed  # noqa: F401
+from tah_b200.ops.torch_ref import duo_mask, sample  # noqa: F401
 
 
 def _use_cuda(x: torch.Tensor) -> bool:
@@ -46,6 +46,13 @@ def swiglu(gate_up):
         from tah_b200.ops import autograd_ops
         return autograd_ops.swiglu(gate_up)
     return torch_ref.swiglu(gate_up)
+
+
+def topk_softmax_embed(logits, embedding_weight, topk: int):
+    if _use_cuda(logits):
+        from tah_b200.ops import autograd_ops
+        return autograd_ops.topk_softmax_embed(logits, embedding_weight, topk)
+    return torch_ref.topk_softmax_embed(logits, embedding_weight, topk)
 
 
 def duo_attention(q, k, v, q_pos, kv_pos, kv_valid, q_depth=None, kv_depth=None):

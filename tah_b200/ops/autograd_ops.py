@@ -71,6 +71,11 @@ class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gy):
         x, w = ctx.saved_tensors
+        if x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+            x2 = x.reshape(-1, x.shape[-1]).contiguous()
+            g2 = gy.reshape(-1, x.shape[-1]).contiguous()
+            gx, gw = K.rms_norm_bwd(x2, w.contiguous(), g2, ctx.eps, want_gw=ctx.needs_input_grad[1])
+            return (gx.view_as(x) if ctx.needs_input_grad[0] else None), (gw.to(w.dtype) if gw is not None else None), None
         xf, gf, wf = x.float(), gy.float(), w.float()
         rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + ctx.eps)
         xn = xf * rstd
@@ -89,8 +94,37 @@ def rms_norm(x, weight, eps):
     return torch_ref.rms_norm(x, weight, eps)
 
 
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        g2 = gate_up.reshape(-1, gate_up.shape[-1]).contiguous()
+        ctx.save_for_backward(g2)
+        ctx.shape = gate_up.shape
+        return K.swiglu(g2).view(*gate_up.shape[:-1], gate_up.shape[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (g2,) = ctx.saved_tensors
+        return K.swiglu_bwd(g2, gy.reshape(-1, gy.shape[-1]).contiguous()).view(ctx.shape)
+
+
 def swiglu(gate_up):
+    if gate_up.dtype == torch.bfloat16 and gate_up.shape[-1] % 16 == 0 and gate_up.numel() > 0:
+        return _SwiGLU.apply(gate_up)
     return torch_ref.swiglu(gate_up)
+
+
+def topk_softmax_embed(logits, embedding_weight, topk: int):
+    """Soft next-pass input with the top-k indices from the radix-select kernel; the values are gathered
+    from ``logits`` so that gradients flow to the logits and to the embedding rows as in the reference."""
+    k = min(topk, logits.size(-1))
+    if logits.dtype != torch.bfloat16 or logits.dim() != 2 or k > 128 or logits.numel() == 0:
+        return torch_ref.topk_softmax_embed(logits, embedding_weight, topk)
+    _, idx = K.topk_rows(logits.detach().contiguous(), k)
+    idx = idx.long()
+    vals = logits.gather(-1, idx)
+    probs = torch.softmax(vals, dim=-1)
+    return (probs.unsqueeze(-1) * embedding_weight[idx]).sum(-2).to(embedding_weight.dtype)
 
 
 def duo_attention(q, k, v, q_pos, kv_pos, kv_valid, q_depth=None, kv_depth=None):

@@ -239,6 +239,24 @@ def qk_norm_rope_kv(qkv, q_w, k_w, pos, nq: int, nkv: int, hd: int, eps: float, 
     return q_out
 
 
+def rms_norm_bwd(x: torch.Tensor, w: torch.Tensor, gy: torch.Tensor, eps: float, want_gw: bool = True):
+    """Backward of :func:`rms_norm` on contiguous ``[M, H]`` bf16 tensors: returns ``(gx, gw_fp32 or None)``."""
+    M, H = x.shape
+    gx = torch.empty_like(x)
+    gw = torch.zeros(H, dtype=torch.float32, device=x.device) if want_gw else None
+    _rc(lib().tahb_rmsnorm_bwd(_p(x), _p(w), _p(gy), _p(gx), _p(gw), c_int(M), c_int(H), c_float(eps), _stream()),
+        "tahb_rmsnorm_bwd")
+    return gx, gw
+
+
+def swiglu_bwd(gate_up: torch.Tensor, gy: torch.Tensor) -> torch.Tensor:
+    """Backward of :func:`swiglu`: ``gate_up`` ``[M, 2I]``, ``gy`` ``[M, I]`` (contiguous bf16) -> ``[M, 2I]``."""
+    M, I2 = gate_up.shape
+    out = torch.empty_like(gate_up)
+    _rc(lib().tahb_swiglu_bwd(_p(gate_up), _p(gy), _p(out), c_ll(M), c_int(I2 // 2), _stream()), "tahb_swiglu_bwd")
+    return out
+
+
 def embed_gather(E, tok, out=None):
     M, H = tok.shape[0], E.shape[1]
     if out is None:

@@ -391,6 +391,26 @@ def test_lora_a_rows_and_swiglu():
     _close(Kc.swiglu(gu), torch_ref.swiglu(gu), atol=1e-2, rtol=1e-2)
 
 
+def test_rmsnorm_and_swiglu_backward_kernels():
+    Kc = _cuda()
+    M, H = 77, 2048
+    x = _rand(M, H, seed=1).requires_grad_(True)
+    w = (_rand(H, seed=2) * 0.1 + 1).to(torch.bfloat16).requires_grad_(True)
+    gy = _rand(M, H, seed=3)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yf = wf * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6))
+    yf.backward(gy.float())
+    gx, gw = Kc.rms_norm_bwd(x.detach(), w.detach(), gy, 1e-6)
+    _close(gx, xf.grad, atol=2e-2, rtol=2e-2)
+    _close(gw, wf.grad, atol=5e-2, rtol=2e-2)
+    gu = _rand(33, 2 * 768, seed=4)
+    gy2 = _rand(33, 768, seed=5)
+    guf = gu.float().requires_grad_(True)
+    g, u = guf.chunk(2, -1)
+    (torch.nn.functional.silu(g) * u).backward(gy2.float())
+    _close(Kc.swiglu_bwd(gu, gy2), guf.grad, atol=3e-2, rtol=3e-2)
+
+
 def test_sampler_topk_distribution():
     Kc = _cuda()
     rows, K = 4096, 8
