@@ -31,6 +31,7 @@ sys.path.insert(0, ROOT)
 
 MODEL = "tah-plus-1.7b"
 BATCH, PROMPT, NEW_TOKENS, HARD_P, LORA_R = 256, 256, 2048, 0.06, 64
+MAX_ITER = 2
 # profiling aid only: a shorter prompt makes the (unprofiled) prefill cheap under ncu; results printed
 # with this override are not benchmark values
 PROMPT = int(os.environ.get("TAH_B200_BENCH_PROMPT", PROMPT))
@@ -99,7 +100,7 @@ def build_model(device, n_layers=None):
     cfg = preset(MODEL) if n_layers is None else preset(MODEL, num_hidden_layers=n_layers)
     with torch.device(device):
         base = Qwen3ForCausalLM(cfg, dtype=torch.bfloat16)
-    tcfg = TaHConfig(max_iter=2, iter_decider="SimpleMLPIterDecider",
+    tcfg = TaHConfig(max_iter=MAX_ITER, iter_decider="SimpleMLPIterDecider",
                      iter_decider_kwargs=dict(hidden_states_size=cfg.hidden_size, inner_size=cfg.hidden_size // 4,
                                               threshold=0.5),
                      adapter_kwargs=dict(r=LORA_R, lora_alpha=2 * LORA_R, lora_dropout=0.0, target_modules="all-linear"),
@@ -130,7 +131,8 @@ def run_ours(args):
     from tah_b200.ops import cuda as K
     model = build_model(dev)
     eng = TaHEngine(model, max_rows=BATCH, max_seq_len=PROMPT + NEW_TOKENS + 8, tp=tp)
-    eng.hard_override = eng.make_bernoulli_override(BATCH, (HARD_P,), seed=0)
+    hard_p = HARD_P if isinstance(HARD_P, tuple) else (HARD_P,)
+    eng.hard_override = eng.make_bernoulli_override(BATCH, hard_p, seed=0)
     g = torch.Generator().manual_seed(1234)
     prompts_host = torch.randint(0, model.config.vocab_size, (BATCH, PROMPT), generator=g).pin_memory()
 
@@ -193,12 +195,14 @@ def run_ours(args):
 
     if rank == 0:
         out = {
-            "metric": "TaH-plus-1.7B decode tok/s (2-iter, TP=N)", "value": round(value, 1), "unit": "tokens/s",
+            "metric": ("TaH-plus-1.7B decode tok/s (2-iter, TP=N)" if MODEL == "tah-plus-1.7b" and MAX_ITER == 2
+                       else f"{MODEL} decode tok/s ({MAX_ITER}-iter, TP=N)"), "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": Kt, "warmup": W, "ms_per_step": round(ms / Kt, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": round(value / 8.5, 1), "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": MODEL, "layers": model.config.num_hidden_layers, "global_batch": BATCH, "seq_len": PROMPT,
-                       "new_tokens": NEW_TOKENS, "hard_token_rate": HARD_P, "max_iter": 2, "lora_rank": LORA_R,
+                       "new_tokens": NEW_TOKENS, "hard_token_rate": hard_p[0] if len(hard_p) == 1 else list(hard_p),
+                       "max_iter": MAX_ITER, "lora_rank": LORA_R,
                        "parallelism": f"tp{world}", "step": "one engine tick (one pass of every row)",
                        "l2": "per-tick inputs (3.4 GB weights + KV pages) exceed the 126 MB L2",
                        "baseline_number": "8.5 tok/s single-stream (only published figure)"},
@@ -239,7 +243,7 @@ def run_eager(args):
         def forward(self, logits, iter_depth, **kw):
             if iter_depth >= 2:
                 return self._stop_decision(logits, -10.0)
-            return torch.rand(logits.shape[0], device=dev, generator=self.g) < HARD_P, torch.zeros(logits.shape[0], device=dev)
+            return torch.rand(logits.shape[0], device=dev, generator=self.g) < HARD_P[0], torch.zeros(logits.shape[0], device=dev)
 
     model.iter_decider = model.eval_iter_decider = Coin()
     n = args.steps
@@ -269,13 +273,26 @@ def run_reference(args):
 
 
 def main():
+    global MODEL, BATCH, PROMPT, NEW_TOKENS, HARD_P, MAX_ITER
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1024)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager"])
     ap.add_argument("--eager-batch", type=int, default=64)
+    # the defaults are the headline configuration (batch 256 x prompt 256 -> 2048 new tokens on the
+    # 28-layer model); the flags below select the other serving configurations, e.g.
+    #   --model tah-1.7b --batch 64 --prompt 512 --new-tokens 1024        (27 layers, one GPU)
+    #   --model qwen3-4b --batch 128 --prompt 4096 --new-tokens 4096 --max-iter 3 --hard-p 0.06,0.02
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--new-tokens", type=int, default=NEW_TOKENS)
+    ap.add_argument("--max-iter", type=int, default=2)
+    ap.add_argument("--hard-p", default=str(HARD_P), help="comma-separated continue probabilities per depth")
     args = ap.parse_args()
+    MODEL, BATCH, PROMPT, NEW_TOKENS, MAX_ITER = args.model, args.batch, args.prompt, args.new_tokens, args.max_iter
+    HARD_P = tuple(float(x) for x in args.hard_p.split(","))
     if args.impl == "reference":
         run_reference(args)
     elif args.impl == "eager":
