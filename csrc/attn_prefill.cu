@@ -49,6 +49,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r)::"memory");   // r is valid only after the wait
+  return __uint_as_float(r);
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <int HD>
@@ -63,8 +72,11 @@ struct PfCfg {
   static constexpr int P_BYTES = 128 * BK * 2;                // 128 rows x 64 keys = 16 KiB
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
   static constexpr int NSTAGE = 2;
-  static constexpr int X_BYTES = 2 * 2 * 128 * 4;             // row-maximum exchange [parity][half][row]
-  static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSTAGE * STAGE_BYTES + X_BYTES + 128;
+  // 112 KiB of tiles + barriers: two CTAs fit in an SM's 228 KiB (1 KiB is reserved per CTA), so the
+  // two threads of a query row exchange their partial row maximum / sum through spare tensor-memory
+  // columns of their lane instead of shared memory
+  static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSTAGE * STAGE_BYTES + 128;
+  static constexpr int XCOL = 64;                             // exchange columns 64..67 (parity, half): S is 0..63, O 128..
   static constexpr int TMEM_COLS = 256;                       // S: 64 columns (at 0), O: HD columns (at 128)
 };
 constexpr int PF_THREADS = 320;                               // 2 + 8 warps; two CTAs share an SM
@@ -81,8 +93,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint8_t* q_s = smem;
   uint8_t* p_s = q_s + C::Q_BYTES;
   uint8_t* kv_s = p_s + C::P_BYTES;
-  float* xmax = reinterpret_cast<float*>(kv_s + C::NSTAGE * C::STAGE_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xmax) + C::X_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + C::NSTAGE * C::STAGE_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;                 // [NSTAGE]
   uint64_t* kv_empty = kv_full + C::NSTAGE;     // [NSTAGE]
@@ -228,10 +239,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           }
         }
         // combine the two halves of the row
-        float* xm = xmax + (i & 1) * 256;
-        xm[half * 128 + row] = mx;
+        const uint32_t xcol = tmem_base + lane_off + C::XCOL + (i & 1) * 2;
+        tmem_st1(xcol + half, mx);
+        tmem_st_wait();
+        tc_fence_before();
         named_bar_sync(1, 256);
-        mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]) * sc;
+        tc_fence_after();
+        mx = fmaxf(mx, tmem_ld1(xcol + (half ^ 1))) * sc;
         // lazy reference maximum: refresh only when it grew by more than 8 (a factor 256)
         const bool grow = mx > m_ref + 8.0f;
         const float m_new = grow ? mx : m_ref;
@@ -280,11 +294,16 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // epilogue: O / l, each thread writes its half of head_dim
     if (total_blocks > 0) mbar_wait(pv_done, (total_blocks - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
     tc_fence_after();
-    float* xl = xmax;                            // reuse the exchange buffer for the row sums
-    named_bar_sync(1, 256);
-    xl[half * 128 + row] = l;
-    named_bar_sync(1, 256);
-    l += xl[(half ^ 1) * 128 + row];
+    {                                            // combine the two halves' row sums the same way
+      const uint32_t xcol = tmem_base + lane_off + C::XCOL;
+      named_bar_sync(1, 256);
+      tmem_st1(xcol + half, l);
+      tmem_st_wait();
+      tc_fence_before();
+      named_bar_sync(1, 256);
+      tc_fence_after();
+      l += tmem_ld1(xcol + (half ^ 1));
+    }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     if (p.lse != nullptr && half == 0 && row_ok)
       p.lse[(size_t)(q0 + row) * p.nq + head] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
