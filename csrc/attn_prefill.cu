@@ -30,7 +30,9 @@ struct PrefillParams {
   const int* tile_q0;            // [n_tiles] first packed query index of the tile
   const int* tile_qn;            // [n_tiles] number of query rows (<= 128)
   const int* seg_base[PF_MAX_SEG];   // [n_q] first KV row of the query's sequence in the segment
-  const int* seg_count[PF_MAX_SEG];  // [n_q] number of visible KV rows (non-decreasing inside a tile)
+  const int* seg_count[PF_MAX_SEG];  // [n_q] number of visible KV rows of each query
+  const int* seg_bound[PF_MAX_SEG];  // [n_q] non-decreasing upper bound of seg_count inside a sequence: the
+                                     // bound of a tile's last row tells how many key blocks the tile walks
   int n_seg, nq, nkv;
   float scale_log2;
   float* lse;                    // optional [n_q, nq]: log2-domain log-sum-exp of the scaled scores (for backward)
@@ -120,7 +122,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     seg_b0[s] = 0;
     if (s < p.n_seg) {
       seg_b0[s] = p.seg_base[s][q0];
-      seg_blocks[s] = (p.seg_count[s][q0 + qn - 1] + BK - 1) / BK;
+      seg_blocks[s] = (p.seg_bound[s][q0 + qn - 1] + BK - 1) / BK;
     }
     total_blocks += seg_blocks[s];
   }
@@ -345,7 +347,8 @@ using namespace tahb;
 // q [n_q, nq*hd], out same; ks/vs[s] [n_kv[s], nkv*hd] (contiguous, bf16); tiles: tile_q0/tile_qn [n_tiles];
 // bases/counts[s]: per query token.  Counts must be non-decreasing inside a tile.
 extern "C" int tahb_prefill_attn(const void* q, void* out, void* const* ks, void* const* vs, const long long* n_kv,
-                                 const int* const* bases, const int* const* counts, int n_seg, const int* tile_q0,
+                                 const int* const* bases, const int* const* counts, const int* const* bounds,
+                                 int n_seg, const int* tile_q0,
                                  const int* tile_qn, int n_tiles, long long n_q, int nq, int nkv, int hd, float scale,
                                  float* lse, int* status, cudaStream_t stream) {
   if (n_tiles <= 0 || n_q <= 0) return 0;
@@ -366,6 +369,7 @@ extern "C" int tahb_prefill_attn(const void* q, void* out, void* const* ks, void
     const int ss = s < n_seg ? s : 0;
     p.seg_base[s] = bases[ss];
     p.seg_count[s] = counts[ss];
+    p.seg_bound[s] = bounds[ss];
   }
   p.n_seg = n_seg; p.nq = nq; p.nkv = nkv;
   p.scale_log2 = scale * 1.4426950408889634f;

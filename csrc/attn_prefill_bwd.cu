@@ -29,6 +29,7 @@ struct AttnBwdParams {
   const int* tile_qn;
   const int* seg_base[PF_MAX_SEG];    // [n_q]
   const int* seg_count[PF_MAX_SEG];   // [n_q]
+  const int* seg_bound[PF_MAX_SEG];   // [n_q] non-decreasing upper bound of seg_count (tiling decisions)
   const float* lse;                   // [n_q, nq] base-2 log-sum-exp from the forward
   const float* dsum;                  // [n_q, nq] rowsum(dO * O)
   __nv_bfloat16* dq;                  // [n_q, nq * HD]
@@ -41,6 +42,7 @@ struct AttnBwdParams {
   const int* kv_qa;                   // [n_items] first packed query row of the sequence
   const int* kv_qb;                   // [n_items] one past its last query row
   const int* kv_count;                // [n_q] visible-key counts of this segment (= seg_count[s])
+  const int* kv_bound;                // [n_q] its non-decreasing upper bound (which sub-tiles to skip)
   __nv_bfloat16* dk;                  // [n_kv, nkv * HD]
   __nv_bfloat16* dv;
   int* status;
@@ -100,7 +102,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     seg_b0[s] = 0;
     if (s < p.n_seg) {
       seg_b0[s] = p.seg_base[s][q0];
-      seg_blocks[s] = (p.seg_count[s][q0 + qn - 1] + BK - 1) / BK;
+      seg_blocks[s] = (p.seg_bound[s][q0 + qn - 1] + BK - 1) / BK;
     }
     total_blocks += seg_blocks[s];
   }
@@ -313,7 +315,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   while (lo < hi) {
     const int mid = (lo + hi) >> 1;
     const int last = min(qb, qa + (mid + 1) * BQ) - 1;
-    if (p.kv_count[last] > kidx0) hi = mid; else lo = mid + 1;
+    if (p.kv_bound[last] > kidx0) hi = mid; else lo = mid + 1;
   }
   const int sub0 = lo;
   const int n_iter = (n_sub - sub0) * G;                        // (sub-tile, head of the group) pairs
@@ -543,7 +545,8 @@ using namespace tahb;
 // dQ of the packed attention.  Arguments as tahb_prefill_attn plus dout [n_q, nq*hd], lse and dsum
 // ([n_q, nq] fp32) and the output dq [n_q, nq*hd].
 extern "C" int tahb_attn_bwd_dq(const void* q, const void* dout, void* dq, void* const* ks, void* const* vs,
-                                const long long* n_kv, const int* const* bases, const int* const* counts, int n_seg,
+                                const long long* n_kv, const int* const* bases, const int* const* counts,
+                                const int* const* bounds, int n_seg,
                                 const int* tile_q0, const int* tile_qn, int n_tiles, long long n_q, int nq, int nkv,
                                 int hd, float scale, const float* lse, const float* dsum, int* status,
                                 cudaStream_t stream) {
@@ -565,6 +568,7 @@ extern "C" int tahb_attn_bwd_dq(const void* q, const void* dout, void* dq, void*
     const int ss = s < n_seg ? s : 0;
     p.seg_base[s] = bases[ss];
     p.seg_count[s] = counts[ss];
+    p.seg_bound[s] = bounds[ss];
   }
   p.lse = lse;
   p.dsum = dsum;
@@ -597,7 +601,7 @@ extern "C" int tahb_attn_bwd_dq(const void* q, const void* dout, void* dq, void*
 // item_row0 / item_nkeys / item_kidx0 / item_qa / item_qb, [n_items] each; count: the segment's
 // visible-key counts per packed query.  dk / dv [n_kv, nkv*hd] are written for every key of every item.
 extern "C" int tahb_attn_bwd_dkv(const void* q, const void* dout, const void* k, const void* v, void* dk, void* dv,
-                                 long long n_kv, const int* count, const int* item_row0, const int* item_nkeys,
+                                 long long n_kv, const int* count, const int* bound, const int* item_row0, const int* item_nkeys,
                                  const int* item_kidx0, const int* item_qa, const int* item_qb, int n_items,
                                  long long n_q, int nq, int nkv, int hd, float scale, const float* lse,
                                  const float* dsum, int* status, cudaStream_t stream) {
@@ -617,6 +621,7 @@ extern "C" int tahb_attn_bwd_dkv(const void* q, const void* dout, const void* k,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.kv_row0 = item_row0; p.kv_nkeys = item_nkeys; p.kv_kidx0 = item_kidx0; p.kv_qa = item_qa; p.kv_qb = item_qb;
   p.kv_count = count;
+  p.kv_bound = bound;
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
   p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
   p.status = status;

@@ -78,7 +78,8 @@ class TaHCache(PassKV):
             return None
         ks, vs, ps, ms = seg
         if self._seg_meta is None:
-            self._seg_meta = autograd_ops.SegmentMeta(self.position_ids_to_cache, ps, ms)
+            self._seg_meta = autograd_ops.SegmentMeta(self.position_ids_to_cache, ps, ms,
+                                                      q_valid=self.valid_mask_to_cache)
         out = autograd_ops.segment_attention(q, ks, vs, self._seg_meta)
         if self._store_pass:
             self.update(k, v, layer_idx)

@@ -6,7 +6,7 @@ of 64); the backward passes are written out explicitly here.  Inputs the kernels
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 import torch.nn.functional as F
@@ -144,12 +144,13 @@ class SegmentMeta:
     first valid entry) and ``count`` (prefix length).
     """
 
-    def __init__(self, q_pos: torch.Tensor, seg_pos: Sequence[torch.Tensor], seg_valid: Sequence[torch.Tensor]):
+    def __init__(self, q_pos: torch.Tensor, seg_pos: Sequence[torch.Tensor], seg_valid: Sequence[torch.Tensor],
+                 q_valid: Optional[torch.Tensor] = None):
         B, Tq = q_pos.shape
         dev = q_pos.device
         self.B, self.Tq = B, Tq
         self.tile_q0, self.tile_qn = K.attn_tiles(torch.full((B,), Tq, device=dev))
-        self.bases, self.counts, self.items, self.seg_T = [], [], [], []
+        self.bases, self.counts, self.bounds, self.items, self.seg_T = [], [], [], [], []
         q_rows = torch.full((B,), Tq, device=dev)
         big = torch.iinfo(torch.int64).max
         for pos, valid in zip(seg_pos, seg_valid):
@@ -161,9 +162,14 @@ class SegmentMeta:
             keyed, _ = keyed.sort(dim=-1)
             cnt = torch.searchsorted(keyed, q_pos.to(torch.int64).contiguous(), right=True)
             cnt = torch.minimum(cnt, n_valid[:, None])
+            if q_valid is not None:              # padding queries see nothing (zero output, zero gradients)
+                cnt = cnt * q_valid.to(cnt.dtype)
+            # the kernels size a tile's key walk by its last row: give them a non-decreasing bound
+            bound = torch.cummax(cnt, dim=-1).values
             base = (torch.arange(B, device=dev) * Ts + first)
             self.bases.append(base[:, None].expand(B, Tq).reshape(-1).to(torch.int32).contiguous())
             self.counts.append(cnt.reshape(-1).to(torch.int32).contiguous())
+            self.bounds.append(bound.reshape(-1).to(torch.int32).contiguous())
             self.items.append(K.attn_kv_items(n_valid, base, q_rows))
             self.seg_T.append(Ts)
 
@@ -179,7 +185,7 @@ class _SegmentAttention(torch.autograd.Function):
         vs = [kv[2 * s + 1].reshape(-1, nkv * hd).contiguous() for s in range(n_seg)]
         lse = torch.empty(B * Tq, nq, dtype=torch.float32, device=q.device)
         out = K.prefill_attn(q2, ks, vs, meta.bases, meta.counts, meta.tile_q0, meta.tile_qn, nq, nkv, hd, hd ** -0.5,
-                             lse=lse)
+                             lse=lse, bounds=meta.bounds)
         ctx.meta, ctx.dims = meta, (B, Tq, nq, nkv, hd, n_seg)
         ctx.save_for_backward(q2, out, lse, *ks, *vs)
         return out.view(B, Tq, nq, hd)
@@ -195,10 +201,11 @@ class _SegmentAttention(torch.autograd.Function):
         dsum = (do2.float() * out.float()).view(B * Tq, nq, hd).sum(-1).contiguous()
         scale = hd ** -0.5
         dq = K.attn_bwd_dq(q2, do2, ks, vs, meta.bases, meta.counts, meta.tile_q0, meta.tile_qn, nq, nkv, hd, scale,
-                           lse, dsum)
+                           lse, dsum, bounds=meta.bounds)
         grads = []
         for s in range(n_seg):
-            dk, dv = K.attn_bwd_dkv(q2, do2, ks[s], vs[s], meta.counts[s], meta.items[s], nq, nkv, hd, scale, lse, dsum)
+            dk, dv = K.attn_bwd_dkv(q2, do2, ks[s], vs[s], meta.counts[s], meta.items[s], nq, nkv, hd, scale, lse, dsum,
+                                    bound=meta.bounds[s])
             grads += [dk.view(B, meta.seg_T[s], nkv, hd), dv.view(B, meta.seg_T[s], nkv, hd)]
         return (dq.view(B, Tq, nq, hd), None, *grads)
 

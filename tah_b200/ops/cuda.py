@@ -348,10 +348,11 @@ def attn_tiles(seq_counts: torch.Tensor, tile: int = 128):
     return q0.to(torch.int32).contiguous(), qn.to(torch.int32).contiguous()
 
 
-def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, out=None, lse=None):
+def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, out=None, lse=None, bounds=None):
     """Packed duo-causal attention on the tensor cores (``csrc/attn_prefill.cu``).  Same contract as
     :func:`varlen_attn_naive` plus the query tiling of :func:`attn_tiles`: the tokens of a tile belong
-    to one sequence, share ``bases[s]`` and have non-decreasing ``counts[s]``.  ``lse`` (optional fp32
+    to one sequence and share ``bases[s]``.  ``counts[s]`` must be non-decreasing along a sequence's rows, or
+    ``bounds[s]`` must give such a non-decreasing upper bound (rows whose count was zeroed, e.g. padding).  ``lse`` (optional fp32
     ``[n_q, nq]``) receives the base-2 log-sum-exp of the scaled scores, which the backward kernels take."""
     if out is None:
         out = torch.empty_like(q)
@@ -361,7 +362,7 @@ def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale,
             raise ValueError("prefill_attn wants contiguous bf16 tensors")
     n_kv = (c_ll * n)(*[k.shape[0] for k in ks])
     _rc(lib().tahb_prefill_attn(_p(q), _p(out), _ptr_array(ks), _ptr_array(vs), n_kv, _ptr_array(bases),
-                                _ptr_array(counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
+                                _ptr_array(counts), _ptr_array(bounds if bounds is not None else counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
                                 c_ll(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse),
                                 _p(status_word(q.device)), _stream()), "tahb_prefill_attn")
     return out
@@ -389,20 +390,21 @@ def attn_kv_items(seq_kv_counts: torch.Tensor, seq_kv_base: torch.Tensor, seq_q_
     return i32(row0), i32(nkeys), i32(kidx0), i32(qa), i32(qb)
 
 
-def attn_bwd_dq(q, dout, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, lse, dsum, out=None):
+def attn_bwd_dq(q, dout, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, lse, dsum, out=None,
+                bounds=None):
     """dQ of :func:`prefill_attn` (``csrc/attn_prefill_bwd.cu``); ``dsum = rowsum(dO * O)`` per (query, head)."""
     if out is None:
         out = torch.empty_like(q)
     n = len(ks)
     n_kv = (c_ll * n)(*[k.shape[0] for k in ks])
     _rc(lib().tahb_attn_bwd_dq(_p(q), _p(dout), _p(out), _ptr_array(ks), _ptr_array(vs), n_kv, _ptr_array(bases),
-                               _ptr_array(counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
+                               _ptr_array(counts), _ptr_array(bounds if bounds is not None else counts), c_int(n), _p(tile_q0), _p(tile_qn), c_int(tile_q0.numel()),
                                c_ll(q.shape[0]), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse), _p(dsum),
                                _p(status_word(q.device)), _stream()), "tahb_attn_bwd_dq")
     return out
 
 
-def attn_bwd_dkv(q, dout, k, v, count, items, nq, nkv, hd, scale, lse, dsum, dk=None, dv=None):
+def attn_bwd_dkv(q, dout, k, v, count, items, nq, nkv, hd, scale, lse, dsum, dk=None, dv=None, bound=None):
     """dK, dV of one KV segment of :func:`prefill_attn`; ``items`` from :func:`attn_kv_items`, ``count`` the
     segment's visible-key counts per packed query.  Keys outside every item keep a zero gradient."""
     if dk is None:
@@ -410,7 +412,8 @@ def attn_bwd_dkv(q, dout, k, v, count, items, nq, nkv, hd, scale, lse, dsum, dk=
     if dv is None:
         dv = torch.zeros_like(v)
     row0, nkeys, kidx0, qa, qb = items
-    _rc(lib().tahb_attn_bwd_dkv(_p(q), _p(dout), _p(k), _p(v), _p(dk), _p(dv), c_ll(k.shape[0]), _p(count), _p(row0),
+    _rc(lib().tahb_attn_bwd_dkv(_p(q), _p(dout), _p(k), _p(v), _p(dk), _p(dv), c_ll(k.shape[0]), _p(count),
+                                _p(bound if bound is not None else count), _p(row0),
                                 _p(nkeys), _p(kidx0), _p(qa), _p(qb), c_int(row0.numel()), c_ll(q.shape[0]),
                                 c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse), _p(dsum),
                                 _p(status_word(q.device)), _stream()), "tahb_attn_bwd_dkv")

@@ -458,8 +458,10 @@ def test_zero_adamw_cuda_single_gpu_matches_fp32_adamw():
             off += k
 
 
-def test_training_step_on_gpu_matches_cpu_reference():
-    """bf16 model on the GPU (kernel forward, explicit backward) vs the same model in fp32 on the CPU."""
+@pytest.mark.parametrize("pad", [False, True])
+def test_training_step_on_gpu_matches_cpu_reference(pad):
+    """bf16 model on the GPU (kernel forward, explicit backward) vs the same model in fp32 on the CPU;
+    with ``pad`` the second sample is left-padded (padding queries and keys, ragged deeper pass)."""
     import copy
     from tests.helpers import tiny_tah
     model = tiny_tah(dtype=torch.bfloat16)
@@ -469,11 +471,16 @@ def test_training_step_on_gpu_matches_cpu_reference():
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, 1024, (2, 48), generator=g)
     hard = (torch.rand(2, 48, generator=g) < 0.1).long() + 1
-    out = model(ids.cuda(), labels=ids.cuda(), iter_count_labels=hard.cuda())
+    mask = torch.ones(2, 48, dtype=torch.long)
+    labels = ids.clone()
+    if pad:
+        mask[1, :13] = 0
+        labels[1, :13] = -100
+    out = model(ids.cuda(), attention_mask=mask.cuda(), labels=labels.cuda(), iter_count_labels=hard.cuda())
     out.loss.backward()
-    rout = ref(ids, labels=ids, iter_count_labels=hard)
+    rout = ref(ids, attention_mask=mask, labels=labels, iter_count_labels=hard)
     rout.loss.backward()
-    assert abs(float(out.loss) - float(rout.loss)) < 0.05
+    assert abs(float(out.loss.detach()) - float(rout.loss.detach())) < 0.05
     ga = model.simple_base_model.model.layers[0].self_attn.qkv_proj.weight.grad.float().cpu()
     gb = ref.simple_base_model.model.layers[0].self_attn.qkv_proj.weight.grad
     cos = torch.nn.functional.cosine_similarity(ga.flatten(), gb.flatten(), dim=0)

@@ -245,3 +245,52 @@ def test_padding_positions_count_one_pass():
     with torch.no_grad():
         out = model(ids, attention_mask=attn, labels=ids, iter_count_labels=hard)
     assert out.iter_count[0, :3].tolist() == [1, 1, 1] and (out.iter_count[attn.bool()] == 2).all()
+
+
+def test_segment_meta_matches_duo_mask_cpu():
+    """The (base, count) prefixes handed to the tensor-core attention kernels describe exactly the keys
+    that the duo-causal mask allows, for left-padded and right-padded batches and a sparse deeper pass."""
+    import torch
+    from tah_b200.ops.autograd_ops import SegmentMeta
+    from tah_b200.ops.torch_ref import duo_mask
+    B, T = 3, 11
+    for pad_left in (True, False):
+        lens = torch.tensor([11, 7, 3])
+        valid0 = torch.zeros(B, T, dtype=torch.long)
+        for b, n in enumerate(lens.tolist()):
+            if pad_left:
+                valid0[b, T - n:] = 1
+            else:
+                valid0[b, :n] = 1
+        pos0 = (valid0.cumsum(-1) - 1).clamp(min=0)
+        # deeper pass: a subset of the valid tokens, packed to the left of a narrower block
+        g = torch.Generator().manual_seed(3)
+        act = (torch.rand(B, T, generator=g) < 0.5) & valid0.bool()
+        act[:, -1] |= valid0[:, -1].bool()
+        width = int(act.sum(1).max())
+        pos1 = torch.zeros(B, width, dtype=torch.long)
+        valid1 = torch.zeros(B, width, dtype=torch.long)
+        for b in range(B):
+            idx = act[b].nonzero().flatten()
+            pos1[b, :idx.numel()] = pos0[b, idx]
+            valid1[b, :idx.numel()] = 1
+        # queries of the deeper pass see depth-0 keys and depth-1 keys
+        meta = SegmentMeta(pos1, [pos0, pos1], [valid0, valid1], q_valid=valid1)
+        for s, (kp, kv, Ts) in enumerate(((pos0, valid0, T), (pos1, valid1, width))):
+            mask = duo_mask(pos1, kp, kv)                               # [B, width, Ts]
+            base = meta.bases[s].view(B, width)
+            cnt = meta.counts[s].view(B, width)
+            for b in range(B):
+                for i in range(width):
+                    if not valid1[b, i]:
+                        continue
+                    want = mask[b, i].nonzero().flatten() + b * Ts
+                    got = torch.arange(int(base[b, i]), int(base[b, i]) + int(cnt[b, i]))
+                    assert torch.equal(want, got), (pad_left, s, b, i)
+            # padding queries see nothing; the tiling bound never decreases along a sample's rows and
+            # is never below the count
+            assert (cnt[valid1 == 0] == 0).all()
+            bound = meta.bounds[s].view(B, width)
+            assert (bound[:, 1:] >= bound[:, :-1]).all() and (bound >= cnt).all()
+        row0, nkeys, kidx0, qa, qb = meta.items[0]
+        assert int(nkeys.sum()) == int(valid0.sum()) and torch.equal(qb - qa, torch.full_like(qa, width))
