@@ -134,9 +134,136 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward of the per-head QK RMSNorm + rotate-half RoPE (forward: qk_norm_rope_kv_kernel in
+// elementwise.cu).  One warp per (token, head), grid-stride; lane l owns elements l*EPL..+EPL-1.
+//   n = w * (x * rstd),  y = n * cos + rot(n) * sin      (q and k heads; v heads pass through)
+//   gn = gy * cos +/- partner(gy) * sin ;  gx = rstd * (gn*w - xn * mean(gn*w*xn)) ;  gw += gn * xn
+// The weight gradients are summed per CTA in shared memory and added to the fp32 buffers once.
+// ---------------------------------------------------------------------------------------------
+struct QkRopeBwdParams {
+  const __nv_bfloat16* qkv;      // [M, (nq + 2 nkv) * HD] forward input
+  const __nv_bfloat16* q_w;
+  const __nv_bfloat16* k_w;
+  const __nv_bfloat16* gq;       // [M, nq * HD]
+  const __nv_bfloat16* gk;       // [M, nkv * HD]
+  const __nv_bfloat16* gv;       // [M, nkv * HD]
+  __nv_bfloat16* gqkv;           // [M, (nq + 2 nkv) * HD]
+  float* gq_w;                   // [HD] fp32, added to
+  float* gk_w;
+  const int* pos;
+  int M, nq, nkv;
+  float eps, log2_theta;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) qk_norm_rope_bwd_kernel(const QkRopeBwdParams p) {
+  constexpr int EPL = HD / 32;
+  __shared__ float s_gw[2][HD];
+  for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x) (&s_gw[0][0])[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int heads = p.nq + 2 * p.nkv;
+  const long long total = (long long)p.M * heads;
+  const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+  float gw_q[EPL], gw_k[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) { gw_q[i] = 0.f; gw_k[i] = 0.f; }
+  for (long long wg = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wg < total; wg += stride) {
+    const int t = (int)(wg / heads);
+    const int h = (int)(wg % heads);
+    const bool is_q = h < p.nq;
+    const bool is_k = !is_q && h < p.nq + p.nkv;
+    __nv_bfloat16* dst = p.gqkv + ((size_t)t * heads + h) * HD + lane * EPL;
+    if (!is_q && !is_k) {
+      const __nv_bfloat16* g = p.gv + ((size_t)t * p.nkv + (h - p.nq - p.nkv)) * HD + lane * EPL;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) dst[i] = g[i];
+      continue;
+    }
+    const __nv_bfloat16* src = p.qkv + ((size_t)t * heads + h) * HD + lane * EPL;
+    const __nv_bfloat16* g = is_q ? p.gq + ((size_t)t * p.nq + h) * HD + lane * EPL
+                                  : p.gk + ((size_t)t * p.nkv + (h - p.nq)) * HD + lane * EPL;
+    const __nv_bfloat16* w = (is_q ? p.q_w : p.k_w) + lane * EPL;
+    float x[EPL], gy[EPL], wv[EPL], gpart[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      x[i] = __bfloat162float(src[i]);
+      gy[i] = __bfloat162float(g[i]);
+      wv[i] = __bfloat162float(w[i]);
+      ss += x[i] * x[i];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)HD + p.eps);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) gpart[i] = __shfl_xor_sync(0xffffffffu, gy[i], 16);
+    const float posf = (float)p.pos[t];
+    const bool upper = lane >= 16;
+    float gn[EPL], xn[EPL];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int d = lane * EPL + i;
+      const int j = upper ? d - HD / 2 : d;
+      const float inv = exp2f(-(2.0f * (float)j / (float)HD) * p.log2_theta);
+      const float ang = posf * inv;
+      const float c = bf16_round(cosf(ang)), sn = bf16_round(sinf(ang));
+      gn[i] = gy[i] * c + (upper ? -gpart[i] : gpart[i]) * sn;
+      xn[i] = x[i] * rstd;
+      dot += gn[i] * wv[i] * xn[i];
+    }
+    dot = warp_sum(dot) / (float)HD;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      dst[i] = __float2bfloat16_rn(rstd * (gn[i] * wv[i] - xn[i] * dot));
+      if (is_q) gw_q[i] += gn[i] * xn[i];
+      else gw_k[i] += gn[i] * xn[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    atomicAdd(&s_gw[0][lane * EPL + i], gw_q[i]);
+    atomicAdd(&s_gw[1][lane * EPL + i], gw_k[i]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+    if (p.gq_w != nullptr) atomicAdd(p.gq_w + i, s_gw[0][i]);
+    if (p.gk_w != nullptr) atomicAdd(p.gk_w + i, s_gw[1][i]);
+  }
+}
+
 }  // namespace tahb
 
 using namespace tahb;
+
+// Backward of tahb_qk_norm_rope_kv for contiguous tensors.  gq_w / gk_w: fp32 [hd] the kernel adds into.
+extern "C" int tahb_qk_norm_rope_bwd(const void* qkv, const void* q_w, const void* k_w, const void* gq, const void* gk,
+                                     const void* gv, void* gqkv, float* gq_w, float* gk_w, const int* pos, int M,
+                                     int nq, int nkv, int hd, float eps, float theta, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  QkRopeBwdParams p;
+  p.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
+  p.q_w = reinterpret_cast<const __nv_bfloat16*>(q_w);
+  p.k_w = reinterpret_cast<const __nv_bfloat16*>(k_w);
+  p.gq = reinterpret_cast<const __nv_bfloat16*>(gq);
+  p.gk = reinterpret_cast<const __nv_bfloat16*>(gk);
+  p.gv = reinterpret_cast<const __nv_bfloat16*>(gv);
+  p.gqkv = reinterpret_cast<__nv_bfloat16*>(gqkv);
+  p.gq_w = gq_w;
+  p.gk_w = gk_w;
+  p.pos = pos;
+  p.M = M; p.nq = nq; p.nkv = nkv;
+  p.eps = eps;
+  p.log2_theta = log2f(theta);
+  const long long warps = (long long)M * (nq + 2 * nkv);
+  long long blocks = (warps + 3) / 4;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (hd == 128) qk_norm_rope_bwd_kernel<128><<<(int)blocks, 128, 0, stream>>>(p);
+  else if (hd == 64) qk_norm_rope_bwd_kernel<64><<<(int)blocks, 128, 0, stream>>>(p);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 // x, gy, gx: [M, H] bf16 contiguous; w [H] bf16; gw: fp32 [H] that the kernel ADDS into (or null).
 extern "C" int tahb_rmsnorm_bwd(const void* x, const void* w, const void* gy, void* gx, float* gw, int M, int H,

@@ -253,11 +253,16 @@ class Attention(nn.Module):
         self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, **kw)
         self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, **kw)
 
-    def project_qkv(self, x, cos, sin, lora_on: bool):
-        """Fused QKV projection, per-head QK-norm and RoPE: returns q, k, v as ``[B,T,heads,hd]``."""
+    def project_qkv(self, x, cos, sin, lora_on: bool, pos=None):
+        """Fused QKV projection, per-head QK-norm and RoPE: returns q, k, v as ``[B,T,heads,hd]``.
+        With ``pos`` (the integer position ids the tables were built from) a bf16 CUDA pass runs the
+        norm + rotation as one kernel forward and one backward."""
         cfg = self.cfg
         B, T, _ = x.shape
         qkv = self.qkv_proj(x, lora_on)
+        if pos is not None and ops.fused_qk_norm_rope_ok(qkv, cfg.head_dim):
+            return ops.qk_norm_rope(qkv, self.q_norm.weight, self.k_norm.weight, pos, cfg.num_attention_heads,
+                                    cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps, cfg.rope_theta)
         q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
         q = self.q_norm(q.view(B, T, cfg.num_attention_heads, cfg.head_dim))
         k = self.k_norm(k.view(B, T, cfg.num_key_value_heads, cfg.head_dim))
@@ -292,24 +297,24 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **kw)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **kw)
 
-    def _pre_attention(self, h, cos, sin, lora_on: bool):
-        return self.self_attn.project_qkv(self.input_layernorm(h), cos, sin, lora_on)
+    def _pre_attention(self, h, cos, sin, lora_on: bool, pos=None):
+        return self.self_attn.project_qkv(self.input_layernorm(h), cos, sin, lora_on, pos)
 
     def _post_attention(self, h, o, lora_on: bool):
         h = h + self.self_attn.o_proj(o, lora_on)
         return h + self.mlp(self.post_attention_layernorm(h), lora_on)
 
-    def forward(self, h, cos, sin, kv, lora_on: bool, checkpoint: bool = False):
+    def forward(self, h, cos, sin, kv, lora_on: bool, checkpoint: bool = False, pos=None):
         """With ``checkpoint`` the two dense stages are recomputed in backward while the
         attention itself (and the K/V handed to the cache) stays in the autograd graph,
         so later passes can still back-propagate into this pass's K/V."""
         B, T, _ = h.shape
         if checkpoint:
             from torch.utils.checkpoint import checkpoint as ckpt
-            q, k, v = ckpt(self._pre_attention, h, cos, sin, lora_on, use_reentrant=False)
+            q, k, v = ckpt(self._pre_attention, h, cos, sin, lora_on, pos, use_reentrant=False)
             o = kv.attend(self.self_attn.layer_idx, q, k, v).reshape(B, T, -1)
             return ckpt(self._post_attention, h, o, lora_on, use_reentrant=False)
-        q, k, v = self._pre_attention(h, cos, sin, lora_on)
+        q, k, v = self._pre_attention(h, cos, sin, lora_on, pos)
         o = kv.attend(self.self_attn.layer_idx, q, k, v).reshape(B, T, -1)
         return self._post_attention(h, o, lora_on)
 
@@ -406,7 +411,7 @@ class Qwen3ForCausalLM(nn.Module):
             if i in want:
                 taps[i] = h
             ck = self.gradient_checkpointing and self.training and torch.is_grad_enabled()
-            h = layer(h, cos, sin, kv, lora_on, checkpoint=ck)
+            h = layer(h, cos, sin, kv, lora_on, checkpoint=ck, pos=position_ids)
         h = self.model.norm(h)
         if cfg.num_hidden_layers in want:
             taps[cfg.num_hidden_layers] = h

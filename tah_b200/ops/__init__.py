@@ -48,6 +48,20 @@ def swiglu(gate_up):
     return torch_ref.swiglu(gate_up)
 
 
+def fused_qk_norm_rope_ok(qkv, head_dim: int) -> bool:
+    if not _use_cuda(qkv):
+        return False
+    from tah_b200.ops import autograd_ops
+    return autograd_ops.qk_norm_rope_ok(qkv, head_dim)
+
+
+def qk_norm_rope(qkv, q_w, k_w, position_ids, nq, nkv, hd, eps, theta):
+    """Per-head RMSNorm of q and k + rotate-half RoPE of a fused qkv projection (CUDA bf16 only; callers
+    check :func:`fused_qk_norm_rope_ok` and otherwise use the module-level PyTorch statement)."""
+    from tah_b200.ops import autograd_ops
+    return autograd_ops.qk_norm_rope(qkv, q_w, k_w, position_ids, nq, nkv, hd, eps, theta)
+
+
 def topk_softmax_embed(logits, embedding_weight, topk: int):
     if _use_cuda(logits):
         from tah_b200.ops import autograd_ops

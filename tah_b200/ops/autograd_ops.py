@@ -94,6 +94,39 @@ def rms_norm(x, weight, eps):
     return torch_ref.rms_norm(x, weight, eps)
 
 
+class _QKNormRope(torch.autograd.Function):
+    """Per-head QK RMSNorm + rotate-half RoPE of a fused ``[B, T, (nq + 2 nkv) * hd]`` projection."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_w, k_w, pos, nq, nkv, hd, eps, theta):
+        B, T, _ = qkv.shape
+        x2 = qkv.reshape(B * T, -1).contiguous()
+        p32 = pos.reshape(-1).to(torch.int32).contiguous()
+        k = torch.empty(B * T, nkv * hd, dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty_like(k)
+        q = K.qk_norm_rope_kv(x2, q_w, k_w, p32, nq, nkv, hd, eps, theta, k_dense=k, v_dense=v)
+        ctx.save_for_backward(x2, q_w, k_w, p32)
+        ctx.dims = (B, T, nq, nkv, hd, eps, theta)
+        return q.view(B, T, nq, hd), k.view(B, T, nkv, hd), v.view(B, T, nkv, hd)
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        x2, q_w, k_w, p32 = ctx.saved_tensors
+        B, T, nq, nkv, hd, eps, theta = ctx.dims
+        gqkv, gqw, gkw = K.qk_norm_rope_bwd(x2, q_w, k_w, gq.reshape(B * T, -1).contiguous(),
+                                            gk.reshape(B * T, -1).contiguous(), gv.reshape(B * T, -1).contiguous(),
+                                            p32, nq, nkv, hd, eps, theta)
+        return gqkv.view(B, T, -1), gqw.to(q_w.dtype), gkw.to(k_w.dtype), None, None, None, None, None, None
+
+
+def qk_norm_rope_ok(qkv: torch.Tensor, hd: int) -> bool:
+    return qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd in (64, 128) and qkv.dim() == 3 and qkv.numel() > 0
+
+
+def qk_norm_rope(qkv, q_w, k_w, position_ids, nq, nkv, hd, eps, theta):
+    return _QKNormRope.apply(qkv, q_w, k_w, position_ids, nq, nkv, hd, eps, theta)
+
+
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gate_up):

@@ -257,6 +257,18 @@ def swiglu_bwd(gate_up: torch.Tensor, gy: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def qk_norm_rope_bwd(qkv, q_w, k_w, gq, gk, gv, pos, nq: int, nkv: int, hd: int, eps: float, theta: float):
+    """Backward of :func:`qk_norm_rope_kv` (dense outputs): returns ``(gqkv, gq_w_fp32, gk_w_fp32)``."""
+    M = qkv.shape[0]
+    gqkv = torch.empty_like(qkv)
+    gqw = torch.zeros(hd, dtype=torch.float32, device=qkv.device)
+    gkw = torch.zeros(hd, dtype=torch.float32, device=qkv.device)
+    _rc(lib().tahb_qk_norm_rope_bwd(_p(qkv), _p(q_w), _p(k_w), _p(gq), _p(gk), _p(gv), _p(gqkv), _p(gqw), _p(gkw),
+                                    _p(pos), c_int(M), c_int(nq), c_int(nkv), c_int(hd), c_float(eps), c_float(theta),
+                                    _stream()), "tahb_qk_norm_rope_bwd")
+    return gqkv, gqw, gkw
+
+
 def embed_gather(E, tok, out=None):
     M, H = tok.shape[0], E.shape[1]
     if out is None:

@@ -411,6 +411,35 @@ def test_rmsnorm_and_swiglu_backward_kernels():
     _close(Kc.swiglu_bwd(gu, gy2), guf.grad, atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_qk_norm_rope_forward_backward(hd):
+    """Fused QK-norm + RoPE autograd function against the module-level PyTorch statement in fp32."""
+    from tah_b200.ops import autograd_ops
+    from tah_b200.models.qwen3 import apply_rope, rope_cos_sin
+    B, T, nq, nkv = 2, 37, 4, 2
+    qkv = _rand(B, T, (nq + 2 * nkv) * hd, seed=1).requires_grad_(True)
+    qw = (_rand(hd, seed=2) * 0.1 + 1).to(torch.bfloat16).requires_grad_(True)
+    kw = (_rand(hd, seed=3) * 0.1 + 1).to(torch.bfloat16).requires_grad_(True)
+    pos = torch.arange(T, device="cuda")[None].repeat(B, 1) + torch.tensor([[0], [5]], device="cuda")
+    q, k, v = autograd_ops.qk_norm_rope(qkv, qw, kw, pos, nq, nkv, hd, 1e-6, 1e6)
+    gq, gk, gv = _rand(B, T, nq, hd, seed=4), _rand(B, T, nkv, hd, seed=5), _rand(B, T, nkv, hd, seed=6)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    x = qkv.detach().float().requires_grad_(True)
+    qwf, kwf = qw.detach().float().requires_grad_(True), kw.detach().float().requires_grad_(True)
+    cos, sin = rope_cos_sin(pos, hd, 1e6, torch.float32)
+    xq, xk, xv = x.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
+    norm = lambda t, w: w * (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6))
+    rq = apply_rope(norm(xq.view(B, T, nq, hd), qwf), cos, sin)
+    rk = apply_rope(norm(xk.view(B, T, nkv, hd), kwf), cos, sin)
+    rv = xv.reshape(B, T, nkv, hd)
+    torch.autograd.backward([rq, rk, rv], [gq.float(), gk.float(), gv.float()])
+    _close(q, rq, atol=3e-2, rtol=3e-2)
+    _close(k, rk, atol=3e-2, rtol=3e-2)
+    _close(qkv.grad, x.grad, atol=4e-2, rtol=4e-2)
+    _close(qw.grad, qwf.grad, atol=0.3, rtol=5e-2)
+    _close(kw.grad, kwf.grad, atol=0.3, rtol=5e-2)
+
+
 def test_sampler_topk_distribution():
     Kc = _cuda()
     rows, K = 4096, 8
