@@ -168,7 +168,9 @@ def duo_attention(q, k, v, q_pos, kv_pos, kv_valid, q_depth=None, kv_depth=None)
 # Duo-causal attention over per-depth KV segments on the tensor-core kernels (forward + backward)
 # ---------------------------------------------------------------------------------------------
 class SegmentMeta:
-    """Index arrays that the packed attention kernels take, built once per backbone pass.
+    """Index arrays that the packed attention kernels take, built once per backbone pass (the
+    counterpart of the reference's per-pass mask construction, ``tah/model/tah_model.py:744-791``,
+    with the KV order ``[iter-0 slot | iter-1 slot | ...]`` of ``tah/model/causal_cache.py:97-109``).
 
     Queries are the ``[B, Tq]`` tokens of the pass (row ``b * Tq + i``); segment ``s`` is the
     ``[B, Ts]`` K/V of iteration depth ``s``.  A query sees, in every segment, the valid entries of

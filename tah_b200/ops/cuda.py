@@ -361,7 +361,10 @@ def attn_tiles(seq_counts: torch.Tensor, tile: int = 128):
 
 
 def prefill_attn(q, ks, vs, bases, counts, tile_q0, tile_qn, nq, nkv, hd, scale, out=None, lse=None, bounds=None):
-    """Packed duo-causal attention on the tensor cores (``csrc/attn_prefill.cu``).  Same contract as
+    """Packed duo-causal attention on the tensor cores (``csrc/attn_prefill.cu``).  The reference builds a
+    dense additive mask ``(kv_pos <= q_pos) & (kv_iter <= q_iter) & kv_valid`` per pass (reference
+    ``tah/model/tah_model.py:744-791``) and hands it to SDPA; here the same rule is the per-query prefix
+    ``bases[s] .. bases[s] + counts[s]`` of every depth's K/V and no mask tensor exists.  Same contract as
     :func:`varlen_attn_naive` plus the query tiling of :func:`attn_tiles`: the tokens of a tile belong
     to one sequence and share ``bases[s]``.  ``counts[s]`` must be non-decreasing along a sequence's rows, or
     ``bounds[s]`` must give such a non-decreasing upper bound (rows whose count was zeroed, e.g. padding).  ``lse`` (optional fp32
