@@ -10,8 +10,8 @@ sequences of ``--seq`` uniform-random token ids, one sequence per micro-batch an
 micro-batches per optimizer step on every rank, per-token hard labels Bernoulli(``--hard-rate``) (1.0 =
 every token takes the second iteration, the oracle-iteration mode) followed by the label decider,
 next-token cross entropy on the iteration-selected logits (plus the decider BCE with ``--decider mlp``),
-bf16 parameters with fp32 master weights in the sharded AdamW (lr 2e-5, weight decay 0.01), gradient
-checkpointing per decoder stage.  One step = forward + backward of ``accum`` micro-batches + the
+bf16 parameters with fp32 master weights in the sharded AdamW (lr 2e-5, weight decay 0.01); ``--checkpoint``
+turns on gradient checkpointing per decoder stage (the 1.7B model at 8192 tokens fits without it).  One step = forward + backward of ``accum`` micro-batches + the
 optimizer step (gradient reduce-scatter, AdamW, parameter broadcast).  Time is CUDA-event time of
 ``--steps`` steps after ``--warmup``, maximum over ranks; prints one JSON line on rank 0.
 """
@@ -37,6 +37,8 @@ def main():
     ap.add_argument("--model", default="tah-plus-1.7b")
     ap.add_argument("--decider", default="label", choices=["label", "mlp"])
     ap.add_argument("--lora-rank", type=int, default=64)
+    ap.add_argument("--checkpoint", action="store_true",
+                    help="recompute the dense stages of every layer in backward (needed for longer sequences / larger models)")
     a = ap.parse_args()
 
     import torch
@@ -72,7 +74,8 @@ def main():
     model = TaHForCausalLM(base, tcfg).to(dev)
     model.iter_decider.to(device=dev, dtype=torch.bfloat16)
     model.train()
-    model.gradient_checkpointing_enable()
+    if a.checkpoint:
+        model.gradient_checkpointing_enable()
     opt = ZeroAdamW(model.parameters(), lr=2e-5, weight_decay=0.01, max_grad_norm=1.0)
 
     g = torch.Generator().manual_seed(100 + rank)
@@ -120,7 +123,7 @@ def main():
             "data": "synthetic", "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
             "config": {"model": a.model, "seq_len": a.seq, "micro_batches_per_step": a.accum, "global_batch": a.accum * world,
                        "hard_rate": a.hard_rate, "decider": a.decider, "lora_rank": a.lora_rank, "max_iter": 2,
-                       "parallelism": f"dp{world} + sharded AdamW", "grad_checkpointing": True}}))
+                       "parallelism": f"dp{world} + sharded AdamW", "grad_checkpointing": bool(a.checkpoint)}}))
     if world > 1:
         dist.barrier()
         sys.stdout.flush()
