@@ -45,6 +45,9 @@ struct GemmParams {
   int kb_ext;   // R / 64
   int splits;   // cluster size along z (1 = no split-K)
   int tma_out;  // 1: stage the output tile in shared memory and write it with a TMA store
+  int pair;     // DUAL kernels only. 0: SwiGLU of the two accumulators.  1: the accumulators are two plain
+                // output tiles (features f0.. and up_off + f0..) that share the CTA's activation tile, which
+                // halves the activation bytes a CTA pulls per unit of work (requires the staged/TMA output path)
   int* status;
   unsigned long long* trace;   // optional [n_ctas][8] globaltimer stamps (debug aid), else nullptr
   // Tensor-parallel reduce-scatter by push (row-parallel GEMMs): instead of writing `out`, the tile
@@ -56,6 +59,7 @@ struct GemmParams {
   int push_world;   // 0 = off
   int push_rank;
   int push_rpr;     // token rows per owner
+  int push_ld;      // row pitch of the slot buffers (the full hidden size)
   // Tensor-parallel all-gather wait (column-parallel GEMMs): X rows arrive from their owners by
   // peer stores; before the first X load the producer waits until flag[q] has reached target[q]
   // for every owner q.  Both arrays are local device memory.
@@ -117,7 +121,7 @@ __device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u,
 __device__ __forceinline__ void push_rows(const GemmParams& p, const __nv_bfloat16* stg, int ta, int n_tok, int f0) {
   const int e = threadIdx.x - 64;                 // 0..127
   const int sub = e & 15, r0 = e >> 4;            // 16-byte piece of the row, first row of this thread
-  const int H = p.F;
+  const int H = p.push_ld;
   for (int r = r0; r < n_tok; r += 8) {
     const int t = ta + r;
     if (t >= p.M) break;
@@ -252,11 +256,14 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 1] = globaltimer_ns();
     if (S == 1) {
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [BN tokens][128 features]
+      __nv_bfloat16* stg1 = stg + BN * 128;                            // second tile of a pair
+      const bool pair = DUAL && p.pair != 0;
       const bool res_tma = p.tma_out && p.residual != nullptr;
       if (res_tma) {
         if (threadIdx.x == 64) {
-          mbar_expect_tx(res_bar, BN * 256);
+          mbar_expect_tx(res_bar, BN * 256 * (pair ? 2 : 1));
           tma_load_2d(stg, &tm_res, f0, t0, res_bar);
+          if (pair) tma_load_2d(stg1, &tm_res, p.up_off + f0, t0, res_bar);
         }
         mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       }
@@ -267,7 +274,13 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tmem_ld_chunk<C::CHUNK>(trow + c0, a);
         if constexpr (DUAL) tmem_ld_chunk<C::CHUNK>(trow + BN + c0, u);
         tmem_ld_wait();
-        if (p.tma_out) {
+        if (pair) {
+#pragma unroll
+          for (int j = 0; j < C::CHUNK; ++j) {
+            stage_one<false>(stg + (c0 + j) * 128 + row, a[j], 0.f, res_tma);
+            stage_one<false>(stg1 + (c0 + j) * 128 + row, DUAL ? u[j] : 0.f, 0.f, res_tma);
+          }
+        } else if (p.tma_out) {
 #pragma unroll
           for (int j = 0; j < C::CHUNK; ++j)
             stage_one<DUAL>(stg + (c0 + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
@@ -282,11 +295,13 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       if (p.push_world > 0) {
         named_bar_sync(1, 128);
         push_rows(p, stg, t0, BN, f0);
+        if (pair) push_rows(p, stg1, t0, BN, p.up_off + f0);
       } else if (p.tma_out) {
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
           tma_store_2d(&tm_out, stg, f0, t0);
+          if (pair) tma_store_2d(&tm_out, stg1, p.up_off + f0, t0);
           tma_store_commit();
           tma_store_wait_read();
         }
@@ -346,11 +361,14 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const float* red = reinterpret_cast<const float*>(smem);
       // output staging tile [per tokens][128 features] lives behind the received blocks
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + split_stage_offset(S, C::NACC * per));
+      __nv_bfloat16* stg1 = stg + per * 128;
+      const bool pair = DUAL && p.pair != 0;
       const bool res_tma = p.tma_out && p.residual != nullptr;
       if (res_tma) {
         if (threadIdx.x == 64) {
-          mbar_expect_tx(res_bar, per * 256);
+          mbar_expect_tx(res_bar, per * 256 * (pair ? 2 : 1));
           tma_load_2d(stg, &tm_res, f0, t0 + rank * per, res_bar);
+          if (pair) tma_load_2d(stg1, &tm_res, p.up_off + f0, t0 + rank * per, res_bar);
         }
         mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       }
@@ -371,7 +389,13 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             for (int j = 0; j < 16; ++j) u[j] += src[(per + j) * 128];
           }
         }
-        if (p.tma_out) {
+        if (pair) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            stage_one<false>(stg + (c + j) * 128 + row, a[j], 0.f, res_tma);
+            stage_one<false>(stg1 + (c + j) * 128 + row, DUAL ? u[j] : 0.f, 0.f, res_tma);
+          }
+        } else if (p.tma_out) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) stage_one<DUAL>(stg + (c + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
         } else if (f < p.F) {
@@ -385,11 +409,13 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       if (p.push_world > 0) {
         named_bar_sync(1, 128);
         push_rows(p, stg, t0 + rank * per, per, f0);
+        if (pair) push_rows(p, stg1, t0 + rank * per, per, p.up_off + f0);
       } else if (p.tma_out) {
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
           tma_store_2d(&tm_out, stg, f0, t0 + rank * per);
+          if (pair) tma_store_2d(&tm_out, stg1, p.up_off + f0, t0 + rank * per);
           tma_store_commit();
           tma_store_wait_read();
         }
@@ -458,7 +484,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
   }
   if (p.splits > 1) {
     const int per = BN / p.splits;
-    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 >
+    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 * (p.pair ? 2 : 1) >
                         (size_t)C::NS * C::STAGE_BYTES)
       return -11;
   }
@@ -509,7 +535,17 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
                      int* status, cudaStream_t stream, const GemmTpArgs& tp) {
   if (M <= 0 || F <= 0) return 0;
   const bool push = tp.push_world > 0;
-  if (push && (dual || residual != nullptr || F % 128 || tp.push_world > GEMM_MAX_RANKS || tp.push_rpr <= 0)) return -23;
+  // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 2 = pair: two plain
+  // output tiles per CTA (features f and F/2 + f) sharing the activation tile
+  const bool pair = dual == 2;
+  const int F_full = F;
+  if (pair) {
+    if (F % 256) return -24;
+    F = F / 2;
+    up_off = F;
+  }
+  if (push && (dual == 1 || residual != nullptr || F_full % 128 || tp.push_world > GEMM_MAX_RANKS || tp.push_rpr <= 0))
+    return -23;
   if (K % 64 || R % 64 || K <= 0) return -20;
   if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   if (splits < 1) splits = 1;
@@ -529,12 +565,15 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   }
   // output (and residual) through TMA when their layout allows it, else element-wise stores
   CUtensorMap mo, mr;
-  int tma_out = !push && make_map(&mo, out, M, F, ldo, bn / splits, false) == 0;
-  if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F, ldr, bn / splits, false) == 0;
+  int tma_out = !push && make_map(&mo, out, M, F_full, ldo, bn / splits, false) == 0;
+  if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F_full, ldr, bn / splits, false) == 0;
+  if (pair && !tma_out && !push) return -25;     // the pair epilogue only exists on the staged path
   if (!tma_out) mo = mw;
   if (!tma_out || residual == nullptr) mr = mo;
   GemmParams p;
   p.tma_out = tma_out || push;          // push mode stages the tile in shared memory as well
+  p.pair = pair ? 1 : 0;
+  p.push_ld = F_full;
   p.push_world = tp.push_world;
   p.push_rank = tp.push_rank;
   p.push_rpr = tp.push_rpr;

@@ -96,7 +96,7 @@ def _check_bf16_2d(t: torch.Tensor, name: str):
 SM_COUNT = 148
 
 
-def _fits(bn: int, s: int, nacc: int) -> bool:
+def _fits(bn: int, s: int, nacc: int, pair: bool = False) -> bool:
     stage = 16384 * nacc + bn * 128
     ns = min(8, (196 * 1024) // stage)
     if s == 1:
@@ -105,10 +105,10 @@ def _fits(bn: int, s: int, nacc: int) -> bool:
     if bn % s or per % 16:
         return False
     red = ((s - 1) * 128 * nacc * per * 4 + 1023) // 1024 * 1024
-    return red + per * 256 <= ns * stage
+    return red + per * 256 * (2 if pair else 1) <= ns * stage
 
 
-def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
+def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False, pair: bool = False):
     """Pick the token-tile width and the split-K cluster size with a small cost model.
 
     Measured on B200: a k-block (64 of K) costs about 0.3 us of load latency per CTA unless the
@@ -122,7 +122,7 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
     best = None
     for bn in cands:
         for s in (1, 2, 4):
-            if s > 1 and (kb // s < 2 or not _fits(bn, s, nacc)):
+            if s > 1 and (kb // s < 2 or not _fits(bn, s, nacc, pair)):
                 continue
             ctas = ((F + 127) // 128) * ((M + bn - 1) // bn) * s
             waves = (ctas + SM_COUNT - 1) // SM_COUNT
@@ -138,6 +138,9 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
     return best[1], best[2]
 
 
+PAIR_AUTO = os.environ.get("TAH_B200_GEMM_PAIR", "1") != "0"
+
+
 def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
     return plan_gemm(M, F, K, R, dual)[1]
 
@@ -145,9 +148,13 @@ def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
-         bn: int = 0, tp_push=None, tp_wait=None) -> torch.Tensor:
+         bn: int = 0, tp_push=None, tp_wait=None, pair: Optional[bool] = None) -> torch.Tensor:
     """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
     weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
+
+    ``pair``: every CTA computes two 128-feature output tiles (features ``f`` and ``F/2 + f``) from one
+    activation tile, which cuts the activation bytes pulled per output; chosen automatically for decode-sized
+    ``M`` when ``None``.
 
     Tensor parallel (see :class:`tah_b200.parallel.tp.TensorParallel`): ``tp_push =
     (slot_ptrs, cnt_ptrs, rank, rows_per_rank)`` replaces the output by peer stores of the tile
@@ -174,15 +181,18 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         _check_bf16_2d(out, "out")
     if residual is not None:
         _check_bf16_2d(residual, "residual")
+    if pair is None:
+        pair = PAIR_AUTO and not swiglu and M <= 256 and F % 256 == 0 and F >= 1024 and F <= 16384
+    pair = bool(pair) and not swiglu and F % 256 == 0
     if splits is None and bn == 0:
-        bn, splits = plan_gemm(M, F, K, R, swiglu)
+        bn, splits = plan_gemm(M, F // 2, K, R, True, pair=True) if pair else plan_gemm(M, F, K, R, swiglu)
     elif splits is None:
         splits = 1
     args = (_p(w), _p(x), _p(out), _p(residual), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R),
             c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
             c_ll(residual.stride(0) if residual is not None else 0),
             c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
-            c_int(1 if swiglu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+            c_int(1 if swiglu else 2 if pair else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
             _p(status_word(x.device)), _stream())
     if tp_push is None and tp_wait is None:
         rc = lib().tahb_gemm(*args)
