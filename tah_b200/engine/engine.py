@@ -320,6 +320,13 @@ class TaHEngine:
         s.tokens_done = torch.zeros(1, dtype=torch.int64, device=dev)
         s.need_soft, s.best, s.sampled = i32(B), i32(B), i32(B)
         s.best_val = torch.zeros(B, dtype=torch.float32, device=dev)
+        # split the KV walk of a row when (rows x local KV heads) CTAs would leave SM slots empty
+        # (small batches, wide tensor-parallel groups); the partial results meet in a merge kernel
+        s.attn_split = max(1, min(4, (148 * 4) // max(1, B * w.nkv)))
+        s.attn_ws = None
+        if s.attn_split > 1:
+            n_ws = int(K.lib().tahb_decode_attn_ws_floats(B, w.nq, cfg.head_dim, s.attn_split))
+            s.attn_ws = torch.empty(n_ws, dtype=torch.float32, device=dev)
         s.samp_v = torch.zeros(B, 128, dtype=torch.float32, device=dev)
         s.samp_i = i32(B, 128)
         s.x_in, s.soft, s.h, s.xn = bf(B, H), bf(B, H), bf(B, H), bf(B, H)
@@ -398,7 +405,8 @@ class TaHEngine:
                 K.gemm(xn, L.w_qkv, out=s.qkv, tp_wait=self._xn_wait)
             K.qk_norm_rope_kv(s.qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
                               q_out=s.q, caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size)
-            K.decode_attn(s.q, pools[li], kv.page_table, kv.len, s.depth, nq, nkv, hd, self.page_size, scale, out=s.o)
+            K.decode_attn(s.q, pools[li], kv.page_table, kv.len, s.depth, nq, nkv, hd, self.page_size, scale, out=s.o,
+                          n_split=s.attn_split, ws=s.attn_ws)
             xn = self._row_parallel(s.o, L.w_o, L.a_o if lora else None, L.b_o, s.t_o, s.gate, s.h, L.ln2, s.xn, B,
                                     push=push)
             if lora:
