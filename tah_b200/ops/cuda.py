@@ -138,7 +138,9 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False, pair: bool
     return best[1], best[2]
 
 
-PAIR_AUTO = os.environ.get("TAH_B200_GEMM_PAIR", "1") != "0"
+# measured on B200 at 256 rows: pairing halves the CTA count and loses more than the saved activation
+# traffic gains (e.g. 4096x2048: 14.1 us paired vs 12.1 us), so it is opt-in
+PAIR_AUTO = os.environ.get("TAH_B200_GEMM_PAIR", "0") == "1"
 
 
 def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
@@ -153,8 +155,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
 
     ``pair``: every CTA computes two 128-feature output tiles (features ``f`` and ``F/2 + f``) from one
-    activation tile, which cuts the activation bytes pulled per output; chosen automatically for decode-sized
-    ``M`` when ``None``.
+    activation tile, which cuts the activation bytes pulled per output (off unless asked for: it was not
+    faster at decode sizes on B200).
 
     Tensor parallel (see :class:`tah_b200.parallel.tp.TensorParallel`): ``tp_push =
     (slot_ptrs, cnt_ptrs, rank, rows_per_rank)`` replaces the output by peer stores of the tile
