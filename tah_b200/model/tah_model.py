@@ -78,15 +78,24 @@ class ActiveSet:
     def n(self) -> int:
         return self.b.numel()
 
+    @property
+    def full(self) -> bool:
+        """Every slot of the ``(B, width)`` block is active: the block is the active list reshaped."""
+        return self.width > 0 and self.n == self.mask.shape[0] * self.width
+
     def pack(self, dense: Optional[torch.Tensor], pad_value=0):
         if dense is None:
             return None
+        if self.full and self.width == dense.shape[1]:
+            return dense                      # every token active: the block is the tensor itself
         out = dense.new_full((dense.shape[0], self.width) + tuple(dense.shape[2:]), pad_value)
         out[self.b, self.k] = dense[self.b, self.s]
         return out
 
     def pack_flat(self, values: torch.Tensor, pad_value=0):
         """``values`` ``(n, ...)`` in active order -> padded ``(B, width, ...)`` block."""
+        if self.full:
+            return values.view(self.mask.shape[0], self.width, *values.shape[1:])
         out = values.new_full((self.mask.shape[0], self.width) + tuple(values.shape[1:]), pad_value)
         out[self.b, self.k] = values
         return out
@@ -297,6 +306,7 @@ class TaHForCausalLM(nn.Module):
         taps: Sequence[int] = tuple(getattr(decider, "hidden_states_layer_nums", ()) or ())
         wants_all_layers = bool(getattr(decider, "needs_all_hidden_states", False))
 
+        all_valid = bool(valid_mask.all())            # no padding anywhere: validity gathers are identities
         current = torch.ones(B, T, dtype=torch.bool, device=device)
         act = ActiveSet(current)
         block_embeds = input_embeds                       # (B, width, H) input of the pass
@@ -319,29 +329,35 @@ class TaHForCausalLM(nn.Module):
             pass_logits = base.logits(hidden)              # (B, width, V)
             depth += 1
 
-            flat_logits = pass_logits[act.b, act.k]        # (n, V), active order
+            # (n, V) in active order; with every slot active this is a view, not a gather of the logits
+            flat_logits = pass_logits.reshape(-1, V) if act.full else pass_logits[act.b, act.k]
             updated = additive_logits_update(flat_logits, carried)
 
             v_act = a_valid[act.b, act.k] == 1             # (n,) validity of the active tokens
+            pick = (lambda t: t) if all_valid else (lambda t: t[v_act])
             dec_kwargs = {}
             if wants_all_layers:
                 stack = torch.stack([tapped[i] for i in range(self.config.num_hidden_layers + 1)], dim=2)
-                dec_kwargs["all_hidden_states"] = stack[act.b, act.k][v_act]
+                dec_kwargs["all_hidden_states"] = pick(stack[act.b, act.k])
             elif taps:
-                dec_kwargs["tapped_hidden_states"] = torch.cat([tapped[i] for i in taps], dim=-1)[act.b, act.k][v_act]
+                dec_kwargs["tapped_hidden_states"] = pick(torch.cat([tapped[i] for i in taps], dim=-1)[act.b, act.k])
             decision, continue_logits = decider(
-                logits=updated[v_act], iter_depth=depth,
-                labels_shifted=None if a_labels_all is None else a_labels_all[act.b, act.k][v_act],
-                iter_count_labels=None if a_iter_labels is None else a_iter_labels[act.b, act.k][v_act],
+                logits=pick(updated), iter_depth=depth,
+                labels_shifted=None if a_labels_all is None else pick(a_labels_all[act.b, act.k]),
+                iter_count_labels=None if a_iter_labels is None else pick(a_iter_labels[act.b, act.k]),
                 **dec_kwargs)
             if self.training or labels is not None:
                 decision = self._force_one_continuation(
-                    decision, None if a_labels is None else a_labels[act.b, act.k][v_act], depth)
+                    decision, None if a_labels is None else pick(a_labels[act.b, act.k]), depth)
 
             # finished = invalid tokens, plus valid ones the decider stopped
-            go = torch.zeros(act.n, dtype=torch.bool, device=device)
-            go[v_act] = decision
+            if all_valid:
+                go = decision
+            else:
+                go = torch.zeros(act.n, dtype=torch.bool, device=device)
+                go[v_act] = decision
             finished = ~go
+            n_go = int(go.sum())                           # one host sync; the next ActiveSet needs one anyway
             iter_counts[act.b, act.s] += 1
 
             if labels_shifted is not None and loss_func._is_intra_iter_loss:
@@ -351,7 +367,12 @@ class TaHForCausalLM(nn.Module):
                     active_iter_count_labels=None if a_iter_labels is None else a_iter_labels[act.b, act.k],
                     iter_decider_threshold=decider.threshold, model=self, **self._forward_kwargs(kwargs))
 
-            final_logits.index_put_((act.b[finished], act.s[finished]), updated[finished])
+            if n_go == 0 and act.full and act.width == T:
+                final_logits = updated.view(B, T, V)       # every token ends here: no scatter of the logits
+            elif n_go == 0:
+                final_logits.index_put_((act.b, act.s), updated)
+            elif n_go < act.n:
+                final_logits.index_put_((act.b[finished], act.s[finished]), updated[finished])
 
             if track_labels:
                 prop = a_iter_labels[act.b, act.k]
@@ -367,7 +388,7 @@ class TaHForCausalLM(nn.Module):
             nxt = ActiveSet(current)
             if nxt.n == 0 and not self.uniform_passes:
                 break
-            carried = updated[go]
+            carried = updated if n_go == act.n else updated[go]
             soft = topk_softmax_input_update(carried, embed_w, self.input_topk)
             block_embeds = nxt.pack_flat(soft)
             act = nxt

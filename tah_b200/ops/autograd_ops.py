@@ -48,8 +48,43 @@ def linear(x, w):
     return torch_ref.linear(x, w)
 
 
+class _LoRALinear(torch.autograd.Function):
+    """``x W^T + t Bd^T`` in one tcgen05 GEMM (the adapter is a K-extension of the base GEMM, as in the
+    inference engine); ``t = xa A^T`` and the block-diagonal scaled ``Bd`` are built by the caller."""
+
+    @staticmethod
+    def forward(ctx, x, w, t, bd):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        t2 = t.reshape(-1, t.shape[-1]).contiguous()
+        ctx.save_for_backward(x2, w, t2, bd)
+        ctx.shapes = (x.shape, t.shape)
+        out = K.gemm(x2, w if w.is_contiguous() else w.contiguous(), x2=t2, w2=bd)
+        return out.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w, t2, bd = ctx.saved_tensors
+        xs, ts = ctx.shapes
+        g2 = gy.reshape(-1, gy.shape[-1])
+        gx = (g2 @ w).view(xs) if ctx.needs_input_grad[0] else None
+        gw = g2.t() @ x2 if ctx.needs_input_grad[1] else None
+        gt = (g2 @ bd).view(ts) if ctx.needs_input_grad[2] else None
+        gbd = g2.t() @ t2 if ctx.needs_input_grad[3] else None
+        return gx, gw, gt, gbd
+
+
 def lora_linear(x, w, xa, lora_A, lora_B: List[torch.Tensor], adapted: Sequence[int], out_splits: Sequence[int],
                 r: int, scaling: float):
+    R = len(adapted) * r
+    if _gemm_ok(x, w) and R % 64 == 0 and lora_A.dtype == torch.bfloat16:
+        t = F.linear(xa, lora_A)
+        bd = w.new_zeros(w.shape[0], R)
+        off = [0]
+        for sz in out_splits:
+            off.append(off[-1] + sz)
+        for j, idx in enumerate(adapted):
+            bd[off[idx]:off[idx + 1], j * r:(j + 1) * r] = lora_B[j] * scaling
+        return _LoRALinear.apply(x, w, t, bd)
     y = linear(x, w)
     t = F.linear(xa, lora_A)
     pieces = list(y.split(list(out_splits), dim=-1))
