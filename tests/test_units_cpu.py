@@ -294,3 +294,15 @@ def test_segment_meta_matches_duo_mask_cpu():
             assert (bound[:, 1:] >= bound[:, :-1]).all() and (bound >= cnt).all()
         row0, nkeys, kidx0, qa, qb = meta.items[0]
         assert int(nkeys.sum()) == int(valid0.sum()) and torch.equal(qb - qa, torch.full_like(qa, width))
+
+
+def test_attention_tiling_helpers_cpu():
+    """Query tiles and key-block work items of the packed attention kernels (pure index arithmetic)."""
+    import torch
+    from tah_b200.ops.cuda import attn_kv_items, attn_tiles
+    q0, qn = attn_tiles(torch.tensor([300, 0, 128, 5]))
+    assert q0.tolist() == [0, 128, 256, 300, 428] and qn.tolist() == [128, 128, 44, 128, 5]
+    row0, nkeys, kidx0, qa, qb = attn_kv_items(torch.tensor([260, 3]), torch.tensor([10, 500]), torch.tensor([7, 9]))
+    assert row0.tolist() == [10, 138, 266, 500] and nkeys.tolist() == [128, 128, 4, 3]
+    assert kidx0.tolist() == [0, 128, 256, 0]
+    assert qa.tolist() == [0, 0, 0, 7] and qb.tolist() == [7, 7, 7, 16]
