@@ -414,6 +414,23 @@ __global__ void decide_kernel(const float* __restrict__ z, float threshold, cons
   need_soft[r] = (hard && d + 1 < max_iter) ? 1 : 0;
 }
 
+// Second half of the two-layer decider MLP: z[r] = bf16( sum_j bf16(silu(h[r, j])) * w2[j] + b2 ), where h
+// is the first layer's bf16 output (bias already added inside the GEMM accumulation).  One warp per row.
+__global__ void __launch_bounds__(128) decider_head_kernel(const __nv_bfloat16* __restrict__ h,
+                                                           const __nv_bfloat16* __restrict__ w2,
+                                                           const __nv_bfloat16* __restrict__ b2, float* __restrict__ z,
+                                                           int rows, int inner, long long ldh) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const __nv_bfloat16* hr = h + (size_t)r * ldh;
+  float acc = 0.f;
+  for (int j = lane; j < inner; j += 32)
+    acc += bf16_round(silu(__bfloat162float(hr[j]))) * __bfloat162float(w2[j]);
+  acc = warp_sum(acc);
+  if (lane == 0) z[r] = bf16_round(acc + (b2 != nullptr ? __bfloat162float(b2[0]) : 0.f));
+}
+
 // End of a tick: rows that iterate again go one level deeper; the others emit `next_tok`
 // (never the EOS itself), return to depth 0 and advance their position.
 __global__ void tick_end_kernel(const TickState s, const int* __restrict__ need_soft, const int* __restrict__ next_tok) {
@@ -525,6 +542,15 @@ extern "C" int tahb_decide(const float* z, float threshold, const signed char* o
   if (rows <= 0) return 0;
   decide_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(z, threshold, override_, override_ld, pos, depth, max_iter,
                                                         need_soft, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int tahb_decider_head(const void* h, const void* w2, const void* b2, float* z, int rows, int inner,
+                                 long long ldh, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  decider_head_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(h),
+                                                          reinterpret_cast<const __nv_bfloat16*>(w2),
+                                                          reinterpret_cast<const __nv_bfloat16*>(b2), z, rows, inner, ldh);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -94,8 +94,29 @@ class TaHEngine:
         if isinstance(inner, MLPIterDecider):
             return inner.score(taps, topk_vals.to(taps.dtype)).float()
         if isinstance(inner, SimpleMLPIterDecider):
-            return inner.score(taps).float()
+            return self._score_simple_mlp(inner, taps)
         return None
+
+    def _score_simple_mlp(self, dec: SimpleMLPIterDecider, taps: torch.Tensor) -> torch.Tensor:
+        """The two-layer decider as kernels: tcgen05 GEMM for the first layer (its bias enters the fp32
+        accumulation as a K-extension: a column of ones times the bias), then SiLU + dot + bias per row."""
+        w1 = dec.fc1.weight
+        if (taps.dtype != torch.bfloat16 or w1.dtype != torch.bfloat16 or not taps.is_cuda or taps.shape[-1] % 64
+                or w1.shape[0] % 8):
+            return dec.score(taps).float()
+        M = taps.shape[0]
+        cache = getattr(self, "_dec_cache", None)
+        if cache is None or cache[0] is not w1 or cache[1].shape[0] < M:
+            ones = torch.zeros(max(M, self.max_rows), 64, dtype=torch.bfloat16, device=taps.device)
+            ones[:, 0] = 1
+            bias_ext = torch.zeros(w1.shape[0], 64, dtype=torch.bfloat16, device=taps.device)
+            if dec.fc1.bias is not None:
+                bias_ext[:, 0] = dec.fc1.bias.detach()
+            cache = self._dec_cache = (w1, ones, bias_ext)
+        _, ones, bias_ext = cache
+        x = taps if taps.is_contiguous() else taps.contiguous()
+        h1 = K.gemm(x, w1.detach(), x2=ones[:M], w2=bias_ext)
+        return K.decider_head(h1, dec.fc2.weight.detach()[0].contiguous(), dec.fc2.bias.detach() if dec.fc2.bias is not None else None)
 
     def _needs_topk_for_decider(self) -> bool:
         return isinstance(self._decider()[1], MLPIterDecider)

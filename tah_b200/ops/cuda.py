@@ -484,6 +484,17 @@ def sample_topk(val, idx, temperature: float, top_p: float, min_p: float, seed: 
     return out
 
 
+def decider_head(h, w2, b2, out=None):
+    """``z[r] = bf16(sum_j bf16(silu(h[r, j])) * w2[j] + b2)`` as fp32: the output layer of the two-layer
+    decider MLP on the first layer's bf16 activations ``h`` (``[rows, inner]``)."""
+    rows, inner = h.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=h.device)
+    _rc(lib().tahb_decider_head(_p(h), _p(w2), _p(b2), _p(out), c_int(rows), c_int(inner), c_ll(h.stride(0)),
+                                _stream()), "tahb_decider_head")
+    return out
+
+
 def decide(z, threshold: float, override, pos, depth, max_iter: int, need_soft):
     rows = need_soft.shape[0]
     _rc(lib().tahb_decide(_p(z), c_float(threshold), _p(override), c_int(override.shape[1] if override is not None else 0),

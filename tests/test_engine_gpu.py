@@ -95,3 +95,27 @@ def test_sampling_runs_and_is_seeded():
     c = eng.generate(ids.cuda(), None, seed=8, **kw)
     assert a.tokens == b.tokens
     assert a.tokens != c.tokens
+
+
+def test_simple_mlp_decider_kernel_chain_matches_module():
+    """The decider's kernel chain (GEMM with the bias as a K-extension, then SiLU + dot per row) gives the
+    module's logits, and an engine driven by that decider (no override) iterates on some tokens."""
+    from tah_b200.engine import TaHEngine
+    H = 256
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16, decider="SimpleMLPIterDecider",
+                     decider_kwargs=dict(hidden_states_size=H, inner_size=64, threshold=0.5)).cuda().eval()
+    dec = model.iter_decider.cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        dec.fc1.bias.normal_(std=0.5)
+        dec.fc2.weight.normal_(std=0.5)
+    eng = TaHEngine(model, max_rows=8, max_seq_len=64, use_cuda_graph=True, deep_fraction=1.0)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    taps = (torch.randn(37, H, generator=g, device="cuda") * 1.5).to(torch.bfloat16)
+    z = eng._score_simple_mlp(dec, taps)
+    ref = dec.score(taps).float()
+    torch.testing.assert_close(z, ref, atol=2e-2, rtol=2e-2)
+    assert ((z > 0) == (ref > 0)).float().mean().item() > 0.97
+    ids = torch.randint(0, 1024, (4, 12), generator=torch.Generator().manual_seed(1)).cuda()
+    res = eng.generate(ids, None, max_new_tokens=12, do_sample=False)
+    assert all(len(t) == 12 for t in res.tokens)
+    assert 1.0 <= sum(res.iter_counts) / len(res.iter_counts) <= 2.0
