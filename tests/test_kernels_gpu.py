@@ -535,3 +535,32 @@ def test_training_step_on_gpu_matches_cpu_reference(pad):
     gb = ref.simple_base_model.model.layers[0].self_attn.qkv_proj.weight.grad
     cos = torch.nn.functional.cosine_similarity(ga.flatten(), gb.flatten(), dim=0)
     assert float(cos) > 0.98
+
+
+def test_training_step_kernel_path_matches_torch_path_multi_tile(monkeypatch):
+    """Same bf16 model, same batch (300 tokens, one left-padded sample, ~30 % hard tokens): loss and
+    gradients of the kernel path against the all-PyTorch path of this repository, both on the GPU."""
+    import copy
+    from tests.helpers import tiny_tah
+    model = tiny_tah(dtype=torch.bfloat16).cuda().train()
+    twin = copy.deepcopy(model)
+    g = torch.Generator().manual_seed(0)
+    B, T = 2, 300
+    ids = torch.randint(0, 1024, (B, T), generator=g).cuda()
+    hard = ((torch.rand(B, T, generator=g) < 0.3).long() + 1).cuda()
+    mask = torch.ones(B, T, dtype=torch.long, device="cuda")
+    labels = ids.clone()
+    mask[1, :77] = 0
+    labels[1, :77] = -100
+    out = model(ids, attention_mask=mask, labels=labels, iter_count_labels=hard)
+    out.loss.backward()
+    monkeypatch.setenv("TAH_B200_FORCE_TORCH", "1")
+    ref = twin(ids, attention_mask=mask, labels=labels, iter_count_labels=hard)
+    ref.loss.backward()
+    monkeypatch.delenv("TAH_B200_FORCE_TORCH")
+    assert abs(float(out.loss.detach()) - float(ref.loss.detach())) < 0.03
+    for name in ("layers.0.self_attn.qkv_proj.weight", "layers.3.mlp.down_proj.weight", "layers.1.self_attn.q_norm.weight"):
+        ga = dict(model.simple_base_model.model.named_parameters())[name].grad.float().flatten()
+        gb = dict(twin.simple_base_model.model.named_parameters())[name].grad.float().flatten()
+        cos = torch.nn.functional.cosine_similarity(ga, gb, dim=0)
+        assert float(cos) > 0.97, (name, float(cos))
