@@ -435,3 +435,138 @@ extern "C" int tahb_push_reduce_norm_bcast(const void* slot, void* cnt, void* cn
   else return -2;
   return e == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Sharded-parameter all-gather by push, consumed by the GEMM through landing flags.
+//
+// Every rank keeps 1/world of a weight matrix (a contiguous block of rows).  Ahead of the layer that
+// needs the matrix, each rank launches this kernel on a side stream: it copies its shard into the
+// gather buffer of EVERY rank (its own included) at its row offset - `multimem.st` when the buffer has
+// a multicast mapping, peer stores otherwise - fences, and advances landed[peer][this rank] by one per
+// CTA.  The consuming GEMM (tahb_gemm_tp with wait_flag = landed, wait_target = target) starts its TMA
+// loads only once every rank's CTAs have reported, so there is no separate all-gather step and no
+// host synchronisation; the copy overlaps the layers before it.
+//
+// Re-use of a gather buffer: a rank may only overwrite its peers' buffer once they have finished the
+// GEMM that read the previous contents.  Each rank launches this kernel after its own previous reader
+// in stream order (an event), so at kernel entry "I am done with the buffer" holds locally; CTA 0
+// tells every peer (ready[peer][this rank] = use) and waits until all peers said the same, then opens a
+// local gate that the other CTAs wait on.  All waits are bounded.  The grid must be co-resident.
+// ---------------------------------------------------------------------------------------------
+namespace tahb {
+
+struct ShardGatherParams {
+  const uint4* src;                      // local shard
+  uint4* dst[COMM_MAX_RANKS];            // every rank's gather buffer + this rank's offset
+  uint4* mc_dst;                         // multicast address of the same place, or nullptr
+  uint32_t* landed[COMM_MAX_RANKS];      // every rank's landing flags [world] (indexed by source rank)
+  uint32_t* ready[COMM_MAX_RANKS];       // every rank's buffer-free flags [world] (indexed by source rank)
+  uint32_t* target;                      // local [world]: landing targets the consumer waits for
+  uint32_t* state;                       // local [3]: use counter, CTA arrivals, gate
+  long long n16;                         // shard size in 16-byte units
+  int rank, world;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) shard_gather_push_kernel(const ShardGatherParams p) {
+  __shared__ int s_ok;
+  const uint32_t use = p.state[0] + 1;               // this launch's sequence number (same on all ranks)
+  if (blockIdx.x == 0) {
+    bool ok = true;
+    if ((int)threadIdx.x < p.world) {
+      const int q = threadIdx.x;
+      __threadfence_system();
+      st_relaxed_sys(p.ready[q] + p.rank, use);
+      const uint32_t* mine = p.ready[p.rank] + q;
+      unsigned long long t0 = 0;
+      uint32_t spins = 0;
+      while ((int32_t)(ld_relaxed_sys(mine) - use) < 0) {
+        if ((++spins & 0xff) == 0) {
+          const unsigned long long now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > WAIT_TIMEOUT_NS) { atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER_FLAG); ok = false; break; }
+        }
+      }
+      __threadfence_system();
+    }
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicExch(&p.state[2], all_ok ? use : 0x80000000u | use);    // open the gate (or report failure)
+    }
+  }
+  if (threadIdx.x == 0) {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    int ok = 1;
+    while (true) {
+      const uint32_t g = *reinterpret_cast<volatile uint32_t*>(&p.state[2]);
+      if (g == use) break;
+      if (g == (0x80000000u | use)) { ok = 0; break; }
+      if ((++spins & 0xff) == 0) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > WAIT_TIMEOUT_NS) { atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER_FLAG); ok = 0; break; }
+      }
+    }
+    __threadfence();
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < p.n16; i += stride) {
+      const uint4 v = p.src[i];
+      if (p.mc_dst != nullptr) {
+        multimem_st_v4(p.mc_dst + i, v);
+      } else {
+        for (int q = 0; q < p.world; ++q) p.dst[q][i] = v;
+      }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < p.world) {
+      __threadfence_system();
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.landed[threadIdx.x] + p.rank), "r"(1u) : "memory");
+    }
+  }
+  // last CTA: advance the consumer's targets and the use counter for the next launch
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(&p.state[1], 1u) == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    if ((int)threadIdx.x < p.world) p.target[threadIdx.x] += gridDim.x;
+    if (threadIdx.x == 0) { p.state[0] = use; p.state[1] = 0; }
+  }
+}
+
+}  // namespace tahb
+
+// src: local shard (`bytes`, a multiple of 16); dst: `world` pointers to the place of this rank's shard in
+// every rank's gather buffer; mc_dst: the multicast address of that place or null; landed / ready: `world`
+// pointers to every rank's flag arrays; target / state: local device arrays ([world] and [3] uint32, zeroed
+// once).  The same grid (<= 148 CTAs) on every rank.
+extern "C" int tahb_shard_gather_push(const void* src, void* const* dst, void* mc_dst, void* const* landed,
+                                      void* const* ready, void* target, void* state, long long bytes, int rank,
+                                      int world, int grid, int* status, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  if (world < 1 || world > COMM_MAX_RANKS || bytes % 16 || grid < 1 || grid > 148) return -1;
+  ShardGatherParams p;
+  p.src = reinterpret_cast<const uint4*>(src);
+  for (int q = 0; q < COMM_MAX_RANKS; ++q) {
+    const int qq = q < world ? q : 0;
+    p.dst[q] = reinterpret_cast<uint4*>(dst[qq]);
+    p.landed[q] = reinterpret_cast<uint32_t*>(landed[qq]);
+    p.ready[q] = reinterpret_cast<uint32_t*>(ready[qq]);
+  }
+  p.mc_dst = reinterpret_cast<uint4*>(mc_dst);
+  p.target = reinterpret_cast<uint32_t*>(target);
+  p.state = reinterpret_cast<uint32_t*>(state);
+  p.n16 = bytes / 16;
+  p.rank = rank; p.world = world;
+  p.status = status;
+  shard_gather_push_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

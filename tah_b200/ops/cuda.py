@@ -530,6 +530,18 @@ def push_reduce_norm_bcast(slot, cnt, cnt_target, xout_ptrs, mc_xout: int, xflag
         "tahb_push_reduce_norm_bcast")
 
 
+def shard_gather_push(shard, dst_ptrs, mc_dst: int, landed_ptrs, ready_ptrs, target, state, rank: int, world: int,
+                      grid: int):
+    """Store this rank's parameter shard into every rank's gather buffer and advance the landing flags
+    (``shard_gather_push_kernel`` in ``csrc/comm.cu``); the consumer is :func:`gemm` with ``tp_wait``."""
+    n = len(dst_ptrs)
+    arr = lambda ptrs: (c_void_p * n)(*ptrs)
+    _rc(lib().tahb_shard_gather_push(_p(shard), arr(dst_ptrs), c_void_p(mc_dst), arr(landed_ptrs), arr(ready_ptrs),
+                                     _p(target), _p(state), c_ll(shard.numel() * shard.element_size()), c_int(rank),
+                                     c_int(world), c_int(grid), _p(status_word(shard.device)), _stream()),
+        "tahb_shard_gather_push")
+
+
 class TickStateBinding:
     """Packs the scheduler state tensors into the pointer/int arrays the tick kernels take."""
 

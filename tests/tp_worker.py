@@ -102,6 +102,33 @@ def main():
                 print(f"push path multicast={use_mc} iter={it}: max err h {e1:.4f} consumer {e2:.4f} xn {e3:.4f} {'ok' if good else 'BAD'}")
             dist.barrier()
 
+    # ---- sharded parameters: all-gather by push on a side stream, consumed by the GEMM through flags ----
+    from tah_b200.parallel.fsdp import ShardedWeightStore
+    for use_mc in (False, True):
+        gw = torch.Generator(device=dev).manual_seed(21)
+        shapes = [(512, 256), (256 * world, 512), (1024, 256)]
+        full = [(torch.randn(F, Kd, generator=gw, device=dev) * Kd ** -0.5).to(torch.bfloat16) for F, Kd in shapes]
+        store = ShardedWeightStore(dist.group.WORLD, dev, full, n_buffers=2, use_multicast=use_mc)
+        worst = 0.0
+        store.prefetch(0)
+        for rnd in range(3):
+            for i in range(len(full)):
+                nxt = (i + 1) % len(full)
+                store.prefetch(nxt)                              # one weight ahead, into the other buffer
+                gx = torch.Generator(device=dev).manual_seed(100 * rnd + i)     # same activations on all ranks
+                x = torch.randn(48, shapes[i][1], generator=gx, device=dev).to(torch.bfloat16)
+                y = store.linear(x, i)
+                ref = x.float() @ full[i].float().t()
+                worst = max(worst, (y.float() - ref).abs().max().item())
+        store.linear(torch.zeros(16, shapes[0][1], dtype=torch.bfloat16, device=dev), 0)   # consume the last prefetch
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        good = worst < 0.06
+        ok = ok and good
+        if rank == 0:
+            print(f"sharded weights multicast={use_mc and store.buf_mc[0] != 0}: max err {worst:.4f} {'ok' if good else 'BAD'}")
+        dist.barrier()
+
     # ---- ZeRO optimizer: fused reduce-scatter + AdamW + parameter broadcast over peer memory -----
     from tah_b200.parallel.zero import ZeroAdamW
     for use_mc in (False, True):
