@@ -67,6 +67,7 @@ class ShardedWeightStore:
         self._state = torch.zeros(n_buffers, 4, dtype=torch.int32, device=device)
         self._uses = [0] * n_buffers
         self._where = {}
+        self._next = 0
         self._reader_done: List[Optional[torch.cuda.Event]] = [None] * n_buffers
         self.side = torch.cuda.Stream(device=device)
         torch.cuda.synchronize(device)
@@ -75,7 +76,11 @@ class ShardedWeightStore:
     # ------------------------------------------------------------------------------------------
     def prefetch(self, i: int) -> None:
         """Start gathering weight ``i`` into the next buffer (asynchronous, side stream)."""
-        b = i % self.n_buffers
+        b = self._next % self.n_buffers                  # buffers are used round-robin in prefetch order
+        if any(bb == b for bb, _ in self._where.values()):
+            raise RuntimeError(f"gather buffer {b} still holds a weight that has not been consumed "
+                               f"(at most {self.n_buffers} prefetches may be outstanding)")
+        self._next += 1
         F, Kd = self.shapes[i]
         shard = self.shards[i]
         off = self.rank * shard.numel() * 2
