@@ -278,8 +278,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float a = exp2f(fmaf(sv[c * 8 + 2 * j], sc, neg_m));
-            const float bb = exp2f(fmaf(sv[c * 8 + 2 * j + 1], sc, neg_m));
+            const float a = ex2_approx(fmaf(sv[c * 8 + 2 * j], sc, neg_m));
+            const float bb = ex2_approx(fmaf(sv[c * 8 + 2 * j + 1], sc, neg_m));
             p2[j] = __floats2bfloat162_rn(a, bb);
             psum0 += a;
             psum1 += bb;

@@ -190,7 +190,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float sc = p.scale_log2;
     float lse = row_ok ? p.lse[(size_t)(q0 + row) * p.nq + head] : -INFINITY;
-    const float dsum = row_ok ? p.dsum[(size_t)(q0 + row) * p.nq + head] : 0.f;
+    const float dsum_s = (row_ok ? p.dsum[(size_t)(q0 + row) * p.nq + head] : 0.f) * p.scale;   // D * scale
     const float neg_lse = (lse == -INFINITY) ? 0.f : -lse;
     int i = 0;
     for (int s = 0; s < p.n_seg; ++s) {
@@ -211,9 +211,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int c0 = c * 8 + 2 * j;
-            const float pa = c0 < valid ? exp2f(fmaf(sv[c0], sc, neg_lse)) : 0.f;
-            const float pb = c0 + 1 < valid ? exp2f(fmaf(sv[c0 + 1], sc, neg_lse)) : 0.f;
-            p2[j] = __floats2bfloat162_rn(pa * (dp[c0] - dsum) * p.scale, pb * (dp[c0 + 1] - dsum) * p.scale);
+            const float pa = c0 < valid ? ex2_approx(fmaf(sv[c0], sc, neg_lse)) : 0.f;
+            const float pb = c0 + 1 < valid ? ex2_approx(fmaf(sv[c0 + 1], sc, neg_lse)) : 0.f;
+            p2[j] = __floats2bfloat162_rn(pa * fmaf(dp[c0], p.scale, -dsum_s), pb * fmaf(dp[c0 + 1], p.scale, -dsum_s));
           }
           const int cc = half * 4 + c;
           *reinterpret_cast<uint4*>(ds_s + row * 128 + ((cc ^ (row & 7)) << 4)) = pk;
@@ -436,8 +436,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (qr < qb) {
           const int hh = kvh * G + j % G;
           m_c = p.kv_count[qr];
-          m_l = p.lse[(size_t)qr * p.nq + hh];
-          m_d = p.dsum[(size_t)qr * p.nq + hh];
+          m_l = -p.lse[(size_t)qr * p.nq + hh];               // stored negated / pre-scaled for the inner loop
+          m_d = p.dsum[(size_t)qr * p.nq + hh] * p.scale;
         }
       }
     };
@@ -482,9 +482,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           for (int e = 0; e < 2; ++e) {
             const int cl = 2 * j + e, col = c * 8 + cl;
             const bool vis = key_ok && kidx < cv[cl];
-            const float pe = vis ? exp2f(fmaf(sv[col], sc, -lv[cl])) : 0.f;
+            const float pe = vis ? ex2_approx(fmaf(sv[col], sc, lv[cl])) : 0.f;
             pv[e] = pe;
-            dsv[e] = pe * (dp[col] - dv8[cl]) * p.scale;
+            dsv[e] = pe * fmaf(dp[col], p.scale, -dv8[cl]);
           }
           p2[j] = __floats2bfloat162_rn(pv[0], pv[1]);
           d2[j] = __floats2bfloat162_rn(dsv[0], dsv[1]);
