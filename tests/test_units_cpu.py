@@ -306,3 +306,17 @@ def test_attention_tiling_helpers_cpu():
     assert row0.tolist() == [10, 138, 266, 500] and nkeys.tolist() == [128, 128, 4, 3]
     assert kidx0.tolist() == [0, 128, 256, 0]
     assert qa.tolist() == [0, 0, 0, 7] and qb.tolist() == [7, 7, 7, 16]
+
+
+def test_gemm_planner_choices_cpu():
+    """The split-K / tile planner (pure host arithmetic): legal plans, split-K for small-M long-K shapes,
+    none for shapes that already fill the GPU."""
+    from tah_b200.ops.cuda import _fits, plan_gemm
+    for (M, F, Kd, R, dual) in [(256, 4096, 2048, 192, False), (256, 2048, 6144, 64, False), (64, 2048, 2048, 0, False),
+                                (256, 6144, 2048, 128, True), (8192, 4096, 2048, 0, False), (1, 128, 128, 0, False)]:
+        bn, s = plan_gemm(M, F, Kd, R, dual)
+        assert bn in (16, 32, 64, 128, 256) and s in (1, 2, 4)
+        assert s == 1 or (bn % s == 0 and (bn // s) % 16 == 0 and _fits(bn, s, 2 if dual else 1))
+    assert plan_gemm(256, 2048, 6144)[1] > 1            # few feature tiles, long K: split
+    assert plan_gemm(8192, 4096, 2048)[1] == 1          # 1024 CTAs already
+    assert plan_gemm(256, 151936, 2048)[1] == 1         # LM head
