@@ -204,6 +204,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_ld32(tmem_dp + lane_off + half * 32, dp);
         tmem_ld_wait();
         if (i > 0) mbar_wait(dq_done, (i - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
+        const bool all_visible = __all_sync(0xffffffffu, valid >= 32);    // no masking inside this block
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 pk;
@@ -211,8 +212,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int c0 = c * 8 + 2 * j;
-            const float pa = c0 < valid ? ex2_approx(fmaf(sv[c0], sc, neg_lse)) : 0.f;
-            const float pb = c0 + 1 < valid ? ex2_approx(fmaf(sv[c0 + 1], sc, neg_lse)) : 0.f;
+            float pa = ex2_approx(fmaf(sv[c0], sc, neg_lse));
+            float pb = ex2_approx(fmaf(sv[c0 + 1], sc, neg_lse));
+            if (!all_visible) {
+              pa = c0 < valid ? pa : 0.f;
+              pb = c0 + 1 < valid ? pb : 0.f;
+            }
             p2[j] = __floats2bfloat162_rn(pa * fmaf(dp[c0], p.scale, -dsum_s), pb * fmaf(dp[c0 + 1], p.scale, -dsum_s));
           }
           const int cc = half * 4 + c;
@@ -462,6 +467,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       tmem_ld32(tmem_sc[it & 1] + 64 + lane_off + half * 32, dp);
       tmem_ld_wait();
       if (it > 0) mbar_wait(acc_done, (it - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
+      // every key of the block visible to every query of this thread's 32 columns: no masking needed.  The
+      // columns' counts are the same for all lanes of the warp, so the test is warp-uniform.
+      int cmin = 0x7fffffff;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int4 cv4 = *reinterpret_cast<const int4*>(mb + 2 * BQ + c * 4);
+        cmin = min(cmin, min(min(cv4.x, cv4.y), min(cv4.z, cv4.w)));
+      }
+      const bool all_visible = nkeys == 128 && kidx0 + 127 < cmin;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint4 pk, dk;
@@ -481,8 +495,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int cl = 2 * j + e, col = c * 8 + cl;
-            const bool vis = key_ok && kidx < cv[cl];
-            const float pe = vis ? ex2_approx(fmaf(sv[col], sc, lv[cl])) : 0.f;
+            float pe = ex2_approx(fmaf(sv[col], sc, lv[cl]));
+            if (!all_visible) pe = (key_ok && kidx < cv[cl]) ? pe : 0.f;
             pv[e] = pe;
             dsv[e] = pe * fmaf(dp[col], p.scale, -dv8[cl]);
           }
