@@ -256,15 +256,23 @@ __global__ void __launch_bounds__(256) soft_embed_rows_kernel(const float* __res
   __syncthreads();
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int k = 0; k < K; ++k) {
-      const uint4 e = reinterpret_cast<const uint4*>(E + (size_t)id[k] * H)[v];
-      const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&e);
-      const float pk = prob[k];
+    // eight embedding rows in flight per thread; the accumulation order (k ascending) is unchanged
+    for (int k0 = 0; k0 < K; k0 += 8) {
+      uint4 e8[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(eh[j]);
-        acc[2 * j] += bf16_round(pk * f.x);
-        acc[2 * j + 1] += bf16_round(pk * f.y);
+      for (int u = 0; u < 8; ++u)
+        e8[u] = (k0 + u < K) ? reinterpret_cast<const uint4*>(E + (size_t)id[k0 + u] * H)[v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (k0 + u >= K) break;
+        const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&e8[u]);
+        const float pk = prob[k0 + u];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(eh[j]);
+          acc[2 * j] += bf16_round(pk * f.x);
+          acc[2 * j + 1] += bf16_round(pk * f.y);
+        }
       }
     }
     uint4 o;
