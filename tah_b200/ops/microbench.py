@@ -104,10 +104,14 @@ def bench_decode_attn(a):
     depth = (torch.rand(rows, device="cuda") < 0.06).int()
     q = _rand(rows, nq * hd)
     out = torch.empty_like(q)
-    fn = lambda i: K.decode_attn(q, [pools[i % n], pool1], [pt, pt1], [ln, ln1], depth, nq, nkv, hd, page, hd ** -0.5, out=out)
+    ws = None
+    if a.nsplit > 1:
+        ws = torch.empty(int(K.lib().tahb_decode_attn_ws_floats(rows, nq, hd, a.nsplit)), dtype=torch.float32, device="cuda")
+    fn = lambda i: K.decode_attn(q, [pools[i % n], pool1], [pt, pt1], [ln, ln1], depth, nq, nkv, hd, page, hd ** -0.5, out=out,
+                                 n_split=a.nsplit, ws=ws)
     t = _time(fn, a.iters, a.warmup)
     byts = rows * ctx * 2 * nkv * hd * 2
-    return {"op": "decode_attn", "rows": rows, "ctx": ctx, "nq": nq, "nkv": nkv, "hd": hd}, t, 4.0 * rows * nq * hd * ctx, byts
+    return {"op": "decode_attn", "rows": rows, "ctx": ctx, "nq": nq, "nkv": nkv, "hd": hd, "n_split": a.nsplit}, t, 4.0 * rows * nq * hd * ctx, byts
 
 
 def bench_prefill_attn(a):
@@ -196,6 +200,7 @@ def main(argv=None):
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on the same operands")
     ap.add_argument("--rows", type=int, default=256, help="decode rows / prefill sequences / top-k rows")
     ap.add_argument("--ctx", type=int, default=1024, help="context (decode) or sequence length (prefill)")
+    ap.add_argument("--nsplit", type=int, default=1, help="decode attention: split each row's KV walk over this many CTAs")
     ap.add_argument("--nq", type=int, default=16)
     ap.add_argument("--nkv", type=int, default=8)
     ap.add_argument("--hd", type=int, default=128)
