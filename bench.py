@@ -1,17 +1,31 @@
 #!/usr/bin/env python
-"""Headline benchmark: TaH-plus-1.7B decode throughput (2 iterations, tensor parallel over N GPUs).
+"""Headline benchmark: TaH-plus-1.7B decode throughput (2 iterations, tensor parallel over N GPUs), with the
+training step of the same model as a sub-record.
 
 Workload (the tensor-parallel serving configuration): Qwen3-1.7B shapes, 28 layers, hidden 2048,
 16 q / 8 kv heads, head_dim 128, intermediate 6144, vocab 151936, tied embeddings, LoRA rank 64 on
 all seven projections for iteration 2, decider MLP 2048 -> 512 -> 1, max_iter 2.  256 prompts of
-256 uniform-random token ids, greedy decode, hard-token mask = seeded Bernoulli(0.06) overriding
-the random-init decider.  Random-init weights, synthetic data, bf16.
+256 uniform-random token ids, greedy decode of 2048 new tokens, hard-token mask = seeded Bernoulli(0.06)
+overriding the random-init decider.  Random-init weights, synthetic data, bf16.
 
 A *step* is one engine tick: every one of the 256 rows advances by one pass (an easy row emits a
-token, a hard row spends two ticks on its token).  The metric is emitted tokens per second over
-the K timed ticks, device-timed with CUDA events, max over ranks.  Per tick the kernels read the
-3.4 GB of weights plus the rows' KV pages, far more than the 126 MB L2, so no explicit L2 flush
-is needed between steps.
+token, a hard row spends two ticks on its token).  The cost of a tick grows with the KV context (256 at the
+start of the decode, 2304 at its end), so the K timed ticks are spread over five decode depths - the
+midpoints of the five fifths of the 2048-token run - by fast-forwarding the rows' KV lengths and page tables
+between windows (``TaHEngine.fast_forward``; the cost of a tick depends on the lengths, not on the cached
+values).  ``value`` = emitted tokens / device time summed over the windows, i.e. the throughput of the whole
+run estimated from K ticks; ``ms_by_context`` has the per-depth tick time.  Device-timed with CUDA events,
+max over ranks.  Per tick the kernels read the 3.4 GB of weights plus the rows' KV pages, far more than the
+126 MB L2, so no explicit L2 flush is needed between steps.
+
+``e2e`` is the public call a user makes - ``TaHEngine.generate`` on the 256 prompts for all 2048 new tokens -
+timed on the host from the pinned-memory prompt upload to the last token id read back (one device-to-host
+copy of the 256 new token ids per tick).
+
+``vs_eager`` compares with the same model run through plain PyTorch ops (the restated reference: cuBLAS GEMMs,
+SDPA with a materialised duo-causal mask, unfused LoRA, ``torch.cat`` KV cache, token-by-token Python loop) at
+the same batch and prompt, over its first decode steps (its cheapest context).  ``train`` is the SFT step of the
+same model (CE + decider BCE, second iteration on every token, sequence 8192, sharded AdamW) on the same GPUs.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|eager]
 """
@@ -30,11 +44,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODEL = "tah-plus-1.7b"
-BATCH, PROMPT, NEW_TOKENS, HARD_P, LORA_R = 256, 256, 2048, 0.06, 64
+BATCH, PROMPT, NEW_TOKENS, HARD_P, LORA_R = 256, 256, 2048, (0.06,), 64
 MAX_ITER = 2
-# profiling aid only: a shorter prompt makes the (unprofiled) prefill cheap under ncu; results printed
-# with this override are not benchmark values
-PROMPT = int(os.environ.get("TAH_B200_BENCH_PROMPT", PROMPT))
+N_WINDOWS = 5
 
 
 def _unavailable(reason: str):
@@ -102,7 +114,7 @@ def build_model(device, n_layers=None):
         base = Qwen3ForCausalLM(cfg, dtype=torch.bfloat16)
     tcfg = TaHConfig(max_iter=MAX_ITER, iter_decider="SimpleMLPIterDecider",
                      iter_decider_kwargs=dict(hidden_states_size=cfg.hidden_size, inner_size=cfg.hidden_size // 4,
-                                              threshold=0.5),
+                                              hidden_states_layer_nums=[cfg.num_hidden_layers], threshold=0.5),
                      adapter_kwargs=dict(r=LORA_R, lora_alpha=2 * LORA_R, lora_dropout=0.0, target_modules="all-linear"),
                      input_updater_kwargs={"topk": 100}, train_loss="NextTokenPredLoss")
     model = TaHForCausalLM(base, tcfg)
@@ -112,6 +124,61 @@ def build_model(device, n_layers=None):
                 p.normal_(std=0.01)      # a trained adapter is not the zero matrix
     model.iter_decider.to(device=device, dtype=torch.bfloat16)
     return model.eval()
+
+
+def window_plan(steps: int):
+    """Decode depths at which ticks are timed and how many ticks each gets (sum = steps)."""
+    n = max(1, min(N_WINDOWS, steps))
+    contexts = [int(PROMPT + NEW_TOKENS * (i + 0.5) / n) for i in range(n)]
+    per = [steps // n + (1 if i < steps % n else 0) for i in range(n)]
+    return contexts, per
+
+
+def eager_anchor(model, dev, steps: int, batch: int):
+    """Tokens/s of the restated reference path over ``steps`` decode steps after its prefill
+    (difference of two generate calls, so the prefill is not in the number)."""
+    import torch
+    from tah_b200.model.iter_decider import IterDecider
+    from tah_b200.model.utils import generate_loop
+    prev = os.environ.get("TAH_B200_FORCE_TORCH")
+    os.environ["TAH_B200_FORCE_TORCH"] = "1"
+    saved = (model.iter_decider, model.eval_iter_decider)
+
+    class Coin(IterDecider):
+        def __init__(self):
+            super().__init__(max_iter=MAX_ITER)
+            self.g = torch.Generator(device=dev).manual_seed(0)
+
+        def forward(self, logits, iter_depth, **kw):
+            if iter_depth >= MAX_ITER:
+                return self._stop_decision(logits, -10.0)
+            p = HARD_P[min(iter_depth - 1, len(HARD_P) - 1)]
+            return (torch.rand(logits.shape[0], device=dev, generator=self.g) < p,
+                    torch.zeros(logits.shape[0], device=dev))
+
+    try:
+        model.iter_decider = model.eval_iter_decider = Coin()
+        g = torch.Generator().manual_seed(1234)
+        ids = torch.randint(0, model.config.vocab_size, (batch, PROMPT), generator=g).to(dev)
+        times = []
+        for n in (2, 2 + steps):                      # first call also warms the library kernels up
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            toks, _ = generate_loop(model, None, {"input_ids": ids}, max_new_tokens=n, do_sample=False, verbose=False)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+        dt = max(1e-9, times[1] - times[0])
+        return {"value": round(batch * steps / dt, 1), "unit": "tokens/s", "steps": steps, "global_batch": batch,
+                "seq_len": PROMPT, "context": f"{PROMPT}..{PROMPT + 2 + steps}", "n_gpus": 1,
+                "with_prefill_tok_s": round(batch * (2 + steps) / times[1], 1),
+                "impl": "restated reference: same model, plain PyTorch ops + Python decode loop"}
+    finally:
+        model.iter_decider, model.eval_iter_decider = saved
+        if prev is None:
+            os.environ.pop("TAH_B200_FORCE_TORCH", None)
+        else:
+            os.environ["TAH_B200_FORCE_TORCH"] = prev
+        torch.cuda.empty_cache()
 
 
 def run_ours(args):
@@ -128,91 +195,148 @@ def run_ours(args):
         from tah_b200.parallel.tp import TensorParallel
         tp = TensorParallel(dist.group.WORLD, dev)
     from tah_b200.engine import TaHEngine
-    from tah_b200.ops import cuda as K
     model = build_model(dev)
-    eng = TaHEngine(model, max_rows=BATCH, max_seq_len=PROMPT + NEW_TOKENS + 8, tp=tp)
-    hard_p = HARD_P if isinstance(HARD_P, tuple) else (HARD_P,)
-    eng.hard_override = eng.make_bernoulli_override(BATCH, hard_p, seed=0)
+    slack = 64                                         # rows must not run out of budget inside the last window
+    eng = TaHEngine(model, max_rows=BATCH, max_seq_len=PROMPT + NEW_TOKENS + slack + 8, tp=tp)
+    eng.hard_override = eng.make_bernoulli_override(BATCH, HARD_P, seed=0)
     g = torch.Generator().manual_seed(1234)
     prompts_host = torch.randint(0, model.config.vocab_size, (BATCH, PROMPT), generator=g).pin_memory()
 
-    # ---------------- kernel-timed arm: K ticks after W warm-up ticks ----------------
-    state = {}
-    timed = {"start": None, "end": None, "tok0": None, "tok1": None, "launch0": 0}
-    W, Kt = args.warmup, args.steps
-    sampler = ClockSampler(local)
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
-    def on_tick(t, s):
-        if t == W:
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            timed["tok0"] = int(s.tokens_done.item())
-            sampler.start()
-            timed["start"] = torch.cuda.Event(enable_timing=True)
-            timed["start"].record()
-        elif t == W + Kt:
-            timed["end"] = torch.cuda.Event(enable_timing=True)
-            timed["end"].record()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            timed["tok1"] = int(s.tokens_done.item())
-            timed["clocks"] = sampler.stop()
+    # ---------------- device-timed arm: K ticks in windows at several decode depths ----------------
+    W, Kt = args.warmup, args.steps
+    contexts, per = window_plan(Kt)
+    sampler = ClockSampler(local)
+    # tick index (1-based, counted by generate) -> what happens after that tick.  W warm-up ticks at the prompt's
+    # depth; then per window: jump to its depth, one untimed tick to settle, its timed ticks.
+    events, t = {}, W
+    for i, n in enumerate(per):
+        events.setdefault(t, []).append(("jump", i))
+        t += 1
+        events.setdefault(t, []).append(("start", i))
+        t += n
+        events.setdefault(t, []).append(("end", i))
+    total_ticks = t
+    win = [{"ctx": c, "ticks": n} for c, n in zip(contexts, per)]
+
+    def on_tick(tk, s):
+        for kind, i in events.get(tk, ()):
+            if kind == "jump":
+                eng.fast_forward(s, win[i]["ctx"])
+            elif kind == "start":
+                barrier()
+                if i == 0:
+                    sampler.start()
+                win[i]["tok0"] = int(s.tokens_done.item())
+                win[i]["e0"] = torch.cuda.Event(enable_timing=True)
+                win[i]["e1"] = torch.cuda.Event(enable_timing=True)
+                win[i]["e0"].record()
+            else:
+                win[i]["e1"].record()
+                barrier()
+                win[i]["tok1"] = int(s.tokens_done.item())
+                if i + 1 == len(win):
+                    win[i]["clocks"] = sampler.stop()
 
     ids = prompts_host.to(dev, non_blocking=True)
-    res = eng.generate(ids, None, max_new_tokens=NEW_TOKENS, do_sample=False, max_ticks=W + Kt, sync_every=1 << 30,
-                       on_tick=on_tick)
-    ms = timed["start"].elapsed_time(timed["end"])
-    toks = timed["tok1"] - timed["tok0"]
-    t_ms = torch.tensor([ms], device=dev)
+    res = eng.generate(ids, None, max_new_tokens=NEW_TOKENS + slack, do_sample=False, max_ticks=total_ticks,
+                       sync_every=1 << 30, on_tick=on_tick)
+    ms_list = [w["e0"].elapsed_time(w["e1"]) for w in win]
+    t_ms = torch.tensor(ms_list, device=dev)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms = float(t_ms.item())
+    ms_list = [float(x) for x in t_ms.tolist()]
+    toks = sum(w["tok1"] - w["tok0"] for w in win)
+    ms = sum(ms_list)
     value = toks / (ms / 1e3)
     launches = eng.kernel_launches_per_tick * Kt
+    clocks = win[-1].get("clocks")
+    prefill_ms = res.prefill_ms
 
-    # ---------------- end-to-end arm: the public generate call, H2D prompts + D2H tokens ---------
-    e2e_ticks = W + Kt                                 # the same ticks as above, now with prefill and copies
+    # ---------------- end-to-end arm: the public generate call on the whole workload ----------------
+    e2e_new = args.e2e_new_tokens if args.e2e_new_tokens > 0 else NEW_TOKENS
     host_tok = torch.empty(BATCH, dtype=torch.int32).pin_memory()
+    n_ticks_seen = [0]
 
-    def stream_out(t, s):
+    def stream_out(tk, s):
         host_tok.copy_(s.tok, non_blocking=True)       # result of the step, read back every tick
+        n_ticks_seen[0] = tk
 
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+    # one short call first so that the tick buffers and the captured graph of this (rows, max_new) shape exist
+    eng.generate(prompts_host.to(dev), None, max_new_tokens=e2e_new, do_sample=False, max_ticks=2, sync_every=1 << 30)
+    barrier()
     t0 = time.perf_counter()
     ids2 = prompts_host.to(dev, non_blocking=True)     # prompt H2D from pinned memory is inside the timed call
-    res2 = eng.generate(ids2, None, max_new_tokens=NEW_TOKENS, do_sample=False, max_ticks=e2e_ticks,
-                        sync_every=1 << 30, on_tick=stream_out)
+    res2 = eng.generate(ids2, None, max_new_tokens=e2e_new, do_sample=False, on_tick=stream_out)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     t_e = torch.tensor([e2e_s], device=dev)
     if world > 1:
         dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
-    e2e_val = res2.tokens_emitted / float(t_e.item())
+    e2e_s = float(t_e.item())
+    e2e_val = res2.tokens_emitted / e2e_s
+    e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "ticks": res2.ticks, "new_tokens": e2e_new,
+           "tokens": res2.tokens_emitted, "seconds": round(e2e_s, 3), "prefill_ms": round(res2.prefill_ms, 2),
+           "graph_captured_in_timed_call": False,
+           "includes": "prompt H2D (pinned), prefill, every decode tick of the run, per-tick token D2H, final sync",
+           "h2d_bytes_per_step": round(prompts_host.numel() * 8 / max(1, res2.ticks), 1),
+           "d2h_bytes_per_step": BATCH * 4}
+
+    # ---------------- anchors on the same box: eager path, training step ----------------
+    del res, res2
+    eng.kv = None
+    eng._states.clear()
+    del eng
+    tp = None
+    torch.cuda.empty_cache()
+    eager = None
+    if not args.no_eager:
+        if rank == 0:
+            try:
+                eager = eager_anchor(model, dev, steps=max(4, min(16, Kt)), batch=BATCH)
+            except Exception as exc:                   # out of memory at this batch: report, do not fail the run
+                eager = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        barrier()
+    del model
+    torch.cuda.empty_cache()
+    train = None
+    if not args.no_train:
+        import bench_train
+        ta = argparse.Namespace(seq=8192, accum=1, hard_rate=None, train_model=MODEL, decider="oracle-mlp",
+                                lora_rank=LORA_R, strategy=args.train_strategy, checkpoint=False)
+        try:
+            train = bench_train.run(ta, steps=2, warmup=1)
+        except Exception as exc:
+            train = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
 
     if rank == 0:
         out = {
             "metric": ("TaH-plus-1.7B decode tok/s (2-iter, TP=N)" if MODEL == "tah-plus-1.7b" and MAX_ITER == 2
                        else f"{MODEL} decode tok/s ({MAX_ITER}-iter, TP=N)"), "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": Kt, "warmup": W, "ms_per_step": round(ms / Kt, 4), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": round(value / 8.5, 1), "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": MODEL, "layers": model.config.num_hidden_layers, "global_batch": BATCH, "seq_len": PROMPT,
-                       "new_tokens": NEW_TOKENS, "hard_token_rate": hard_p[0] if len(hard_p) == 1 else list(hard_p),
+            "config": {"model": MODEL, "layers": 28 if MODEL == "tah-plus-1.7b" else None, "global_batch": BATCH,
+                       "seq_len": PROMPT, "new_tokens": NEW_TOKENS,
+                       "hard_token_rate": HARD_P[0] if len(HARD_P) == 1 else list(HARD_P),
                        "max_iter": MAX_ITER, "lora_rank": LORA_R,
                        "parallelism": f"tp{world}", "step": "one engine tick (one pass of every row)",
+                       "timed_contexts": contexts,
                        "l2": "per-tick inputs (3.4 GB weights + KV pages) exceed the 126 MB L2",
-                       "baseline_number": "8.5 tok/s single-stream (only published figure)"},
-            "clocks": timed.get("clocks"),
-            "e2e": {"value": round(e2e_val, 1), "unit": "tokens/s", "ticks": e2e_ticks,
-                    "includes": "prompt H2D (pinned), prefill, decode ticks, per-tick token D2H",
-                    "h2d_bytes_per_step": round(prompts_host.numel() * 8 / max(1, e2e_ticks), 1),
-                    "d2h_bytes_per_step": BATCH * 4},
+                       "baseline_number": "none published for this configuration (the reference's only figure is "
+                                          "8.5 tok/s single-stream at batch 1)"},
+            "ms_by_context": {str(c): round(m / n, 4) for c, m, n in zip(contexts, ms_list, per)},
+            "clocks": clocks,
+            "e2e": e2e,
             "gpu_launches": launches,
-            "tokens_timed": toks, "prefill_ms": round(res.prefill_ms, 2),
+            "tokens_timed": toks, "prefill_ms": round(prefill_ms, 2),
+            "eager": eager,
+            "vs_eager": (round(value / eager["value"], 2) if eager and eager.get("value") else None),
+            "train": train,
         }
         print(json.dumps(out))
     if world > 1:
@@ -222,64 +346,172 @@ def run_ours(args):
 
 
 def run_eager(args):
-    """Restated reference path: the same model through plain PyTorch ops (cuBLAS GEMMs, SDPA with a
-    materialised mask, unfused LoRA, torch.cat KV cache) and the token-by-token Python loop."""
-    os.environ["TAH_B200_FORCE_TORCH"] = "1"
+    """Restated reference path alone: ``--impl eager`` prints its own line (one GPU)."""
     import torch
-    from tah_b200.model.iter_decider import IterDecider
-    from tah_b200.model.utils import generate_loop
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(dev)
     model = build_model(dev)
-    g = torch.Generator().manual_seed(1234)
-    B = args.eager_batch
-    ids = torch.randint(0, model.config.vocab_size, (B, PROMPT), generator=g).to(dev)
-
-    class Coin(IterDecider):
-        def __init__(self):
-            super().__init__(max_iter=2)
-            self.g = torch.Generator(device=dev).manual_seed(0)
-
-        def forward(self, logits, iter_depth, **kw):
-            if iter_depth >= 2:
-                return self._stop_decision(logits, -10.0)
-            return torch.rand(logits.shape[0], device=dev, generator=self.g) < HARD_P[0], torch.zeros(logits.shape[0], device=dev)
-
-    model.iter_decider = model.eval_iter_decider = Coin()
-    n = args.steps
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    toks, _ = generate_loop(model, None, {"input_ids": ids}, max_new_tokens=n, do_sample=False, verbose=False)
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    total = sum(len(t) for t in toks)
-    print(json.dumps({"metric": "TaH-plus-1.7B decode tok/s (2-iter)", "impl": "eager-restated-reference",
-                      "value": round(total / dt, 1), "unit": "tokens/s", "n_gpus": 1, "steps": n,
-                      "includes": "prefill + decode, Python loop", "config": {"global_batch": B, "seq_len": PROMPT}}))
+    rec = eager_anchor(model, dev, steps=max(4, args.steps), batch=args.eager_batch or BATCH)
+    rec.update({"metric": "TaH-plus-1.7B decode tok/s (2-iter)", "impl": "eager-restated-reference"})
+    print(json.dumps(rec))
 
 
 def run_reference(args):
+    """The unmodified reference package (installed under ``baseline/_ref``) on the same workload, through its
+    own public API: a HuggingFace Qwen3 model of the 1.7B shapes with random weights, wrapped by the
+    reference's ``TaHForCausalLM`` and driven by its ``TaHForCasualLM_generate`` (reference
+    ``tah/evaluate/backends.py:154-190``, ``tah/model/utils.py:196-264``).  The hard-token mask is a seeded
+    Bernoulli decider written against the reference's ``IterDecider`` contract.  With N GPUs the 256 rows are
+    split over N independent model replicas, which is how the reference's evaluation driver uses several GPUs
+    (``tah/evaluate/jobs.py:399-423``; its ``tah`` backend has no tensor parallelism).
+
+    ``peft`` is not installed on this image; the reference's ``from peft import LoraConfig, get_peft_model`` is
+    served by the stand-in under ``baseline/peft_standin`` (plain unfused LoRA linears with PEFT's arithmetic and
+    names), which the printed line declares."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "tah")):
         _unavailable("baseline/_ref/tah is not installed")
+    shimmed = []
+    try:
+        import peft  # noqa: F401
+    except ImportError:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "peft_standin"))
+        shimmed.append("peft (stand-in: baseline/peft_standin)")
     sys.path.insert(0, ref_dir)
     try:
+        import torch
         import tah  # noqa: F401
-    except Exception as exc:  # the reference imports peft at module import time
-        _unavailable(f"reference import fails offline: {type(exc).__name__}: {exc} "
-                     "(peft/accelerate/deepspeed are not installed and not in the offline wheelhouse; "
-                     "the reference pins transformers==4.52.4, the image has 5.5.0)")
-    _unavailable("reference imported but no driver for it exists in this build")
+        from tah import TaHConfig, TaHForCausalLM
+        from tah.model.iter_decider import IterDecider
+        from tah.model.utils import TaHForCasualLM_generate
+        from transformers import AutoModelForCausalLM, Qwen3Config
+    except Exception as exc:
+        _unavailable(f"reference import fails offline: {type(exc).__name__}: {exc}")
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from tah_b200.models import preset          # shapes only (a dataclass of numbers), no model code of this repo
+    shp = preset(MODEL)
+    cfg = Qwen3Config(vocab_size=shp.vocab_size, hidden_size=shp.hidden_size, intermediate_size=shp.intermediate_size,
+                      num_hidden_layers=shp.num_hidden_layers, num_attention_heads=shp.num_attention_heads,
+                      num_key_value_heads=shp.num_key_value_heads, head_dim=shp.head_dim, rms_norm_eps=shp.rms_norm_eps,
+                      rope_theta=shp.rope_theta, tie_word_embeddings=True,
+                      max_position_embeddings=max(40960, PROMPT + NEW_TOKENS + 64))
+    torch.manual_seed(0)
+    with torch.device(dev):
+        base = AutoModelForCausalLM.from_config(cfg, attn_implementation="sdpa", torch_dtype=torch.bfloat16)
+    base = base.to(device=dev, dtype=torch.bfloat16)
+    tcfg = TaHConfig(max_iter=MAX_ITER, iter_decider="IterLabelDecider",
+                     adapter_kwargs=dict(r=LORA_R, lora_alpha=2 * LORA_R, lora_dropout=0.0, target_modules="all-linear"),
+                     input_updater_kwargs={"topk": 100}, train_loss="NextTokenPredLoss")
+    model = TaHForCausalLM(base, tcfg).to(device=dev, dtype=torch.bfloat16).eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "lora_B" in n:
+                p.normal_(std=0.01)
+
+    class Coin(IterDecider):
+        def __init__(self):
+            super().__init__(max_iter=MAX_ITER)
+            self.g = torch.Generator(device=dev).manual_seed(rank)
+
+        def forward(self, logits, iter_depth, **kw):
+            if iter_depth >= MAX_ITER:
+                return self._stop_decision(logits, -10.0)
+            p = HARD_P[min(iter_depth - 1, len(HARD_P) - 1)]
+            return (torch.rand(logits.shape[0], device=dev, generator=self.g) < p,
+                    torch.zeros(logits.shape[0], device=dev, dtype=logits.dtype))
+
+    model.iter_decider = model.eval_iter_decider = Coin().to(dev)
+
+    class Tok:
+        eos_token_id = None
+        pad_token_id = 0
+
+        def decode(self, ids, **kw):
+            return ""
+
+    rows = args.ref_batch or BATCH
+    rows_here = rows // world
+    g = torch.Generator().manual_seed(1234)
+    prompts_host = torch.randint(0, shp.vocab_size, (rows, PROMPT), generator=g)[rank * rows_here:(rank + 1) * rows_here].pin_memory()
+    W, Kt = max(1, args.warmup), args.steps
+    sampler = ClockSampler(local)
+
+    def call(n_new):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        ids = prompts_host.to(dev, non_blocking=True)
+        toks, _ = TaHForCasualLM_generate(model, Tok(), {"input_ids": ids, "attention_mask": torch.ones_like(ids)},
+                                          max_new_tokens=n_new, do_sample=False, verbose=False)
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        t = torch.tensor([e0.elapsed_time(e1), wall * 1e3], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]), float(t[1]), sum(len(x) for x in toks)
+
+    try:
+        call(2)                                        # library warm-up (cuBLAS handles, SDPA selection)
+        ms_w, _, _ = call(W)                           # prefill + W decode steps
+        sampler.start()
+        ms_wk, wall_wk, n_tok = call(W + Kt)           # prefill + W + K decode steps
+        clocks = sampler.stop()
+    except torch.cuda.OutOfMemoryError as exc:
+        _unavailable(f"the reference runs out of device memory at {rows_here} rows x {PROMPT} prompt tokens per GPU "
+                     f"(dense (B,T,V) logits buffers): {str(exc)[:120]}")
+    ms = max(1e-6, ms_wk - ms_w)                       # K decode steps at context PROMPT+W .. PROMPT+W+K
+    value = rows * Kt / (ms / 1e3)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "TaH-plus-1.7B decode tok/s (2-iter, TP=N)", "impl": "reference", "value": round(value, 1),
+            "unit": "tokens/s", "n_gpus": world, "steps": Kt, "warmup": W, "ms_per_step": round(ms / Kt, 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": MODEL, "layers": shp.num_hidden_layers, "global_batch": rows, "seq_len": PROMPT,
+                       "new_tokens": NEW_TOKENS, "hard_token_rate": HARD_P[0], "max_iter": MAX_ITER, "lora_rank": LORA_R,
+                       "parallelism": f"dp{world} (independent replicas, {rows_here} rows each)",
+                       "step": "one decode step of the reference loop (one new token per row; a second full-batch "
+                               "pass whenever any row is hard)",
+                       "timed_contexts": [PROMPT + W, PROMPT + W + Kt],
+                       "timing": "difference of two generate calls (W+K and W new tokens), CUDA events, max over ranks",
+                       "l2": "3.4 GB of weights per pass exceed the 126 MB L2"},
+            "deps_not_in_image": shimmed, "transformers": __import__("transformers").__version__,
+            "clocks": clocks,
+            "e2e": {"value": round(n_tok * world / (wall_wk / 1e3), 1), "unit": "tokens/s", "new_tokens": W + Kt,
+                    "includes": "prompt H2D (pinned), prefill, decode loop with its per-token host reads",
+                    "h2d_bytes_per_step": round(prompts_host.numel() * 8 / (W + Kt), 1),
+                    "d2h_bytes_per_step": rows_here * 8},
+            "gpu_launches": 0,
+        }))
+    if world > 1:
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():
     global MODEL, BATCH, PROMPT, NEW_TOKENS, HARD_P, MAX_ITER
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1024)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "eager"])
-    ap.add_argument("--eager-batch", type=int, default=64)
+    ap.add_argument("--eager-batch", type=int, default=0)
+    ap.add_argument("--ref-batch", type=int, default=0)
+    ap.add_argument("--no-eager", action="store_true", help="skip the eager anchor")
+    ap.add_argument("--no-train", action="store_true", help="skip the training sub-record")
+    ap.add_argument("--train-strategy", default="zero2", choices=["zero2", "zero3"])
+    ap.add_argument("--e2e-new-tokens", type=int, default=0, help="new tokens of the end-to-end call (0 = the workload's)")
     # the defaults are the headline configuration (batch 256 x prompt 256 -> 2048 new tokens on the
     # 28-layer model); the flags below select the other serving configurations, e.g.
     #   --model tah-1.7b --batch 64 --prompt 512 --new-tokens 1024        (27 layers, one GPU)
@@ -289,7 +521,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--new-tokens", type=int, default=NEW_TOKENS)
     ap.add_argument("--max-iter", type=int, default=2)
-    ap.add_argument("--hard-p", default=str(HARD_P), help="comma-separated continue probabilities per depth")
+    ap.add_argument("--hard-p", default=",".join(str(x) for x in HARD_P), help="comma-separated continue probabilities per depth")
     args = ap.parse_args()
     MODEL, BATCH, PROMPT, NEW_TOKENS, MAX_ITER = args.model, args.batch, args.prompt, args.new_tokens, args.max_iter
     HARD_P = tuple(float(x) for x in args.hard_p.split(","))

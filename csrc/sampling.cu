@@ -294,10 +294,20 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
   x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
   return x ^ (x >> 31);
 }
+// Uniform in (0, 1) for (row, step): a hash of the call's seed, so that a draw does not depend on which
+// other rows share the batch.  `seed_dev` (optional, device memory) is mixed in when given: a captured
+// graph can then be replayed with a new seed by writing that word.
+__device__ __forceinline__ float draw_uniform(unsigned long long seed, const unsigned long long* seed_dev, int step,
+                                              int r) {
+  const uint64_t sd = seed_dev != nullptr ? (seed ^ splitmix64(*seed_dev)) : seed;
+  const uint64_t h = splitmix64(sd ^ splitmix64(((uint64_t)(uint32_t)step << 32) | (uint32_t)r));
+  return (float)((h >> 40) + 0.5) * (1.0f / 16777216.0f);
+}
 
 __global__ void sample_topk_kernel(const float* __restrict__ val, const int* __restrict__ idx, int* __restrict__ out,
                                    int rows, int K, float temperature, float top_p, float min_p,
-                                   unsigned long long seed, const int* __restrict__ step) {
+                                   unsigned long long seed, const unsigned long long* __restrict__ seed_dev,
+                                   const int* __restrict__ step) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const float* v = val + (size_t)r * K;
@@ -323,8 +333,7 @@ __global__ void sample_topk_kernel(const float* __restrict__ val, const int* __r
     tot = 0.f;
     for (int k = 0; k < n; ++k) tot += w[k];
   }
-  const uint64_t h = splitmix64(seed ^ splitmix64(((uint64_t)(step ? step[r] : 0) << 32) | (uint32_t)r));
-  const float u = (float)((h >> 40) + 0.5) * (1.0f / 16777216.0f) * tot;
+  const float u = draw_uniform(seed, seed_dev, step ? step[r] : 0, r) * tot;
   float c = 0.f;
   int pick = n - 1;
   for (int k = 0; k < n; ++k) {
@@ -332,6 +341,185 @@ __global__ void sample_topk_kernel(const float* __restrict__ val, const int* __r
     if (u < c) { pick = k; break; }
   }
   out[r] = idx[(size_t)r * K + pick];
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sampler over the whole vocabulary, for top_k == 0 (no top-k filter) or top_k > 128, where the
+// sorted-top-k route above does not apply.  Same filter order: temperature -> softmax -> min_p ->
+// top_k -> top_p -> draw.  One CTA of 1024 threads per row.
+//
+// With e_i = exp((x_i - max) / T) every filter is a threshold on e_i, and because x is bf16 a
+// threshold is one of 65536 order-preserving keys, found by a 16-step bisection:
+//   min_p : e_i >= min_p (p_max = 1 / Z), no data pass;
+//   top_k : the largest key t with count(key >= t) >= top_k (ties at t are all kept);
+//   top_p : the largest key t with mass(key >= t) >= top_p * mass(kept so far) (the element that
+//           crosses top_p is kept).
+// Counts are integers and masses are summed in a fixed order, so the result is deterministic.  The
+// draw is the inverse CDF over the kept elements in index order.
+// ---------------------------------------------------------------------------------------------
+constexpr int SFULL_THREADS = 1024;
+
+struct SampleFullShared {
+  float fsum[32];
+  int isum[32];
+  float total_f;
+  int total_i;
+  int pick;
+};
+
+// count and mass of the row's elements whose key is >= t (block-wide, every thread gets the result)
+__device__ __forceinline__ void count_mass_ge(SampleFullShared& sh, const __nv_bfloat16* __restrict__ xr, int V,
+                                              uint32_t t, float m, float inv_t, int* count, float* mass) {
+  int c = 0;
+  float s = 0.f;
+  const int nvec = V / 8;
+  for (int i = threadIdx.x; i < nvec; i += SFULL_THREADS) {
+    const uint4 v = reinterpret_cast<const uint4*>(xr)[i];
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (order_key(e[j]) >= t) {
+        c += 1;
+        s += __expf((__bfloat162float(e[j]) - m) * inv_t);
+      }
+    }
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += SFULL_THREADS) {
+    if (order_key(xr[i]) >= t) {
+      c += 1;
+      s += __expf((__bfloat162float(xr[i]) - m) * inv_t);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();                       // the previous call's totals have been read by everyone
+  if (lane == 0) { sh.isum[warp] = c; sh.fsum[warp] = s; }
+  __syncthreads();
+  if (warp == 0) {
+    c = sh.isum[lane];
+    s = sh.fsum[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      c += __shfl_xor_sync(0xffffffffu, c, o);
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+    }
+    if (lane == 0) { sh.total_i = c; sh.total_f = s; }
+  }
+  __syncthreads();
+  *count = sh.total_i;
+  *mass = sh.total_f;
+}
+
+__global__ void __launch_bounds__(SFULL_THREADS) sample_full_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                    int* __restrict__ out, int V, long long ldx,
+                                                                    float temperature, int top_k, float top_p,
+                                                                    float min_p, unsigned long long seed,
+                                                                    const unsigned long long* __restrict__ seed_dev,
+                                                                    const int* __restrict__ step) {
+  __shared__ SampleFullShared sh;
+  const int r = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const __nv_bfloat16* xr = x + (size_t)r * ldx;
+  // ---- max key ----
+  uint32_t km = 0;
+  for (int i = tid; i < V; i += SFULL_THREADS) km = max(km, order_key(xr[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) km = max(km, __shfl_xor_sync(0xffffffffu, km, o));
+  if (lane == 0) sh.isum[warp] = (int)km;
+  __syncthreads();
+  km = 0;
+  for (int w = 0; w < 32; ++w) km = max(km, (uint32_t)sh.isum[w]);
+  const float m = key_value(km);
+  const float inv_t = 1.0f / temperature;
+  int cnt;
+  float mass;
+  // ---- min_p: smallest key whose e is still >= min_p (monotone in the key; no data pass) ----
+  uint32_t cut = 0;
+  if (min_p > 0.f) {
+    uint32_t lo = 0, hi = km;              // e(hi) = 1 >= min_p holds for min_p <= 1
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi) >> 1;
+      const float xv = key_value(mid);
+      const bool ok = (xv == xv) && __expf((xv - m) * inv_t) >= min_p;     // NaN keys never pass
+      if (ok) hi = mid; else lo = mid + 1;
+    }
+    cut = lo;
+  }
+  // ---- top_k: largest key t >= cut with count(>= t) >= top_k ----
+  if (top_k > 0 && top_k < V) {
+    count_mass_ge(sh, xr, V, cut, m, inv_t, &cnt, &mass);
+    if (cnt > top_k) {
+      uint32_t lo = cut, hi = km;          // invariant: count(>= lo) >= top_k
+      while (lo < hi) {
+        const uint32_t mid = (lo + hi + 1) >> 1;
+        count_mass_ge(sh, xr, V, mid, m, inv_t, &cnt, &mass);
+        if (cnt >= top_k) lo = mid; else hi = mid - 1;
+      }
+      cut = lo;
+    }
+  }
+  count_mass_ge(sh, xr, V, cut, m, inv_t, &cnt, &mass);
+  // ---- top_p: largest key t >= cut with mass(>= t) >= top_p * mass(>= cut) ----
+  if (top_p < 1.0f) {
+    const float target = top_p * mass;
+    uint32_t lo = cut, hi = km;            // invariant: mass(>= lo) >= target
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi + 1) >> 1;
+      float mm;
+      count_mass_ge(sh, xr, V, mid, m, inv_t, &cnt, &mm);
+      if (mm >= target) lo = mid; else hi = mid - 1;
+    }
+    cut = lo;
+    count_mass_ge(sh, xr, V, cut, m, inv_t, &cnt, &mass);
+  }
+  // ---- draw: inverse CDF over the kept elements in index order ----
+  const int chunk = (V + SFULL_THREADS - 1) / SFULL_THREADS;
+  const int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
+  float own = 0.f;
+  for (int i = i0; i < i1; ++i)
+    if (order_key(xr[i]) >= cut) own += __expf((__bfloat162float(xr[i]) - m) * inv_t);
+  // block exclusive scan of `own` (fixed order)
+  float incl = own;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  __syncthreads();
+  if (lane == 31) sh.fsum[warp] = incl;
+  if (tid == 0) sh.pick = -1;
+  __syncthreads();
+  float base = 0.f;
+  for (int w = 0; w < warp; ++w) base += sh.fsum[w];
+  float total = 0.f;
+  for (int w = 0; w < 32; ++w) total += sh.fsum[w];
+  const float excl = base + incl - own;
+  const float u = draw_uniform(seed, seed_dev, step ? step[r] : 0, r) * total;
+  if (own > 0.f && u >= excl && u < excl + own) {
+    float c = excl;
+    int pick = -1;
+    for (int i = i0; i < i1; ++i) {
+      if (order_key(xr[i]) >= cut) {
+        c += __expf((__bfloat162float(xr[i]) - m) * inv_t);
+        pick = i;                          // last kept element seen: the answer if rounding leaves u >= c
+        if (u < c) break;
+      }
+    }
+    sh.pick = pick;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int pick = sh.pick;
+    if (pick < 0) {                        // u fell on a boundary lost to rounding: take the arg-max
+      for (int i = 0; i < V; ++i)
+        if (order_key(xr[i]) == km) { pick = i; break; }
+    }
+    out[r] = pick;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -501,11 +689,24 @@ extern "C" int tahb_soft_embed_rows(const float* val, const int* idx, const int*
 }
 
 extern "C" int tahb_sample_topk(const float* val, const int* idx, int* out, int rows, int K, float temperature,
-                                float top_p, float min_p, unsigned long long seed, const int* step,
-                                cudaStream_t stream) {
+                                float top_p, float min_p, unsigned long long seed, const unsigned long long* seed_dev,
+                                const int* step, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (K > 128 || temperature <= 0.f) return -1;
-  sample_topk_kernel<<<(rows + 63) / 64, 64, 0, stream>>>(val, idx, out, rows, K, temperature, top_p, min_p, seed, step);
+  sample_topk_kernel<<<(rows + 63) / 64, 64, 0, stream>>>(val, idx, out, rows, K, temperature, top_p, min_p, seed,
+                                                          seed_dev, step);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// One token per row of bf16 logits x[rows, V] (row pitch ldx, a multiple of 8 elements with a 16-byte
+// aligned base), sampled over the whole vocabulary; top_k <= 0 means no top-k filter.
+extern "C" int tahb_sample_full(const void* x, int* out, int rows, int V, long long ldx, float temperature, int top_k,
+                                float top_p, float min_p, unsigned long long seed,
+                                const unsigned long long* seed_dev, const int* step, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (temperature <= 0.f || V <= 0 || (ldx % 8) || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+  sample_full_kernel<<<rows, SFULL_THREADS, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), out, V, ldx,
+                                                         temperature, top_k, top_p, min_p, seed, seed_dev, step);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

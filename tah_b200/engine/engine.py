@@ -64,8 +64,10 @@ class TaHEngine:
         self.deep_fraction = deep_fraction
         self.use_cuda_graph = use_cuda_graph and os.environ.get("TAH_B200_NO_GRAPH", "0") != "1"
         self.kv: Optional[PagedKVCache] = None
-        self._graph = None
-        self._graph_key = None
+        self._states = {}          # (rows, max_new, sampling, eos, override) -> tick state with its captured graph
+        self._calls = 0
+        self.graph_captures = 0
+        self.graph_reuses = 0
         self.hard_override: Optional[torch.Tensor] = None     # [rows, max_seq_len] int8: extra passes per position
         inner = self._decider()[1]
         thr = getattr(inner, "threshold", None)
@@ -206,7 +208,7 @@ class TaHEngine:
             self.kv = None
             torch.cuda.empty_cache()
             self.kv = PagedKVCache(geo, B, max(max_total, 1), self.max_iter, self.deep_fraction, dev)
-            self._graph = None
+            self._states.clear()          # captured ticks point into the old pools
         self.kv.reset()
         if self.tp is not None:
             self.tp.allocate(cfg.hidden_size, max(int(valid.sum()), B))
@@ -350,6 +352,8 @@ class TaHEngine:
             s.attn_ws = torch.empty(n_ws, dtype=torch.float32, device=dev)
         s.samp_v = torch.zeros(B, 128, dtype=torch.float32, device=dev)
         s.samp_i = i32(B, 128)
+        s.seed_dev = torch.zeros(1, dtype=torch.int64, device=dev)     # per-call sampling seed, read on the device
+        s.graph = None
         s.x_in, s.soft, s.h, s.xn = bf(B, H), bf(B, H), bf(B, H), bf(B, H)
         s.qkv = bf(B, w.qkv_out)
         s.q, s.o = bf(B, w.nq * cfg.head_dim), bf(B, w.nq * cfg.head_dim)
@@ -466,9 +470,14 @@ class TaHEngine:
         nxt = s.best
         if sampling is not None:
             kk = sampling["top_k"]
-            self._topk(cum, kk, None, s.samp_v, s.samp_i)
-            K.sample_topk(s.samp_v, s.samp_i, sampling["temperature"], sampling["top_p"], sampling["min_p"],
-                          sampling["seed"], step=s.pos, out=s.sampled)
+            if 0 < kk <= 128:
+                self._topk(cum, kk, None, s.samp_v, s.samp_i)
+                K.sample_topk(s.samp_v, s.samp_i, sampling["temperature"], sampling["top_p"], sampling["min_p"],
+                              0, step=s.pos, out=s.sampled, seed_dev=s.seed_dev)
+            else:
+                # no top-k filter (the reference's default top_k=0) or a set wider than the sorted route holds
+                K.sample_full(cum, sampling["temperature"], kk, sampling["top_p"], sampling["min_p"], 0, step=s.pos,
+                              out=s.sampled, seed_dev=s.seed_dev)
             nxt = s.sampled
         s.binding.tick_end(s.need_soft, nxt)
 
@@ -483,11 +492,38 @@ class TaHEngine:
     # ------------------------------------------------------------------------------------------
     # generate
     # ------------------------------------------------------------------------------------------
+    def _tick_state(self, B: int, max_new: int, sampling: Optional[dict], eos_token_id: Optional[int]):
+        """Tick buffers + captured graph for this (rows, max_new, sampling, eos, hard mask) shape.  A repeat call
+        with the same shape clears the scheduler state and replays the graph captured by the first one."""
+        samp_key = None if sampling is None else (sampling["temperature"], sampling["top_p"], sampling["min_p"],
+                                                  sampling["top_k"])
+        ov = self.hard_override
+        key = (B, max_new, samp_key, eos_token_id, None if ov is None else (ov.data_ptr(), tuple(ov.shape)))
+        s = self._states.get(key)
+        if s is None:
+            if len(self._states) >= 4:                      # keep a handful of shapes (batch buckets)
+                self._states.pop(next(iter(self._states)))
+            s = self._alloc_tick_buffers(B, max_new)
+            if sampling is not None and 0 < sampling["top_k"] <= 128:
+                s.samp_v = torch.zeros(B, sampling["top_k"], dtype=torch.float32, device=self.device)
+                s.samp_i = torch.zeros(B, sampling["top_k"], dtype=torch.int32, device=self.device)
+            s.ints[8] = -1 if eos_token_id is None else int(eos_token_id)
+            s.binding = K.TickStateBinding(s.tensors, s.ints)
+            self._states[key] = s
+        else:
+            for t in (s.tok, s.depth, s.pos, s.finished, s.n_out, s.out_tokens, s.iter_sum, s.cur_iters, s.slot,
+                      s.gate, s.tokens_done, s.need_soft, s.best, s.sampled):
+                t.zero_()
+        return s
+
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None, *,
                  max_new_tokens: int = 128, do_sample: bool = False, temperature: float = 1.0, top_p: float = 1.0,
-                 top_k: int = 0, min_p: float = 0.0, eos_token_id: Optional[int] = None, seed: int = 0,
+                 top_k: int = 0, min_p: float = 0.0, eos_token_id: Optional[int] = None, seed: Optional[int] = None,
                  max_ticks: Optional[int] = None, sync_every: int = 64, on_tick=None) -> GenerationResult:
+        """Prefill + decode.  ``seed=None`` draws the sampling seed from torch's global generator, so
+        ``set_all_seeds`` / ``torch.manual_seed`` govern it and successive calls differ (the reference's loop
+        samples with ``torch.multinomial`` on the global generator, ``tah/model/utils.py:84-125``)."""
         dev = self.device
         input_ids = input_ids.to(dev)
         if attention_mask is not None:
@@ -498,23 +534,32 @@ class TaHEngine:
         last_logits, lens, _ = self.prefill(input_ids, attention_mask, max_new_tokens)
         sampling = None
         if do_sample:
-            if not (0 < top_k <= 128):
-                raise NotImplementedError("engine sampling needs 0 < top_k <= 128; use the loop path otherwise")
-            sampling = dict(temperature=temperature, top_p=top_p, min_p=min_p, top_k=top_k, seed=seed)
-        s = self._alloc_tick_buffers(B, max_new_tokens)
+            if temperature <= 0:
+                raise ValueError("sampling needs temperature > 0")
+            if not (0 < top_k <= 128) and self.tp is not None:
+                raise NotImplementedError("tensor-parallel engine sampling needs 0 < top_k <= 128 "
+                                          "(the full-vocabulary sampler runs on one GPU)")
+            sampling = dict(temperature=float(temperature), top_p=float(top_p), min_p=float(min_p), top_k=int(top_k))
+            if seed is None:
+                seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+        self._calls += 1
+        s = self._tick_state(B, max_new_tokens, sampling, eos_token_id)
         if sampling is not None:
-            s.samp_v = torch.zeros(B, top_k, dtype=torch.float32, device=dev)
-            s.samp_i = torch.zeros(B, top_k, dtype=torch.int32, device=dev)
-        s.ints[8] = -1 if eos_token_id is None else int(eos_token_id)
-        s.binding = K.TickStateBinding(s.tensors, s.ints)
+            s.seed_dev.fill_(int(seed) & (2 ** 62 - 1))
         # first token from the prefill logits
         if sampling is None:
             first = self._argmax(last_logits)
-        else:
+        elif 0 < top_k <= 128:
             val = torch.zeros(B, top_k, dtype=torch.float32, device=dev)
             idx = torch.zeros(B, top_k, dtype=torch.int32, device=dev)
             self._topk(last_logits, top_k, None, val, idx)
-            first = K.sample_topk(val, idx, temperature, top_p, min_p, seed, step=lens.to(torch.int32) - 1)
+            first = K.sample_topk(val, idx, temperature, top_p, min_p, 0, step=lens.to(torch.int32) - 1,
+                                  seed_dev=s.seed_dev)
+        else:
+            ll = last_logits if last_logits.stride(0) % 8 == 0 else torch.nn.functional.pad(
+                last_logits, (0, -last_logits.shape[1] % 8))[:, :last_logits.shape[1]]
+            first = K.sample_full(ll, temperature, top_k, top_p, min_p, 0, step=lens.to(torch.int32) - 1,
+                                  seed_dev=s.seed_dev)
         s.pos.copy_(lens.to(torch.int32) - 1)
         s.need_soft.zero_()
         s.binding.tick_end(s.need_soft, first)          # emits token 1, pos = len, depth = 0
@@ -522,9 +567,11 @@ class TaHEngine:
         ev[1].record()
         ticks = 0
         limit = max_ticks if max_ticks is not None else max_new_tokens * self.max_iter + 1
-        if self.use_cuda_graph and limit > 0:
+        if self.use_cuda_graph and limit > 0 and s.graph is None:
             self._tick(s, sampling)            # eager tick: lazy one-time kernel setup happens outside capture
             ticks = 1
+            if on_tick is not None:
+                on_tick(ticks, s)
         run = self._tick_runner(s, sampling)
         while ticks < limit:
             run()
@@ -543,7 +590,8 @@ class TaHEngine:
         iters = (s.iter_sum.float() / s.n_out.clamp(min=1).float()).tolist()
         return GenerationResult(tokens=[row[:n] for row, n in zip(out, n_out)], iter_counts=iters, ticks=ticks,
                                 tokens_emitted=int(s.tokens_done.item()), prefill_ms=ev[0].elapsed_time(ev[1]),
-                                decode_ms=ev[1].elapsed_time(ev[2]))
+                                decode_ms=ev[1].elapsed_time(ev[2]),
+                                extra={"graph_captures": self.graph_captures, "graph_reuses": self.graph_reuses})
 
     def _tick_runner(self, s, sampling):
         if not self.use_cuda_graph:
@@ -552,6 +600,9 @@ class TaHEngine:
                 self._tick(s, sampling)
                 self.kernel_launches_per_tick = K.launch_count - before
             return run_eager
+        if s.graph is not None:
+            self.graph_reuses += 1
+            return s.graph.replay
         # Capture records the launches of one tick without running them.  Everything a tick touches
         # was allocated beforehand, so replays reuse the same addresses.
         side = torch.cuda.Stream()
@@ -563,18 +614,73 @@ class TaHEngine:
                 self._tick(s, sampling)
         self.kernel_launches_per_tick = K.launch_count - before      # own kernels recorded in the graph
         torch.cuda.current_stream().wait_stream(side)
-        self._graph = graph
+        s.graph = graph
+        self.graph_captures += 1
         return graph.replay
+
+    # ------------------------------------------------------------------------------------------
+    # synthetic context (benchmarks)
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def fast_forward(self, s, context: int) -> None:
+        """Benchmark aid: make every row look as if it had already processed ``context`` tokens, so that ticks
+        can be timed at a chosen decode depth without generating up to it.  The page tables of every depth
+        get the pages a row of that length owns (taken from the free stacks exactly as a tick would), the
+        lengths and positions are advanced, and the skipped tokens are counted as emitted.  The K/V content of
+        the skipped positions is whatever the pools hold (zeros after allocation): the kernels' work per tick
+        depends on the lengths only.  Call between ticks, with no tick in flight."""
+        kv, ps, dev = self.kv, self.page_size, self.device
+        B = s.pos.shape[0]
+        torch.cuda.synchronize()
+        pos_new = torch.full_like(s.pos, int(context))
+        delta = (pos_new - s.pos).clamp(min=0)
+        targets = [pos_new + (s.depth > 0).to(torch.int32)]
+        for d in range(1, kv.n_depths):
+            if self.hard_override is not None:
+                cnt = (self.hard_override[:B, :context] >= d).sum(1).to(torch.int32)
+            else:
+                cnt = kv.len[d].clone()
+            targets.append(cnt + (s.depth > d).to(torch.int32))
+        rows = torch.arange(B, device=dev)
+        for d, tgt in enumerate(targets):
+            tgt = torch.maximum(tgt, kv.len[d]).to(torch.int64)
+            have = (kv.len[d].to(torch.int64) + ps - 1) // ps
+            need = (tgt + ps - 1) // ps - have
+            total, free = int(need.sum()), int(kv.free_count[d])
+            if total > free or int(((tgt + ps - 1) // ps).max()) > kv.max_pages[d]:
+                raise RuntimeError(f"KV pool of depth {d} too small for a context of {context} tokens")
+            if total > 0:
+                first = torch.cumsum(need, 0) - need
+                row_of_page = torch.repeat_interleave(rows, need)
+                rank = torch.arange(total, device=dev)
+                page_ids = kv.free_stack[d][(free - 1 - rank)]
+                col = have[row_of_page] + rank - first[row_of_page]
+                kv.page_table[d][row_of_page, col] = page_ids
+                kv.free_count[d].fill_(free - total)
+            kv.len[d].copy_(tgt.to(torch.int32))
+        s.n_out += delta
+        s.tokens_done += int(delta.sum())
+        s.pos.copy_(torch.maximum(pos_new, s.pos))
+        torch.cuda.synchronize()
 
 
 _ENGINES = {}
 
 
+def _lora_versions(model) -> tuple:
+    """Version counters of the weights the engine copied or re-laid at construction (LoRA factors always,
+    base weights when they are not already contiguous bf16)."""
+    return tuple(p._version for p in model.simple_base_model.parameters())
+
+
 def get_engine(model, **kw) -> TaHEngine:
-    """One cached engine per model instance."""
+    """One cached engine per model instance.  The engine keeps pre-scaled, re-laid copies of the LoRA factors,
+    so it is rebuilt when those parameters were modified in place since it was made (e.g. by an optimizer step)."""
     key = id(model)
-    eng = _ENGINES.get(key)
-    if eng is None:
-        eng = TaHEngine(model, **kw)
-        _ENGINES[key] = eng
+    ver = _lora_versions(model)
+    hit = _ENGINES.get(key)
+    if hit is not None and hit[1] == ver and hit[0].model is model:
+        return hit[0]
+    eng = TaHEngine(model, **kw)
+    _ENGINES[key] = (eng, ver)
     return eng

@@ -42,7 +42,7 @@ class PagedKVCache:
         for d in range(n_depths):
             pages = rows * ppr if d == 0 else max(rows * 2, int(rows * ppr * deep_fraction))
             self.n_pages.append(pages)
-            self.pool.append(torch.empty(geo.n_layers, pages, 2, geo.n_kv_heads, geo.page_size, geo.head_dim,
+            self.pool.append(torch.zeros(geo.n_layers, pages, 2, geo.n_kv_heads, geo.page_size, geo.head_dim,
                                          dtype=dtype, device=device))
             self.page_table.append(torch.zeros(rows, ppr, dtype=torch.int32, device=device))
             self.len.append(torch.zeros(rows, dtype=torch.int32, device=device))

@@ -474,13 +474,32 @@ def soft_embed_rows(val, idx, E, flag=None, out=None):
     return out
 
 
-def sample_topk(val, idx, temperature: float, top_p: float, min_p: float, seed: int, step=None, out=None):
+def sample_topk(val, idx, temperature: float, top_p: float, min_p: float, seed: int, step=None, out=None,
+                seed_dev: Optional[torch.Tensor] = None):
+    """Draw one token per row from a sorted top-k set.  ``seed_dev`` (optional int64 device scalar) is mixed
+    into the seed on the device, so a captured launch can be replayed with a fresh seed."""
     rows, K = val.shape
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=val.device)
     _rc(lib().tahb_sample_topk(_p(val), _p(idx), _p(out), c_int(rows), c_int(K), c_float(temperature), c_float(top_p),
-                               c_float(min_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _p(step), _stream()),
+                               c_float(min_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _p(seed_dev), _p(step),
+                               _stream()),
         "tahb_sample_topk")
+    return out
+
+
+def sample_full(x, temperature: float, top_k: int, top_p: float, min_p: float, seed: int, step=None, out=None,
+                seed_dev: Optional[torch.Tensor] = None):
+    """Draw one token per row of bf16 logits ``x [rows, V]`` over the whole vocabulary (temperature ->
+    softmax -> min_p -> top_k -> top_p -> draw, reference ``tah/model/utils.py:84-125``); ``top_k <= 0``
+    means no top-k filter.  Used where the sorted top-k route (``top_k <= 128``) does not apply."""
+    _check_bf16_2d(x, "x")
+    rows, V = x.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=x.device)
+    _rc(lib().tahb_sample_full(_p(x), _p(out), c_int(rows), c_int(V), c_ll(x.stride(0)), c_float(temperature),
+                               c_int(top_k), c_float(top_p), c_float(min_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+                               _p(seed_dev), _p(step), _stream()), "tahb_sample_full")
     return out
 
 
