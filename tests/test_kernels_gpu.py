@@ -477,6 +477,56 @@ def test_sampler_topk_distribution():
     assert torch.allclose(freq[:n], expect, atol=0.03)
 
 
+@pytest.mark.parametrize("top_k,top_p,min_p", [(0, 1.0, 0.0), (0, 0.9, 0.0), (5, 1.0, 0.0), (200, 0.8, 0.02), (0, 1.0, 0.05)])
+def test_sampler_full_vocabulary_distribution(top_k, top_p, min_p):
+    """Full-vocabulary sampler against the filtered distribution of the PyTorch statement of the same
+    order (temperature -> softmax -> min_p -> top_k -> top_p)."""
+    Kc = _cuda()
+    rows, V, T = 8192, 1000, 0.8
+    g = torch.Generator().manual_seed(1)
+    base = (torch.randn(V, generator=g) * 2.0).to(torch.bfloat16)
+    x = base.cuda().repeat(rows, 1).contiguous()
+    step = torch.arange(rows, dtype=torch.int32, device="cuda")
+    out = Kc.sample_full(x, T, top_k, top_p, min_p, seed=99, step=step)
+    p = torch.softmax(base.float() / T, -1)
+    if min_p > 0:
+        p = torch.where(p >= min_p * p.max(), p, torch.zeros_like(p))
+        p = p / p.sum()
+    if top_k > 0:
+        kth = torch.topk(p, min(top_k, V)).values[-1]
+        p = torch.where(p < kth, torch.zeros_like(p), p)
+        p = p / p.sum()
+    if top_p < 1.0:
+        sp, si = torch.sort(p, descending=True)
+        drop = sp.cumsum(0) > top_p
+        drop = torch.cat((torch.zeros(1, dtype=torch.bool), drop[:-1]))
+        p[si[drop]] = 0
+        p = p / p.sum()
+    freq = torch.bincount(out.long().cpu(), minlength=V).float() / rows
+    assert int(out.min()) >= 0 and int(out.max()) < V
+    # nothing outside the kept set (ties at a threshold are kept by both statements)
+    assert float(freq[p == 0].sum()) <= 1e-3
+    assert float((freq - p).abs().max()) < 0.02
+    # same seed and step -> same draw; another seed -> another sample
+    again = Kc.sample_full(x, T, top_k, top_p, min_p, seed=99, step=step)
+    other = Kc.sample_full(x, T, top_k, top_p, min_p, seed=100, step=step)
+    assert torch.equal(out, again) and not torch.equal(out, other)
+
+
+def test_sampler_device_seed_word_changes_the_draw():
+    Kc = _cuda()
+    rows, K = 512, 8
+    val = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -2.0, -3.0, -9.0], device="cuda").repeat(rows, 1)
+    idx = torch.arange(K, dtype=torch.int32, device="cuda").repeat(rows, 1)
+    step = torch.arange(rows, dtype=torch.int32, device="cuda")
+    word = torch.zeros(1, dtype=torch.int64, device="cuda")
+    a = Kc.sample_topk(val, idx, 1.0, 1.0, 0.0, 0, step=step, seed_dev=word).clone()
+    b = Kc.sample_topk(val, idx, 1.0, 1.0, 0.0, 0, step=step, seed_dev=word).clone()
+    word.fill_(12345)
+    c = Kc.sample_topk(val, idx, 1.0, 1.0, 0.0, 0, step=step, seed_dev=word)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+
+
 def test_zero_adamw_cuda_single_gpu_matches_fp32_adamw():
     """Fused reduce + AdamW + broadcast kernels (world size 1) against torch.optim.AdamW on fp32 masters."""
     from tah_b200.parallel.zero import ZeroAdamW

@@ -15,21 +15,42 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "baseline", "_ref")
 
 
-def _reference():
+def _purge_tah_modules():
+    for name in [n for n in sys.modules if n == "tah" or n.startswith("tah.")]:
+        del sys.modules[name]
+
+
+@pytest.fixture
+def reference():
+    """Imports the reference's ``tah`` (not this repository's alias package of the same name) for one test and
+    removes it again afterwards."""
     if not os.path.isdir(os.path.join(REF, "tah")):
         pytest.skip("reference package not installed under baseline/_ref")
+    added = []
     try:
         import peft  # noqa: F401
     except ImportError:
-        sys.path.insert(0, os.path.join(ROOT, "baseline", "peft_standin"))
-    if REF not in sys.path:
-        sys.path.insert(0, REF)
+        added.append(os.path.join(ROOT, "baseline", "peft_standin"))
+    added.append(REF)
+    _purge_tah_modules()
+    for p in added:
+        sys.path.insert(0, p)
     try:
-        import tah
-        from transformers import AutoModelForCausalLM, Qwen3Config
-    except Exception as exc:  # pragma: no cover - environment dependent
-        pytest.skip(f"reference does not import here: {type(exc).__name__}: {exc}")
-    return tah, AutoModelForCausalLM, Qwen3Config
+        try:
+            import tah
+            from transformers import AutoModelForCausalLM, Qwen3Config
+        except Exception as exc:  # pragma: no cover - environment dependent
+            pytest.skip(f"reference does not import here: {type(exc).__name__}: {exc}")
+        assert os.path.realpath(tah.__file__).startswith(os.path.realpath(REF))
+        yield tah, AutoModelForCausalLM, Qwen3Config
+    finally:
+        for p in added:
+            if p in sys.path:
+                sys.path.remove(p)
+        _purge_tah_modules()
+        for name in [n for n in sys.modules if n == "peft" or n.startswith("peft.")]:
+            if "peft_standin" in (getattr(sys.modules[name], "__file__", "") or ""):
+                del sys.modules[name]
 
 
 def _ref_model(tah, AutoModelForCausalLM, Qwen3Config, max_iter=2):
@@ -65,8 +86,8 @@ def _coin(base_cls, p, seed):
     return Coin()
 
 
-def test_checkpoint_from_reference_loads_here_and_forward_matches(tmp_path):
-    tah, AM, QC = _reference()
+def test_checkpoint_from_reference_loads_here_and_forward_matches(tmp_path, reference):
+    tah, AM, QC = reference
     from tah_b200 import TaHForCausalLM
     ref = _ref_model(tah, AM, QC)
     ref.save_pretrained(str(tmp_path / "ck"))
@@ -84,8 +105,8 @@ def test_checkpoint_from_reference_loads_here_and_forward_matches(tmp_path):
     torch.testing.assert_close(b.loss, a.loss, atol=1e-5, rtol=1e-5)
 
 
-def test_checkpoint_written_here_loads_in_reference(tmp_path):
-    tah, AM, QC = _reference()
+def test_checkpoint_written_here_loads_in_reference(tmp_path, reference):
+    tah, AM, QC = reference
     from tests.helpers import tiny_tah
     mine = tiny_tah().eval()
     mine.save_pretrained(str(tmp_path / "ck"))
@@ -100,8 +121,8 @@ def test_checkpoint_written_here_loads_in_reference(tmp_path):
     torch.testing.assert_close(b.logits, a.logits, atol=3e-4, rtol=1e-4)
 
 
-def test_greedy_decode_with_seeded_hard_tokens_matches_reference(tmp_path):
-    tah, AM, QC = _reference()
+def test_greedy_decode_with_seeded_hard_tokens_matches_reference(tmp_path, reference):
+    tah, AM, QC = reference
     from tah.model.iter_decider import IterDecider as RefDecider
     from tah.model.utils import TaHForCasualLM_generate as ref_generate
     from tah_b200 import TaHForCausalLM

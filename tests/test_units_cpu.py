@@ -320,3 +320,20 @@ def test_gemm_planner_choices_cpu():
     assert plan_gemm(256, 2048, 6144)[1] > 1            # few feature tiles, long K: split
     assert plan_gemm(8192, 4096, 2048)[1] == 1          # 1024 CTAs already
     assert plan_gemm(256, 151936, 2048)[1] == 1         # LM head
+
+
+def test_reference_import_names_resolve_to_this_package():
+    """``import tah`` (the reference's package name) serves the same module objects as ``tah_b200``."""
+    import importlib
+    import tah
+    import tah_b200
+    assert tah.TaHForCausalLM is tah_b200.TaHForCausalLM
+    for sub in ("model", "model.tah_model", "model.iter_decider", "model.loss", "model.utils", "model.causal_cache",
+                "model.tah_config", "train", "utils", "evaluate", "evaluate.backends", "evaluate.jobs",
+                "evaluate.datasets", "evaluate.matheval", "evaluate.codeeval"):
+        assert importlib.import_module("tah." + sub) is importlib.import_module("tah_b200." + sub)
+    from tah.model.tah_model import additive_logits_update, gather_active, scatter_back, topk_softmax_input_update  # noqa: F401
+    from tah.model.utils import TaHForCasualLM_generate, sample_next_token, set_all_seeds  # noqa: F401
+    from tah.train import CustomTaHDataCollator, CustomTaHTrainer, LoggerCallback, fixed_cross_entropy  # noqa: F401
+    from tah.utils import preprocess_dataset  # noqa: F401
+    from tah.evaluate.backends import cleanup, setup_backend, setup_hf, setup_sglang, setup_tah, time_inference, warmup  # noqa: F401
