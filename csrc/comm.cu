@@ -542,6 +542,122 @@ __global__ void __launch_bounds__(256) shard_gather_push_kernel(const ShardGathe
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Vocabulary-parallel top-k / arg-max merge without a library collective.
+//
+// Every rank holds, per row, a sorted (value desc, index asc) list of k candidates over its
+// vocabulary shard.  One launch per rank, one CTA per row:
+//   1. CTA r stores its row's k (value, global index) pairs into slot [epoch parity][rank][r] of every
+//      rank's symmetric exchange buffer (plain peer stores over NVLink), fences, and adds 1 to word r of
+//      every rank's arrival array;
+//   2. it waits (bounded) until its own arrival word r has reached world * epoch, i.e. CTA r of every rank
+//      has delivered this call's candidates;
+//   3. it merges the `world` sorted lists: each candidate's global rank is its own index plus, for every
+//      other list, the number of entries that precede it (binary search), and the first k go to the output.
+// The epoch is a per-row counter in local memory that the kernel advances itself, so the launch can be
+// replayed from a CUDA graph; a peer can be at most one call ahead of a CTA that is still merging, hence
+// the two slots.  k <= 128, world <= 8.
+// ---------------------------------------------------------------------------------------------
+constexpr int MERGE_MAX_K = 128;
+
+struct TopkMergeParams {
+  float* xval[COMM_MAX_RANKS];        // every rank's exchange buffer: values [2][world][rows][MERGE_MAX_K]
+  int* xidx[COMM_MAX_RANKS];          // indices, same layout
+  uint32_t* arrive[COMM_MAX_RANKS];   // every rank's arrival words [rows]
+  uint32_t* epoch;                    // local [rows]
+  const float* val;                   // local candidates [rows, ldv]
+  const int* idx;
+  float* out_val;                     // merged [rows, ldo] (may be nullptr when only indices are wanted)
+  int* out_idx;
+  int* status;
+  int rows, k, ldv, ldo, rank, world, vocab_lo;
+  unsigned long long wait_limit_ns;
+};
+
+__device__ __forceinline__ bool cand_before(float va, int ia, float vb, int ib) {
+  return va > vb || (va == vb && ia < ib);
+}
+
+__global__ void __launch_bounds__(256) tp_topk_merge_kernel(const TopkMergeParams p) {
+  __shared__ float sv[COMM_MAX_RANKS * MERGE_MAX_K];
+  __shared__ int si[COMM_MAX_RANKS * MERGE_MAX_K];
+  __shared__ int s_ok;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int k = p.k, W = p.world;
+  const uint32_t ep = p.epoch[r] + 1;
+  const int par = ep & 1;
+  // 1. deliver this rank's candidates to every rank (own copy included)
+  for (int j = tid; j < k * W; j += blockDim.x) {
+    const int q = j / k, c = j % k;
+    const size_t off = (((size_t)par * W + p.rank) * p.rows + r) * MERGE_MAX_K + c;
+    p.xval[q][off] = p.val[(size_t)r * p.ldv + c];
+    p.xidx[q][off] = p.idx[(size_t)r * p.ldv + c] + p.vocab_lo;
+  }
+  __syncthreads();
+  if (tid < W) {
+    __threadfence_system();
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.arrive[tid] + r), "r"(1u) : "memory");
+  }
+  // 2. wait for every rank's delivery of this call
+  if (tid == 0) {
+    const uint32_t want = ep * (uint32_t)W;
+    const uint32_t* mine = p.arrive[p.rank] + r;
+    const unsigned long long limit = p.wait_limit_ns ? p.wait_limit_ns : WAIT_TIMEOUT_NS;
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    int ok = 1;
+    while ((int32_t)(ld_acquire_sys(mine) - want) < 0) {
+      if ((++spins & 0xff) == 0) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > limit) {
+          atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER_FLAG);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    __threadfence_system();
+    s_ok = ok;
+    p.epoch[r] = ep;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  // 3. merge
+  const float* lv = p.xval[p.rank] + ((size_t)par * W * p.rows + r) * MERGE_MAX_K;
+  const int* li = p.xidx[p.rank] + ((size_t)par * W * p.rows + r) * MERGE_MAX_K;
+  const size_t qstride = (size_t)p.rows * MERGE_MAX_K;
+  for (int j = tid; j < k * W; j += blockDim.x) {
+    const int q = j / k, c = j % k;
+    sv[q * MERGE_MAX_K + c] = __uint_as_float(ld_relaxed_sys(reinterpret_cast<const uint32_t*>(lv + q * qstride + c)));
+    si[q * MERGE_MAX_K + c] = (int)ld_relaxed_sys(reinterpret_cast<const uint32_t*>(li + q * qstride + c));
+  }
+  __syncthreads();
+  for (int j = tid; j < k * W; j += blockDim.x) {
+    const int q = j / k, c = j % k;
+    const float v = sv[q * MERGE_MAX_K + c];
+    const int ix = si[q * MERGE_MAX_K + c];
+    int rank_g = c;
+    for (int o = 0; o < W; ++o) {
+      if (o == q) continue;
+      // number of entries of list o that come before (v, ix): lists are sorted, binary search
+      int lo = 0, hi = k;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (cand_before(sv[o * MERGE_MAX_K + mid], si[o * MERGE_MAX_K + mid], v, ix)) lo = mid + 1;
+        else hi = mid;
+      }
+      rank_g += lo;
+    }
+    if (rank_g < k) {
+      if (p.out_val != nullptr) p.out_val[(size_t)r * p.ldo + rank_g] = v;
+      p.out_idx[(size_t)r * p.ldo + rank_g] = ix;
+    }
+  }
+}
+
 }  // namespace tahb
 
 // src: local shard (`bytes`, a multiple of 16); dst: `world` pointers to the place of this rank's shard in
@@ -569,4 +685,28 @@ extern "C" int tahb_shard_gather_push(const void* src, void* const* dst, void* m
   p.status = status;
   shard_gather_push_kernel<<<grid, 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Merge per-shard sorted top-k candidate lists over the ranks of a tensor-parallel group (see
+// tp_topk_merge_kernel).  xval / xidx / arrive: the `world` peer pointers of the symmetric exchange
+// buffers; epoch: local per-row counters; val / idx: this rank's [rows, ldv] candidates (local indices,
+// vocab_lo is added); out_val (optional) / out_idx: merged [rows, ldo] lists with global indices.
+extern "C" int tahb_tp_topk_merge(void* const* xval, void* const* xidx, void* const* arrive, void* epoch,
+                                  const float* val, const int* idx, float* out_val, int* out_idx, int* status,
+                                  int rows, int k, int ldv, int ldo, int rank, int world, int vocab_lo,
+                                  cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (k < 1 || k > MERGE_MAX_K || world < 1 || world > COMM_MAX_RANKS) return -1;
+  TopkMergeParams p;
+  for (int q = 0; q < COMM_MAX_RANKS; ++q) {
+    p.xval[q] = q < world ? reinterpret_cast<float*>(xval[q]) : nullptr;
+    p.xidx[q] = q < world ? reinterpret_cast<int*>(xidx[q]) : nullptr;
+    p.arrive[q] = q < world ? reinterpret_cast<uint32_t*>(arrive[q]) : nullptr;
+  }
+  p.epoch = reinterpret_cast<uint32_t*>(epoch);
+  p.val = val; p.idx = idx; p.out_val = out_val; p.out_idx = out_idx; p.status = status;
+  p.rows = rows; p.k = k; p.ldv = ldv; p.ldo = ldo; p.rank = rank; p.world = world; p.vocab_lo = vocab_lo;
+  p.wait_limit_ns = peer_wait_limit_ns();
+  cudaError_t e = launch_chain(tp_topk_merge_kernel, dim3(rows), dim3(256), 0, stream, p);
+  return e == cudaSuccess ? 0 : -3;
 }

@@ -40,6 +40,9 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 // 1 unless the environment variable TAH_B200_PDL is "0" (defined in elementwise.cu)
 int pdl_enabled();
+// Limit of the waits on flags that another GPU advances, in nanoseconds (defined in elementwise.cu; default
+// WAIT_TIMEOUT_NS, changed with tahb_set_peer_wait_limit_ns).  Kernels receive it as a launch parameter.
+unsigned long long peer_wait_limit_ns();
 
 // Launch `kern` with (or without) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
@@ -130,7 +133,9 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Bounded wait of ONE thread until flag[q] has reached target[q] (wrap-around safe) for every q <
 // world.  The flags are local device memory that peers advance over NVLink after they have stored
 // rows into this GPU's memory; target[] is local state.  Returns false after a timeout (status set).
-__device__ __forceinline__ bool wait_peer_rows(const uint32_t* flag, const uint32_t* target, int world, int* status) {
+__device__ __forceinline__ bool wait_peer_rows(const uint32_t* flag, const uint32_t* target, int world, int* status,
+                                               unsigned long long limit_ns = WAIT_TIMEOUT_NS) {
+  if (limit_ns == 0) limit_ns = WAIT_TIMEOUT_NS;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
   for (int q = 0; q < world; ++q) {
@@ -142,7 +147,7 @@ __device__ __forceinline__ bool wait_peer_rows(const uint32_t* flag, const uint3
       if ((++spins & 0xff) == 0) {
         const unsigned long long now = globaltimer_ns();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > WAIT_TIMEOUT_NS) {
+        else if (now - t0 > limit_ns) {
           atomicCAS(status, 0, STATUS_TIMEOUT_PEER_FLAG);
           return false;
         }

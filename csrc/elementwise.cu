@@ -69,6 +69,135 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const __nv_bfloat16* __res
 }
 
 // ---------------------------------------------------------------------------------------------
+// RMSNorm fused with the LoRA-A product of the rows that are at depth >= 1 (decode tick):
+//   y[r] = w * bf16(x[r] * rstd)                     for every row
+//   T[r] = gate[r] ? y[r] A^T : 0                    (A: [R, H], T: [M, ldt])
+// Grid (rows, 1 + NS), 256 threads.  CTA (r, 0) normalises row r, stores y and, when the row is gated
+// off, clears T[r].  CTAs (r, 1 + s) exist for the LoRA-A product: for a gated row each of the NS
+// slices normalises the row again into shared memory (4 KB from L2) and its eight warps compute
+// R / NS of the outputs, three at a time with all loads of a step issued before the arithmetic, so
+// that the product is spread over NS x 8 warps instead of running in one CTA; for the other rows
+// they return at once.  Same summation order per output as lora_a_rows_kernel.  Saves the separate
+// LoRA-A launch in front of the QKV and gate/up projections.
+// ---------------------------------------------------------------------------------------------
+constexpr int NORM_LORA_SLICES = 8;
+
+__global__ void __launch_bounds__(256) rmsnorm_lora_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ y, int H, long long ldx,
+                                                           long long ldy, float eps, const int* __restrict__ gate,
+                                                           const __nv_bfloat16* __restrict__ A,
+                                                           __nv_bfloat16* __restrict__ T, int R, long long ldt) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ uint4 srow[];            // H / 8 vectors: the normalised row (LoRA slices only)
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const int slice = (int)blockIdx.y - 1;     // -1: the norm CTA
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool gated = gate != nullptr && gate[row] != 0;
+  if (slice >= 0 && !gated) return;
+  const int nvec = H / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+  constexpr int VPT = 4;                     // H <= 256 * 8 * 4 = 8192
+  uint4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = tid + i * 256;
+    if (idx < nvec) {
+      v[i] = xr[idx];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += red[k];   // fixed order: every CTA of a row gets the same rstd
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = tid + i * 256;
+    if (idx < nvec) {
+      uint4 wv = wr[idx];
+      uint4 o;
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        float2 g = __bfloat1622float2(wh[j]);
+        oh[j] = __floats2bfloat162_rn(g.x * bf16_round(f.x * rstd), g.y * bf16_round(f.y * rstd));
+      }
+      if (slice < 0) yr[idx] = o;
+      else srow[idx] = o;
+    }
+  }
+  __nv_bfloat16* out = T + (size_t)row * ldt;
+  if (slice < 0) {
+    if (!gated)
+      for (int j = tid; j < R; j += 256) out[j] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  __syncthreads();
+  // outputs [j0, j1) of this slice, three per warp and step
+  const int per = (R + NORM_LORA_SLICES - 1) / NORM_LORA_SLICES;
+  const int j0 = slice * per, j1 = min(R, j0 + per);
+  for (int j = j0 + warp * 3; j < j1; j += 24) {
+    const int ja = j, jb = min(j + 1, j1 - 1), jc = min(j + 2, j1 - 1);
+    const uint4* a0 = reinterpret_cast<const uint4*>(A + (size_t)ja * H);
+    const uint4* a1 = reinterpret_cast<const uint4*>(A + (size_t)jb * H);
+    const uint4* a2 = reinterpret_cast<const uint4*>(A + (size_t)jc * H);
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
+    for (int i0 = lane; i0 < nvec; i0 += 128) {
+      uint4 av0[4], av1[4], av2[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {          // 12 independent 16-byte loads before any arithmetic
+        const int i = i0 + u * 32;
+        if (i < nvec) { av0[u] = a0[i]; av1[u] = a1[i]; av2[u] = a2[i]; }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 32;
+        if (i < nvec) {
+          const uint4 xv = srow[i];
+          const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+          const __nv_bfloat162* ah0 = reinterpret_cast<const __nv_bfloat162*>(&av0[u]);
+          const __nv_bfloat162* ah1 = reinterpret_cast<const __nv_bfloat162*>(&av1[u]);
+          const __nv_bfloat162* ah2 = reinterpret_cast<const __nv_bfloat162*>(&av2[u]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 a = __bfloat1622float2(xh[q]);
+            const float2 b0 = __bfloat1622float2(ah0[q]), b1 = __bfloat1622float2(ah1[q]), b2 = __bfloat1622float2(ah2[q]);
+            acc0 += a.x * b0.x + a.y * b0.y;
+            acc1 += a.x * b1.x + a.y * b1.y;
+            acc2 += a.x * b2.x + a.y * b2.y;
+          }
+        }
+      }
+    }
+    acc0 = warp_sum(acc0);
+    acc1 = warp_sum(acc1);
+    acc2 = warp_sum(acc2);
+    if (lane == 0) {
+      out[ja] = __float2bfloat16_rn(acc0);
+      if (j + 1 < j1) out[jb] = __float2bfloat16_rn(acc1);
+      if (j + 2 < j1) out[jc] = __float2bfloat16_rn(acc2);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Per-head QK RMSNorm + rotate-half RoPE + KV write.  One warp per (token, head).
 //   qkv      [M, (nq + 2 nkv) * HD]
 //   q_out    [M, nq * HD]
@@ -171,6 +300,23 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(const QkvRopeParam
 }
 
 // ---------------------------------------------------------------------------------------------
+// RoPE table of a pass: cs[t, 0 .. HD/2) = bf16(cos(pos[t] * theta^(-2j/HD))), cs[t, HD/2 .. HD) = bf16(sin(..)).
+// The positions of a pass are the same for every layer, so the transcendental work is done once per pass
+// (once per decode tick) and the fused QKV epilogue of each layer only loads the row.
+// ---------------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ pos, __nv_bfloat16* __restrict__ cs, int M, int HD,
+                                  float log2_theta) {
+  const int half = HD / 2;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= (long long)M * half) return;
+  const int t = (int)(i / half), j = (int)(i % half);
+  const float inv = exp2f(-(2.0f * (float)j / (float)HD) * log2_theta);
+  const float ang = (float)pos[t] * inv;
+  cs[(size_t)t * HD + j] = __float2bfloat16_rn(cosf(ang));
+  cs[(size_t)t * HD + half + j] = __float2bfloat16_rn(sinf(ang));
+}
+
+// ---------------------------------------------------------------------------------------------
 // Embedding gather: out[r] = E[tok[r]]  (tok < 0 -> zeros)
 // ---------------------------------------------------------------------------------------------
 __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ E, const int* __restrict__ tok,
@@ -192,7 +338,7 @@ __global__ void __launch_bounds__(256) lora_a_rows_dense_kernel(const __nv_bfloa
                                                           __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
                                                           int K, int R, long long ldx, long long ldt,
                                                           const uint32_t* wait_flag, const uint32_t* wait_target,
-                                                          int wait_world, int* status) {
+                                                          int wait_world, int* status, unsigned long long wait_limit) {
   // grid (rows, ceil(R / 8)): a CTA owns 8 outputs of one row, one per warp, so that a gated row's
   // product is spread over R / 8 CTAs instead of running serially in one
   pdl_launch_dependents();
@@ -207,7 +353,7 @@ __global__ void __launch_bounds__(256) lora_a_rows_dense_kernel(const __nv_bfloa
     return;
   }
   if (wait_world > 0) {     // tensor parallel: x rows are broadcast by their owners (see comm.cu)
-    if (lane == 0) wait_peer_rows(wait_flag, wait_target, wait_world, status);
+    if (lane == 0) wait_peer_rows(wait_flag, wait_target, wait_world, status, wait_limit);
     __syncwarp();
   }
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
@@ -238,7 +384,7 @@ __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ T, const int* __restrict__ gate,
                                                           int M, int K, int R, long long ldx, long long ldt,
                                                           const uint32_t* wait_flag, const uint32_t* wait_target,
-                                                          int wait_world, int* status) {
+                                                          int wait_world, int* status, unsigned long long wait_limit) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ int s_rows[1024];
@@ -284,24 +430,37 @@ __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* _
   }
   if ((int)blockIdx.x >= n) return;
   if (wait_world > 0) {       // tensor parallel: x rows are broadcast by their owners (see comm.cu)
-    if (tid == 0) wait_peer_rows(wait_flag, wait_target, wait_world, status);
+    if (tid == 0) wait_peer_rows(wait_flag, wait_target, wait_world, status, wait_limit);
     __syncthreads();
   }
   const int j = jb * 8 + warp;
   if (j >= R) return;
   const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)j * K);
+  const int nvec = K / 8;
   for (int k = blockIdx.x; k < n; k += gridDim.x) {
     const int r = s_rows[k];
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
     float acc = 0.f;
-    for (int i = lane; i < K / 8; i += 32) {
-      uint4 xv = xr[i], av = ar[i];
-      const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
-      const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
+    // the product is latency-bound (one warp, operands in L2): issue the 16 loads of eight steps before
+    // their arithmetic; the summation order is that of the plain loop
+    for (int i0 = lane; i0 < nvec; i0 += 256) {
+      uint4 xv[8], av[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float2 a = __bfloat1622float2(xh[q]), b = __bfloat1622float2(ah[q]);
-        acc += a.x * b.x + a.y * b.y;
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 32;
+        if (i < nvec) { xv[u] = xr[i]; av[u] = ar[i]; }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (i0 + u * 32 < nvec) {
+          const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv[u]);
+          const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av[u]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float2 a = __bfloat1622float2(xh[q]), b = __bfloat1622float2(ah[q]);
+            acc += a.x * b.x + a.y * b.y;
+          }
+        }
       }
     }
     acc = warp_sum(acc);
@@ -391,6 +550,9 @@ __global__ void __launch_bounds__(1024) logits_post_kernel(const __nv_bfloat16* 
   }
 }
 
+static unsigned long long g_peer_wait_limit_ns = WAIT_TIMEOUT_NS;
+unsigned long long peer_wait_limit_ns() { return g_peer_wait_limit_ns; }
+
 int pdl_enabled() {
   static int on = -1;
   if (on < 0) {
@@ -403,6 +565,15 @@ int pdl_enabled() {
 }  // namespace tahb
 
 using namespace tahb;
+
+// Sets how long a kernel waits for a flag that a peer GPU advances before it records
+// STATUS_TIMEOUT_PEER_FLAG and runs to its end (0 restores the default of 2 s).  Applies to launches made
+// after the call; returns the previous value.
+extern "C" unsigned long long tahb_set_peer_wait_limit_ns(unsigned long long ns) {
+  const unsigned long long prev = g_peer_wait_limit_ns;
+  g_peer_wait_limit_ns = ns == 0 ? WAIT_TIMEOUT_NS : ns;
+  return prev;
+}
 
 extern "C" int tahb_rmsnorm(const void* x, const void* w, void* y, int M, int H, long long ldx, long long ldy,
                             float eps, cudaStream_t stream) {
@@ -418,6 +589,19 @@ extern "C" int tahb_rmsnorm(const void* x, const void* w, void* y, int M, int H,
   else if (nvec <= 512) e = launch_chain(rmsnorm_kernel<4>, dim3(M), dim3(128), 0, stream, X, W, Y, H, ldx, ldy, eps);
   else if (nvec <= 1024) e = launch_chain(rmsnorm_kernel<8>, dim3(M), dim3(128), 0, stream, X, W, Y, H, ldx, ldy, eps);
   else return -2;
+  return e == cudaSuccess ? 0 : -3;
+}
+
+// RMSNorm + gated LoRA-A in one launch (see rmsnorm_lora_kernel).  H % 8 == 0, H <= 8192.
+extern "C" int tahb_rmsnorm_lora(const void* x, const void* w, void* y, int M, int H, long long ldx, long long ldy,
+                                 float eps, const int* gate, const void* A, void* T, int R, long long ldt,
+                                 cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H % 8 || H > 8192 || R <= 0) return -1;
+  cudaError_t e = launch_chain(rmsnorm_lora_kernel, dim3(M, 1 + NORM_LORA_SLICES), dim3(256), (size_t)H * 2, stream,
+                               reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+                               reinterpret_cast<__nv_bfloat16*>(y), H, ldx, ldy, eps, gate,
+                               reinterpret_cast<const __nv_bfloat16*>(A), reinterpret_cast<__nv_bfloat16*>(T), R, ldt);
   return e == cudaSuccess ? 0 : -3;
 }
 
@@ -451,6 +635,14 @@ extern "C" int tahb_qk_norm_rope_kv(const void* qkv, const void* q_w, const void
   return e == cudaSuccess ? 0 : -3;
 }
 
+extern "C" int tahb_rope_table(const int* pos, void* cs, int M, int hd, float theta, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  const long long n = (long long)M * (hd / 2);
+  rope_table_kernel<<<(int)((n + 255) / 256), 256, 0, stream>>>(pos, reinterpret_cast<__nv_bfloat16*>(cs), M, hd,
+                                                               log2f(theta));
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 extern "C" int tahb_embed_gather(const void* E, const int* tok, void* out, int M, int H, long long ld_out,
                                  cudaStream_t stream) {
   if (M <= 0) return 0;
@@ -470,13 +662,13 @@ static int lora_a_rows_launch(const void* x, const void* A, void* T, const int* 
                      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(A),
                      reinterpret_cast<__nv_bfloat16*>(T), gate, M, K, R, ldx, ldt,
                      reinterpret_cast<const uint32_t*>(wait_flag), reinterpret_cast<const uint32_t*>(wait_target),
-                     wait_flag ? wait_world : 0, status);
+                     wait_flag ? wait_world : 0, status, peer_wait_limit_ns());
   else
     e = launch_chain(lora_a_rows_dense_kernel, dim3(M, (R + 7) / 8), dim3(256), 0, stream,
                      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(A),
                      reinterpret_cast<__nv_bfloat16*>(T), gate, K, R, ldx, ldt,
                      reinterpret_cast<const uint32_t*>(wait_flag), reinterpret_cast<const uint32_t*>(wait_target),
-                     wait_flag ? wait_world : 0, status);
+                     wait_flag ? wait_world : 0, status, peer_wait_limit_ns());
   return e == cudaSuccess ? 0 : -3;
 }
 

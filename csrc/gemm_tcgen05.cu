@@ -49,7 +49,6 @@ struct GemmParams {
                 // output tiles (features f0.. and up_off + f0..) that share the CTA's activation tile, which
                 // halves the activation bytes a CTA pulls per unit of work (requires the staged/TMA output path)
   int* status;
-  unsigned long long* trace;   // optional [n_ctas][8] globaltimer stamps (debug aid), else nullptr
   // Tensor-parallel reduce-scatter by push (row-parallel GEMMs): instead of writing `out`, the tile
   // is stored into the symmetric slot buffer of the rank that owns its token rows,
   // slot[owner][(my rank) * rpr + (row - owner * rpr)][f], and the owner's arrival counter is
@@ -66,6 +65,23 @@ struct GemmParams {
   const uint32_t* wait_flag;
   const uint32_t* wait_target;
   int wait_world;   // 0 = off
+  unsigned long long wait_limit_ns;   // how long the peer-flag wait may take before it gives up
+  // Fused epilogue of the QKV projection (head_dim 128, so one 128-feature tile is one head): per-head
+  // RMSNorm of q / k, rotate-half RoPE, q to q_out[t, head], k / v into the paged cache slot of the
+  // token (and / or into packed k_dense / v_dense).  Replaces the output store when qkv_on != 0.
+  int qkv_on;
+  int nq, nkv, page_size;
+  float qk_eps, log2_theta;
+  const __nv_bfloat16* q_norm_w;
+  const __nv_bfloat16* k_norm_w;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_dense;
+  __nv_bfloat16* v_dense;
+  __nv_bfloat16* kv_cache[4];
+  const int* cache_sel;
+  const int* slot;
+  const int* pos;
+  const __nv_bfloat16* rope_cs;   // optional [M, 128] table: cos of the 64 frequencies, then sin (rope_table_kernel)
 };
 
 template <int BN, bool DUAL>
@@ -141,6 +157,117 @@ __device__ __forceinline__ void push_rows(const GemmParams& p, const __nv_bfloat
   }
 }
 
+// QKV epilogue on a staged tile: `stg` holds [n_tok tokens][128 features] bf16 = head `f0 / 128` of tokens
+// ta .. ta + n_tok.  First the 128 epilogue threads bring the per-token inputs into shared memory `aux` with
+// coalesced loads (the tokens' RoPE rows, cache slots and depth selectors: one global round trip instead of
+// one per token); then the four warps take the tokens round robin; a lane owns four consecutive dims of the
+// head, so the head's sum of squares is one warp reduction and the rotate-half partner (dim +- 64) sits in
+// lane +- 16.  Same arithmetic and rounding as qk_norm_rope_kv_kernel.  `aux` needs n_tok * 264 bytes.
+__device__ __forceinline__ void qkv_epilogue(const GemmParams& p, const __nv_bfloat16* stg, uint8_t* aux, int ta,
+                                             int n_tok, int f0) {
+  const int e = threadIdx.x - 64;                 // 0..127
+  const int w4 = e >> 5, lane = e & 31;
+  const int h = f0 >> 7;
+  const bool is_q = h < p.nq;
+  const bool is_k = !is_q && h < p.nq + p.nkv;
+  const bool table = p.rope_cs != nullptr;
+  uint4* s_cs = reinterpret_cast<uint4*>(aux);                       // [n_tok][16] = 256 bytes per token
+  int* s_slot = reinterpret_cast<int*>(aux + (size_t)n_tok * 256);
+  int* s_sel = s_slot + n_tok;
+  if (table && (is_q || is_k)) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.rope_cs);
+    for (int i = e; i < n_tok * 16; i += 128) {
+      const int t = ta + (i >> 4);
+      if (t < p.M) s_cs[i] = src[(size_t)t * 16 + (i & 15)];
+    }
+  }
+  if (!is_q) {
+    for (int i = e; i < n_tok; i += 128) {
+      const int t = ta + i;
+      s_slot[i] = (p.slot != nullptr && t < p.M) ? p.slot[t] : -1;
+      s_sel[i] = (p.cache_sel != nullptr && t < p.M) ? p.cache_sel[t] : 0;
+    }
+  }
+  named_bar_sync(1, 128);
+  const __nv_bfloat16* nw = is_q ? p.q_norm_w : p.k_norm_w;
+  float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  float inv[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool upper = lane >= 16;
+  if (is_q || is_k) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wv[i] = __bfloat162float(nw[lane * 4 + i]);
+      const int d = lane * 4 + i;
+      const int j = upper ? d - 64 : d;
+      inv[i] = exp2f(-(2.0f * (float)j / 128.0f) * p.log2_theta);
+    }
+  }
+  for (int r = w4; r < n_tok; r += 4) {
+    const int t = ta + r;
+    if (t >= p.M) break;
+    const uint2 raw = *reinterpret_cast<const uint2*>(stg + r * 128 + lane * 4);
+    const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float x[4];
+    {
+      const float2 a = __bfloat1622float2(rh[0]), b = __bfloat1622float2(rh[1]);
+      x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+    }
+    uint2 outv = raw;
+    if (is_q || is_k) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / 128.0f + p.qk_eps);
+      float n[4], partner[4], y[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) n[i] = bf16_round(wv[i] * bf16_round(x[i] * rstd));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, n[i], 16);
+      float cv[4], sv[4];
+      if (table) {
+        // lane l owns dims 4l .. 4l+3, whose frequency index is 4 (l mod 16) ..: cos there, sin 64 further
+        const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(s_cs + r * 16) + (lane & 15) * 4;
+        const uint2 cr = *reinterpret_cast<const uint2*>(row), sr = *reinterpret_cast<const uint2*>(row + 64);
+        const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&cr);
+        const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&sr);
+        const float2 c0 = __bfloat1622float2(ch[0]), c1 = __bfloat1622float2(ch[1]);
+        const float2 s0 = __bfloat1622float2(sh[0]), s1 = __bfloat1622float2(sh[1]);
+        cv[0] = c0.x; cv[1] = c0.y; cv[2] = c1.x; cv[3] = c1.y;
+        sv[0] = s0.x; sv[1] = s0.y; sv[2] = s1.x; sv[3] = s1.y;
+      } else {
+        const float posf = (float)p.pos[t];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float ang = posf * inv[i];
+          cv[i] = bf16_round(cosf(ang));
+          sv[i] = bf16_round(sinf(ang));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float rot = upper ? partner[i] : -partner[i];
+        y[i] = bf16_round(bf16_round(n[i] * cv[i]) + bf16_round(rot * sv[i]));
+      }
+      __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0], y[1]), o1 = __floats2bfloat162_rn(y[2], y[3]);
+      outv.x = *reinterpret_cast<uint32_t*>(&o0);
+      outv.y = *reinterpret_cast<uint32_t*>(&o1);
+    }
+    if (is_q) {
+      *reinterpret_cast<uint2*>(p.q_out + ((size_t)t * p.nq + h) * 128 + lane * 4) = outv;
+      continue;
+    }
+    const int kvh = is_k ? h - p.nq : h - p.nq - p.nkv;
+    __nv_bfloat16* dense = is_k ? p.k_dense : p.v_dense;
+    if (dense != nullptr) *reinterpret_cast<uint2*>(dense + ((size_t)t * p.nkv + kvh) * 128 + lane * 4) = outv;
+    const int sl = s_slot[r];
+    if (sl >= 0) {
+      __nv_bfloat16* cache = p.kv_cache[s_sel[r]];
+      const int page = sl / p.page_size, off = sl % p.page_size;
+      *reinterpret_cast<uint2*>(cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * 128 +
+                                lane * 4) = outv;
+    }
+  }
+}
+
 // bytes of the split-K receive area: (S - 1) source blocks of [cols_per_rank][128] floats
 __host__ __device__ constexpr int split_stage_offset(int S, int cols_per_rank) {
   return (((S - 1) * 128 * cols_per_rank * 4) + 1023) & ~1023;
@@ -195,20 +322,19 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   tc_fence_after();
   pdl_wait();                   // set-up above touched no global memory; operands may be read from here on
   const uint32_t tmem_base = *tmem_slot;
-  const int cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-  if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 0] = globaltimer_ns();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       if (p.wait_world > 0) {
-        if (!wait_peer_rows(p.wait_flag, p.wait_target, p.wait_world, p.status)) *abort_flag = 1;
+        if (!wait_peer_rows(p.wait_flag, p.wait_target, p.wait_world, p.status, p.wait_limit_ns)) *abort_flag = 1;
         asm volatile("fence.proxy.async.global;" ::: "memory");   // the TMA loads below see the landed rows
       }
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % C::NS;
         const uint32_t ph = (i / C::NS) & 1;
         mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_STAGE_EMPTY);
+        if (*abort_flag) break;           // a wait gave up: issue no further copies, let the kernel run out
         mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
         const int g = kb_begin + i;
         const bool ext = g >= p.kb_main;
@@ -253,7 +379,6 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const uint32_t trow = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     mbar_wait(accum_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_ACCUM);
     tc_fence_after();
-    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 1] = globaltimer_ns();
     if (S == 1) {
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [BN tokens][128 features]
       __nv_bfloat16* stg1 = stg + BN * 128;                            // second tile of a pair
@@ -292,7 +417,10 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
-      if (p.push_world > 0) {
+      if (p.qkv_on) {
+        named_bar_sync(1, 128);
+        qkv_epilogue(p, stg, smem + BN * 256, t0, BN, f0);        // aux behind the staged tile
+      } else if (p.push_world > 0) {
         named_bar_sync(1, 128);
         push_rows(p, stg, t0, BN, f0);
         if (pair) push_rows(p, stg1, t0, BN, p.up_off + f0);
@@ -319,7 +447,6 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // blocks to its own columns, which never left tensor memory, in a fixed order.  Every thread
     // of every CTA takes part in both barriers.
     cluster_sync_all();
-    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 4] = globaltimer_ns();
     if (warp >= 2) {
       tc_fence_after();
       const int q = warp & 3;
@@ -349,7 +476,6 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       tc_fence_before();
     }
     cluster_sync_all();
-    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 5] = globaltimer_ns();
     if (warp >= 2) {
       tc_fence_after();
       const int q = warp & 3;
@@ -406,7 +532,10 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         }
       }
-      if (p.push_world > 0) {
+      if (p.qkv_on) {
+        named_bar_sync(1, 128);
+        qkv_epilogue(p, stg, reinterpret_cast<uint8_t*>(stg) + per * 256, t0 + rank * per, per, f0);
+      } else if (p.push_world > 0) {
         named_bar_sync(1, 128);
         push_rows(p, stg, t0 + rank * per, per, f0);
         if (pair) push_rows(p, stg1, t0 + rank * per, per, p.up_off + f0);
@@ -422,12 +551,9 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       }
       tc_fence_before();
     }
-    if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 6] = globaltimer_ns();
   }
 
-  if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 2] = globaltimer_ns();
   __syncthreads();
-  if (p.trace && threadIdx.x == 64) p.trace[cta_lin * 8 + 3] = globaltimer_ns();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -484,9 +610,12 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
   }
   if (p.splits > 1) {
     const int per = BN / p.splits;
-    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 * (p.pair ? 2 : 1) >
+    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 * (p.pair ? 2 : 1) +
+                            (p.qkv_on ? (size_t)per * 264 : 0) >
                         (size_t)C::NS * C::STAGE_BYTES)
       return -11;
+  } else if (p.qkv_on && (size_t)BN * (256 + 264) > (size_t)C::NS * C::STAGE_BYTES) {
+    return -11;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.F + 127) / 128, (p.M + BN - 1) / BN, p.splits);
@@ -510,16 +639,27 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
 
 using namespace tahb;
 
-static unsigned long long* g_gemm_trace = nullptr;
-// Debug aid: when set, every GEMM CTA writes four globaltimer stamps (set-up done, accumulator
-// ready, epilogue done, after the final CTA barrier) to trace[cta * 8 ..].
-extern "C" void tahb_gemm_set_trace(unsigned long long* trace) { g_gemm_trace = trace; }
-
 // out[M, F] = X[M, K] W[F, K]^T (+ X2[M, R] W2[F, R]^T) (+ residual) ; dual != 0 => SwiGLU over W rows
 // [0, F) (gate) and [up_off, up_off + F) (up).  All matrices bf16 row-major; K and R multiples of 64.
 // bn = token-tile width (16/32/64/128/256, 0 = choose from M); splits = split-K cluster size (1,2,4,8).
 // Returns 0 on success, a negative code on a host-side error.  *status (device int) is set non-zero
 // by the kernel if a bounded wait ran out.
+// Host-side description of the fused QKV epilogue (see GemmParams::qkv_on); all pointers are device memory.
+struct TahbQkvEpilogue {
+  const void* q_norm_w;
+  const void* k_norm_w;
+  void* q_out;
+  void* k_dense;        // optional packed K [M, nkv * 128]
+  void* v_dense;        // optional packed V
+  void* kv_cache[4];    // paged cache of this layer, one per depth (n_caches of them)
+  const int* cache_sel; // optional per-token depth index into kv_cache
+  const int* slot;      // per-token slot (page * page_size + offset), negative = no cache write; null = no cache
+  const int* pos;       // per-token position id
+  const void* rope_cs;  // optional [M, 128] bf16 cos | sin table of this pass (tahb_rope_table); null = compute in place
+  int n_caches, nq, nkv, page_size;
+  float eps, theta;
+};
+
 struct GemmTpArgs {
   void* const* push_slot = nullptr;     // [world] slot buffers (peer pointers), or null
   void* const* push_cnt = nullptr;      // [world] arrival counters (peer pointers)
@@ -532,9 +672,12 @@ struct GemmTpArgs {
 static int gemm_impl(const void* W, const void* X, void* out, const void* residual, const void* W2,
                      const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
                      long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
-                     int* status, cudaStream_t stream, const GemmTpArgs& tp) {
+                     int* status, cudaStream_t stream, const GemmTpArgs& tp, const TahbQkvEpilogue* qkv = nullptr) {
   if (M <= 0 || F <= 0) return 0;
   const bool push = tp.push_world > 0;
+  if (qkv != nullptr && (dual != 0 || residual != nullptr || push || F != (qkv->nq + 2 * qkv->nkv) * 128 ||
+                         qkv->n_caches > 4 || qkv->q_out == nullptr || qkv->pos == nullptr))
+    return -26;
   // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 2 = pair: two plain
   // output tiles per CTA (features f and F/2 + f) sharing the activation tile
   const bool pair = dual == 2;
@@ -565,13 +708,35 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   }
   // output (and residual) through TMA when their layout allows it, else element-wise stores
   CUtensorMap mo, mr;
-  int tma_out = !push && make_map(&mo, out, M, F_full, ldo, bn / splits, false) == 0;
+  int tma_out = !push && qkv == nullptr && make_map(&mo, out, M, F_full, ldo, bn / splits, false) == 0;
   if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F_full, ldr, bn / splits, false) == 0;
   if (pair && !tma_out && !push) return -25;     // the pair epilogue only exists on the staged path
   if (!tma_out) mo = mw;
   if (!tma_out || residual == nullptr) mr = mo;
   GemmParams p;
-  p.tma_out = tma_out || push;          // push mode stages the tile in shared memory as well
+  p.tma_out = tma_out || push || qkv != nullptr;   // push and QKV modes stage the tile in shared memory as well
+  p.qkv_on = qkv != nullptr ? 1 : 0;
+  p.wait_limit_ns = peer_wait_limit_ns();
+  if (qkv != nullptr) {
+    p.nq = qkv->nq; p.nkv = qkv->nkv; p.page_size = qkv->page_size;
+    p.qk_eps = qkv->eps; p.log2_theta = log2f(qkv->theta);
+    p.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(qkv->q_norm_w);
+    p.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(qkv->k_norm_w);
+    p.q_out = reinterpret_cast<__nv_bfloat16*>(qkv->q_out);
+    p.k_dense = reinterpret_cast<__nv_bfloat16*>(qkv->k_dense);
+    p.v_dense = reinterpret_cast<__nv_bfloat16*>(qkv->v_dense);
+    for (int c = 0; c < 4; ++c) p.kv_cache[c] = c < qkv->n_caches ? reinterpret_cast<__nv_bfloat16*>(qkv->kv_cache[c]) : nullptr;
+    p.cache_sel = qkv->cache_sel;
+    p.slot = qkv->n_caches > 0 ? qkv->slot : nullptr;
+    p.pos = qkv->pos;
+    p.rope_cs = reinterpret_cast<const __nv_bfloat16*>(qkv->rope_cs);
+  } else {
+    p.nq = p.nkv = p.page_size = 0; p.qk_eps = p.log2_theta = 0.f;
+    p.q_norm_w = p.k_norm_w = nullptr; p.q_out = p.k_dense = p.v_dense = nullptr;
+    for (int c = 0; c < 4; ++c) p.kv_cache[c] = nullptr;
+    p.cache_sel = p.slot = p.pos = nullptr;
+    p.rope_cs = nullptr;
+  }
   p.pair = pair ? 1 : 0;
   p.push_ld = F_full;
   p.push_world = tp.push_world;
@@ -595,7 +760,6 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   p.kb_ext = R / 64;
   p.splits = splits;
   p.status = status;
-  p.trace = g_gemm_trace;
 #define TAHB_LAUNCH(BN_)                                                              \
   case BN_:                                                                           \
     return dual ? launch<BN_, true>(mw, mx, mw2, mx2, mo, mr, p, stream) : launch<BN_, false>(mw, mx, mw2, mx2, mo, mr, p, stream);
@@ -634,4 +798,17 @@ extern "C" int tahb_gemm_tp(const void* W, const void* X, void* out, const void*
   tp.wait_flag = wait_flag; tp.wait_target = wait_target; tp.wait_world = wait_world;
   return gemm_impl(W, X, out, residual, W2, X2, M, F, K, R, ldw, ldx, ldo, ldr, ldw2, ldx2, dual, up_off, splits, bn,
                    status, stream, tp);
+}
+
+// QKV projection with the fused epilogue (per-head QK-norm, RoPE, q / paged K,V writes): same operands as
+// tahb_gemm_tp (out / residual unused), F must be (nq + 2 nkv) * 128.
+extern "C" int tahb_gemm_qkv(const void* W, const void* X, const void* W2, const void* X2, int M, int F, int K, int R,
+                             long long ldw, long long ldx, long long ldw2, long long ldx2, int splits, int bn,
+                             int* status, cudaStream_t stream, const void* wait_flag, const void* wait_target,
+                             int wait_world, const TahbQkvEpilogue* qkv) {
+  GemmTpArgs tp;
+  tp.wait_flag = wait_flag; tp.wait_target = wait_target; tp.wait_world = wait_world;
+  if (qkv == nullptr) return -26;
+  return gemm_impl(W, X, nullptr, nullptr, W2, X2, M, F, K, R, ldw, ldx, 0, 0, ldw2, ldx2, 0, 0, splits, bn, status,
+                   stream, tp, qkv);
 }

@@ -37,6 +37,8 @@ struct ZeroParams {
   long long lo, hi;                           // this rank's element range (multiples of 8)
   int rank, world;
   float grad_scale, lr, beta1, beta2, eps, weight_decay, bc1, bc2, max_norm;
+  int accumulate;                             // reduce phase: gshard += (instead of =) and no norm (several
+                                              // reduce-scatters - passes, micro-batches - feed one update)
 };
 
 __device__ __forceinline__ void zst_release_sys(uint32_t* p, uint32_t v) {
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(256) zero_reduce_norm_kernel(const ZeroParams 
   __shared__ float red[8];
   if (threadIdx.x == 0) {
     s_epoch = p.epoch[b];
-    p.epoch[b] = s_epoch + 1;
+    p.epoch[b] = s_epoch + (p.accumulate ? 2 : 1);
   }
   __syncthreads();
   if (!zero_barrier(p, b, s_epoch + 1)) return;     // every rank has finished writing its gradients
@@ -117,8 +119,19 @@ __global__ void __launch_bounds__(256) zero_reduce_norm_kernel(const ZeroParams 
     o1.x = a[4] * p.grad_scale; o1.y = a[5] * p.grad_scale; o1.z = a[6] * p.grad_scale; o1.w = a[7] * p.grad_scale;
     ss += o0.x * o0.x + o0.y * o0.y + o0.z * o0.z + o0.w * o0.w + o1.x * o1.x + o1.y * o1.y + o1.z * o1.z + o1.w * o1.w;
     float4* dst = reinterpret_cast<float4*>(p.gshard + i * 8);
+    if (p.accumulate) {
+      const float4 c0 = dst[0], c1 = dst[1];
+      o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w;
+      o1.x += c1.x; o1.y += c1.y; o1.z += c1.z; o1.w += c1.w;
+    }
     dst[0] = o0;
     dst[1] = o1;
+  }
+  if (p.accumulate) {
+    // the gradient buffers are reused by another layer right away: meet the peers again so that nobody
+    // overwrites a buffer that a peer is still reading; the norm is taken later over the finished sum
+    zero_barrier(p, b, s_epoch + 2);
+    return;
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -128,6 +141,29 @@ __global__ void __launch_bounds__(256) zero_reduce_norm_kernel(const ZeroParams 
     for (int w = 0; w < 8; ++w) t += red[w];
     atomicAdd(p.norm_sq, t);
   }
+}
+
+// Sum of squares of an fp32 gradient shard, added to *norm_sq (local; no cross-rank traffic).
+__global__ void __launch_bounds__(256) zero_norm_kernel(const float* __restrict__ g, long long n, float* norm_sq) {
+  __shared__ float red[8];
+  float ss = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    ss += g[i] * g[i];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    atomicAdd(norm_sq, t);
+  }
+}
+
+// One thread waits (bounded) until flag[q] has reached target[q] for every q < world: a stream-ordered gate in
+// front of kernels that cannot wait themselves (library GEMMs reading a gather buffer that peers fill).
+__global__ void wait_flags_kernel(const uint32_t* flag, const uint32_t* target, int world, int* status,
+                                  unsigned long long limit_ns) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) wait_peer_rows(flag, target, world, status, limit_ns);
 }
 
 __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(const ZeroParams p) {
@@ -211,6 +247,8 @@ static void fill(ZeroParams& p, void* const* grad, void* const* param, void* mc_
 
 // phase 0: reduce-scatter of the gradient shard [lo, hi) + scaling + squared norm (atomicAdd into *norm_sq,
 // which the caller zeroes before the launch and all-reduces afterwards).  phase 1: AdamW + parameter broadcast.
+// phase 2: as phase 0 but the scaled sum is ADDED to gshard and no norm is taken (parameter-sharded training
+// reduce-scatters a layer's gradients once per backward pass and micro-batch into one fp32 accumulator).
 extern "C" int tahb_zero_step(int phase, void* const* grad, void* const* param, void* mc_grad, void* mc_param,
                               float* gshard, float* master, float* m, float* v, float* norm_sq, void* const* flags,
                               void* epoch, int* status, long long lo, long long hi, int rank, int world,
@@ -221,8 +259,27 @@ extern "C" int tahb_zero_step(int phase, void* const* grad, void* const* param, 
   fill(p, grad, param, mc_grad, mc_param, gshard, master, m, v, norm_sq, flags, epoch, status, lo, hi, rank, world);
   p.grad_scale = grad_scale; p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps;
   p.weight_decay = weight_decay; p.bc1 = bc1; p.bc2 = bc2; p.max_norm = max_norm;
+  p.accumulate = phase == 2 ? 1 : 0;
   if (grid < 1) grid = 1;
-  if (phase == 0) zero_reduce_norm_kernel<<<grid, 256, 0, stream>>>(p);
+  if (phase == 0 || phase == 2) zero_reduce_norm_kernel<<<grid, 256, 0, stream>>>(p);
   else zero_adamw_bcast_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// *norm_sq += sum of squares of the fp32 vector g[0 .. n)
+extern "C" int tahb_sumsq_f32(const float* g, long long n, float* norm_sq, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  long long blocks = (n + 256 * 8 - 1) / (256 * 8);
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  zero_norm_kernel<<<(int)blocks, 256, 0, stream>>>(g, n, norm_sq);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Stream-ordered bounded wait until flag[q] >= target[q] (wrap-safe) for q < world; on expiry the status word
+// gets STATUS_TIMEOUT_PEER_FLAG and the stream goes on.
+extern "C" int tahb_wait_flags(const void* flag, const void* target, int world, int* status, cudaStream_t stream) {
+  if (world <= 0) return 0;
+  wait_flags_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint32_t*>(flag),
+                                          reinterpret_cast<const uint32_t*>(target), world, status, peer_wait_limit_ns());
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -550,9 +550,20 @@ struct TickState {
 // (embedding row of `tok` at depth 0, the soft embedding at depth >= 1).
 __global__ void __launch_bounds__(128) tick_begin_kernel(const TickState s, const __nv_bfloat16* __restrict__ E,
                                                          const __nv_bfloat16* __restrict__ soft,
-                                                         __nv_bfloat16* __restrict__ x_in, int H) {
+                                                         __nv_bfloat16* __restrict__ x_in, int H,
+                                                         __nv_bfloat16* __restrict__ rope_cs, int hd, float log2_theta) {
   const int r = blockIdx.x;
   const int d = s.depth[r];
+  if (rope_cs != nullptr) {
+    // RoPE row of this tick's position (cos of the hd/2 frequencies, then sin): every layer's fused QKV
+    // epilogue loads it instead of evaluating cos / sin itself
+    const float posf = (float)s.pos[r];
+    for (int j = threadIdx.x; j < hd / 2; j += blockDim.x) {
+      const float ang = posf * exp2f(-(2.0f * (float)j / (float)hd) * log2_theta);
+      rope_cs[(size_t)r * hd + j] = __float2bfloat16_rn(cosf(ang));
+      rope_cs[(size_t)r * hd + hd / 2 + j] = __float2bfloat16_rn(sinf(ang));
+    }
+  }
   // a row that has finished (EOS or max_new tokens) keeps its slot in the batch but stops
   // consuming KV pages: it recomputes over its existing cache and its outputs are ignored
   const bool done = s.finished[r] != 0 || s.n_out[r] >= s.max_new;
@@ -713,7 +724,7 @@ extern "C" int tahb_sample_full(const void* x, int* out, int rows, int V, long l
 // The scheduler entry points take the state as an array of device pointers + ints, packed by the
 // Python engine in the order of the TickState fields.
 extern "C" int tahb_tick_begin(void* const* ptrs, const int* ints, const void* E, const void* soft, void* x_in, int H,
-                               cudaStream_t stream);
+                               void* rope_cs, int hd, float theta, cudaStream_t stream);
 extern "C" int tahb_tick_end(void* const* ptrs, const int* ints, const int* need_soft, const int* next_tok,
                              cudaStream_t stream);
 
@@ -736,12 +747,14 @@ static TickState unpack_state(void* const* p, const int* n) {
 }
 
 extern "C" int tahb_tick_begin(void* const* ptrs, const int* ints, const void* E, const void* soft, void* x_in, int H,
-                               cudaStream_t stream) {
+                               void* rope_cs, int hd, float theta, cudaStream_t stream) {
   TickState s = unpack_state(ptrs, ints);
   if (s.rows <= 0) return 0;
   tick_begin_kernel<<<s.rows, 128, 0, stream>>>(s, reinterpret_cast<const __nv_bfloat16*>(E),
                                                 reinterpret_cast<const __nv_bfloat16*>(soft),
-                                                reinterpret_cast<__nv_bfloat16*>(x_in), H);
+                                                reinterpret_cast<__nv_bfloat16*>(x_in), H,
+                                                reinterpret_cast<__nv_bfloat16*>(rope_cs), hd,
+                                                theta > 0.f ? log2f(theta) : 0.f);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

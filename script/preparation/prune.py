@@ -5,9 +5,11 @@
 parameter count including the LoRA adapter matches the un-iterated baseline.  For each layer the
 loss on a few calibration texts is measured with that layer skipped; the ``num_prune`` layers with
 the smallest increase are removed and the model is saved in HuggingFace layout
-(procedure of reference ``script/preparation/prune.py:87-143``).
+(procedure and flags of reference ``script/preparation/prune.py:65-85,87-231``: ``--model --dataset --text_field
+--output --num_prune --batch_size --max_samples --max_length --device --dtype``).
 """
 import argparse
+import math
 import os
 import sys
 from typing import List
@@ -58,29 +60,77 @@ def choose_layers(model, batches, num_prune: int):
     return ref, deltas, sorted(i for _, i in deltas[:num_prune])
 
 
+def read_calibration_texts(dataset: str, text_field: str = "real_text", max_samples: int = 16) -> List[str]:
+    """Up to ``max_samples`` non-empty strings of column ``text_field``.  ``dataset`` is a dataset directory
+    written by ``Dataset.save_to_disk`` (e.g. the labeller's output, whose ``real_text`` column is the default
+    field), a hub dataset id, or a plain ``.txt`` file with one calibration text per line."""
+    if os.path.isfile(dataset) and dataset.endswith(".txt"):
+        with open(dataset, encoding="utf-8") as fh:
+            texts = [l.strip() for l in fh if l.strip()][:max_samples]
+    else:
+        import datasets as hfds
+        ds = hfds.load_from_disk(dataset) if os.path.isdir(dataset) else hfds.load_dataset(dataset)
+        if isinstance(ds, hfds.DatasetDict):
+            ds = ds[next(iter(ds))]
+        if text_field not in ds.column_names:
+            raise KeyError(f"column {text_field!r} not found; available: {ds.column_names}")
+        texts = []
+        for value in ds[text_field]:
+            if isinstance(value, str) and value.strip():
+                texts.append(value.strip())
+                if len(texts) >= max_samples:
+                    break
+    if not texts:
+        raise RuntimeError(f"no usable calibration text in {dataset!r} (field {text_field!r})")
+    return texts
+
+
+def _finite(x: float) -> float:
+    return x if math.isfinite(x) else float("inf")
+
+
 def main(argv=None):
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--model", required=True)
-    ap.add_argument("--output", required=True)
+    ap = argparse.ArgumentParser(description="Drop the decoder layers whose removal raises perplexity least")
+    ap.add_argument("--model", default="Qwen/Qwen3-4B-Base", help="model directory (HF Qwen3 layout) or hub id")
+    ap.add_argument("--dataset", "--calibration", dest="dataset", default=None,
+                    help="calibration data: a saved HuggingFace dataset directory, a hub dataset id, or a .txt file")
+    ap.add_argument("--text_field", default="real_text")
+    ap.add_argument("--output", default="model/qwen3_4_base_pruned")
     ap.add_argument("--num_prune", type=int, default=1)
-    ap.add_argument("--calibration", default=None, help=".txt file, one calibration text per line (at most 16 used)")
-    ap.add_argument("--max_length", type=int, default=1024)
+    ap.add_argument("--batch_size", type=int, default=4)
+    ap.add_argument("--max_samples", type=int, default=16)
+    ap.add_argument("--max_length", type=int, default=4096)
+    ap.add_argument("--device", default="", help="e.g. cuda:0 or cpu (default: cuda:0 when available)")
+    ap.add_argument("--dtype", default="auto", choices=["auto", "fp16", "bf16", "fp32"])
     a = ap.parse_args(argv)
     from transformers import AutoTokenizer
     from tah_b200.utils.checkpoint import load_hf_checkpoint, save_hf_checkpoint
-    dev = "cuda" if torch.cuda.is_available() else "cpu"
-    tok = AutoTokenizer.from_pretrained(a.model)
-    model = load_hf_checkpoint(a.model, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, device=dev).eval()
-    if a.calibration:
-        with open(a.calibration, encoding="utf-8") as fh:
-            texts = [l.strip() for l in fh if l.strip()][:16]
+    dev = torch.device(a.device) if a.device else torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
+    dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}.get(
+        a.dtype, torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    tok = AutoTokenizer.from_pretrained(a.model, use_fast=True)
+    if tok.pad_token is None:
+        tok.pad_token = tok.eos_token
+    model = load_hf_checkpoint(a.model, dtype=dtype, device=dev).eval()
+    if a.dataset:
+        texts = read_calibration_texts(a.dataset, a.text_field, a.max_samples)
     else:
         texts = ["The quick brown fox jumps over the lazy dog. " * 20, "Let x be a real number such that x^2 = 2. " * 20]
-    enc = tok(texts, return_tensors="pt", padding=True, truncation=True, max_length=a.max_length).to(dev)
-    batches = [(enc["input_ids"][i:i + 4], enc["attention_mask"][i:i + 4]) for i in range(0, len(texts), 4)]
-    ref, deltas, drop = choose_layers(model, batches, a.num_prune)
-    print(f"reference loss {ref:.4f}; least harmful layers: {[(i, round(d, 4)) for d, i in deltas[:5]]}; dropping {drop}")
+    batches = []
+    for i in range(0, len(texts), max(1, a.batch_size)):
+        enc = tok(texts[i:i + a.batch_size], return_tensors="pt", padding=True, truncation=True, max_length=a.max_length).to(dev)
+        batches.append((enc["input_ids"], enc["attention_mask"]))
+    ref, deltas, drop = choose_layers(model, batches, min(a.num_prune, len(model.model.layers) - 1))
+    ref_ppl = math.exp(ref)
+    print(f"baseline loss {ref:.4f}, PPL {ref_ppl:.4f}")
+    for d, i in sorted(deltas, key=lambda t: t[1]):
+        ppl = _finite(math.exp(ref + d))
+        print(f"layer {i} -> PPL {ppl:.4f}, dPPL {_finite(ppl - ref_ppl):.4f}")
+    print(f"pruning layer indices (smallest dPPL first): {drop}")
     prune_layers_inplace(model, drop)
+    after = lm_loss(model, batches)
+    print(f"PPL after pruning: {math.exp(after):.4f} (d = {math.exp(after) - ref_ppl:.4f})")
+    os.makedirs(a.output, exist_ok=True)
     save_hf_checkpoint(model, a.output)
     tok.save_pretrained(a.output)
 

@@ -129,7 +129,20 @@ def _synthetic(n: int, device, max_iter: int):
     return model, rows
 
 
-def main(config_path: str, synthetic: int = 0, max_steps: int = -1):
+def _parallel_config(path):
+    """Launch-topology file (``script/recipes/parallel_configs/zero{2,3}.yaml``; the reference's accelerate /
+    DeepSpeed files, ``script/recipes/accelerate_configs/zero2.yaml:3-16``, play this role there).  Keys read:
+    ``strategy`` (zero2 | zero3), ``nvls`` (use NVLS multimem in the fused collectives)."""
+    if not path:
+        return {}
+    with open(path, encoding="utf-8") as fh:
+        pc = yaml.safe_load(fh) or {}
+    if pc.get("nvls") is False:
+        os.environ["TAH_B200_NVLS"] = "0"
+    return pc
+
+
+def main(config_path: str, synthetic: int = 0, max_steps: int = -1, parallel_config: str = None):
     if "RANK" in os.environ and not dist.is_initialized():
         local = int(os.environ.get("LOCAL_RANK", 0))
         if torch.cuda.is_available():
@@ -160,6 +173,9 @@ def main(config_path: str, synthetic: int = 0, max_steps: int = -1):
         v = tc.pop(k, None)
         if v and tc.get("report_to") == "wandb":
             os.environ[{"wandb_project": "WANDB_PROJECT", "wandb_name": "WANDB_NAME", "wandb_entity": "WANDB_ENTITY"}[k]] = str(v)
+    pc = _parallel_config(parallel_config or tc.pop("parallel_config", None))
+    if pc.get("strategy") and "strategy" not in tc:
+        tc["strategy"] = pc["strategy"]
     args = TaHTrainingArguments.from_dict(dict(tc, output_dir=out_dir))
     if max_steps > 0:
         args.max_steps = max_steps
@@ -183,5 +199,7 @@ if __name__ == "__main__":
     ap.add_argument("--config", required=True)
     ap.add_argument("--synthetic", type=int, default=0, help="train a tiny random model on N random sequences")
     ap.add_argument("--max_steps", type=int, default=-1)
+    ap.add_argument("--parallel_config", default=None,
+                    help="launch topology YAML (script/recipes/parallel_configs/zero2.yaml or zero3.yaml)")
     a = ap.parse_args()
-    main(a.config, a.synthetic, a.max_steps)
+    main(a.config, a.synthetic, a.max_steps, a.parallel_config)

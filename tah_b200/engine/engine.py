@@ -32,6 +32,7 @@ from tah_b200.engine.weights import EngineWeights
 from tah_b200.model.iter_decider import (BernoulliIterDecider, IterLabelDecider, MLPIterDecider,
                                          SimpleMLPIterDecider)
 from tah_b200.ops import cuda as K
+from tah_b200.utils.observe import MetricsSink, engine_counters, nvtx_range
 
 
 @dataclass
@@ -73,6 +74,11 @@ class TaHEngine:
         thr = getattr(inner, "threshold", None)
         self._thr = float(thr.detach().float().cpu()) if isinstance(thr, torch.Tensor) else 0.5
         self.kernel_launches_per_tick = 0
+        # counters of the last generate() call (KV page occupancy per depth, ticks per token, passes per token,
+        # graph reuse ...); appended to the JSONL file named by TAH_B200_METRICS when that variable is set
+        self.last_counters: dict = {}
+        path = os.environ.get("TAH_B200_METRICS")
+        self.metrics = MetricsSink(path) if path else None
 
     # ------------------------------------------------------------------------------------------
     # decider plumbing
@@ -157,21 +163,25 @@ class TaHEngine:
         t_down = bf(n, w.r_down) if lora else None
         tap_layers = self._tap_layers()
         tensor_core_attn = hd in (64, 128) and os.environ.get("TAH_B200_NAIVE_PREFILL", "0") != "1"
+        fuse_qkv = hd == 128 and os.environ.get("TAH_B200_NO_FUSE", "0") not in ("1", "qkv")
         if tensor_core_attn:
             tile_q0, tile_qn = K.attn_tiles(seq_counts)
+        rope_cs = K.rope_table(pos, hd, cfg.rope_theta) if fuse_qkv else None     # once per pass, shared by the layers
         xn = K.rms_norm(h, w.layers[0].ln1, cfg.rms_norm_eps, out=xn_buf)
         for li, L in enumerate(w.layers):
             if taps_out is not None and li in tap_layers:
                 taps_out[li] = h.clone() if tp is None else tp.gather_rows(h, n)
-            if lora:
-                t = K.gemm(xn, L.a_qkv)
-                qkv = K.gemm(xn, L.w_qkv, x2=t, w2=L.b_qkv)
-            else:
-                qkv = K.gemm(xn, L.w_qkv)
+            kw = dict(x2=K.gemm(xn, L.a_qkv), w2=L.b_qkv) if lora else {}
             kd, vd = bf(n, nkv * hd), bf(n, nkv * hd)
-            q = K.qk_norm_rope_kv(qkv, L.q_norm, L.k_norm, pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
-                                  k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
-                                  page_size=self.page_size)
+            if fuse_qkv:
+                q = K.gemm_qkv(xn, L.w_qkv, L.q_norm, L.k_norm, pos, nq, nkv, cfg.rms_norm_eps, cfg.rope_theta,
+                               k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
+                               page_size=self.page_size, rope_cs=rope_cs, **kw)
+            else:
+                qkv = K.gemm(xn, L.w_qkv, **kw)
+                q = K.qk_norm_rope_kv(qkv, L.q_norm, L.k_norm, pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
+                                      k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
+                                      page_size=self.page_size)
             own.append((kd, vd))
             ks = [sk[li] for sk in seg_k] + [kd]
             vs = [sv[li] for sv in seg_v] + [vd]
@@ -225,7 +235,8 @@ class TaHEngine:
         taps = {}
         base0 = seq_start[rows_idx].contiguous()
         count0 = (pos + 1).contiguous()
-        hn, kv0 = self._packed_pass(x, pos, 0, slots0, [], [], [base0], [count0], lens, taps_out=taps)
+        with nvtx_range("prefill/pass0"):
+            hn, kv0 = self._packed_pass(x, pos, 0, slots0, [], [], [base0], [count0], lens, taps_out=taps)
         seg_k, seg_v = [[k for k, _ in kv0]], [[v for _, v in kv0]]
 
         # ---- continue decision for every prompt token ----------------------------------------
@@ -265,7 +276,8 @@ class TaHEngine:
             counts = [c[cur_idx].contiguous() for c in prev_counts] + [(rank1 + 1).contiguous()]
             # shallower segments (1..depth-1) index into the packed arrays of those passes: their
             # (base, count) were computed against those arrays when the passes ran
-            hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts, cnt1)
+            with nvtx_range(f"prefill/pass{depth}"):
+                hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts, cnt1)
             logits1 = self._lm_head(hn1)
             cum1 = cur_cum + logits1
             want_more = (extra[cur_idx] > depth) & (depth + 1 < self.max_iter)
@@ -353,6 +365,7 @@ class TaHEngine:
         s.samp_v = torch.zeros(B, 128, dtype=torch.float32, device=dev)
         s.samp_i = i32(B, 128)
         s.seed_dev = torch.zeros(1, dtype=torch.int64, device=dev)     # per-call sampling seed, read on the device
+        s.rope_cs = bf(B, cfg.head_dim)                                # RoPE cos | sin row of the tick's positions
         s.graph = None
         s.x_in, s.soft, s.h, s.xn = bf(B, H), bf(B, H), bf(B, H), bf(B, H)
         s.qkv = bf(B, w.qkv_out)
@@ -375,12 +388,14 @@ class TaHEngine:
         s.tensors = tensors
         return s
 
-    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M, push=False, final=False):
+    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M, push=False, final=False, next_lora=None):
         """Row-parallel projection + residual + the RMSNorm that follows it.
 
         One GPU: the GEMM epilogue adds the residual in place and a norm kernel follows.  Tensor
         parallel: the GEMM writes this rank's partial result into symmetric memory and the fused
-        NVLink kernel does all-reduce + residual + norm + broadcast; ``h`` stays row-sharded."""
+        NVLink kernel does all-reduce + residual + norm + broadcast; ``h`` stays row-sharded.
+        ``next_lora = (A, t_buf)`` (one GPU, decode): fuse the LoRA-A product of the consumer of ``xn`` into the
+        norm launch."""
         cfg, tp = self.cfg, self.tp
         lora = a_ is not None and t_buf is not None
         if lora:
@@ -391,6 +406,9 @@ class TaHEngine:
         kw = dict(x2=t_buf, w2=b_) if lora else {}
         if tp is None:
             K.gemm(x, w_, residual=h, out=h, **kw)
+            if next_lora is not None:
+                # the norm kernel also forms t = gate * xn A^T for the projection that consumes xn
+                return K.rms_norm_lora(h, ln_w, cfg.rms_norm_eps, gate, next_lora[0], out=xn_out, t_out=next_lora[1])[0]
             return K.rms_norm(h, ln_w, cfg.rms_norm_eps, out=xn_out)
         desc = tp.push_desc(M) if push else None
         if desc is not None:
@@ -413,35 +431,52 @@ class TaHEngine:
         tl = self._tap_layers()
         H = cfg.hidden_size
         nL = len(w.layers)
-        s.binding.tick_begin(w.embed, s.soft, s.x_in)
-        s.h.copy_(s.x_in)
+        off = os.environ.get("TAH_B200_NO_FUSE", "0")          # "1": both fusions off; "lora" / "qkv": that one off
+        fuse_norm_lora = off not in ("1", "lora") and lora and tp is None   # RMSNorm + LoRA-A of the gated rows in one launch
+        fuse_qkv = off not in ("1", "qkv") and hd == 128         # QK-norm + RoPE + KV write in the QKV GEMM epilogue
+        rope = dict(rope_cs=s.rope_cs, hd=hd, theta=cfg.rope_theta) if fuse_qkv else {}
+        if tp is None:
+            s.binding.tick_begin(w.embed, s.soft, s.h, **rope)   # the input embedding is the residual stream
+        else:
+            s.binding.tick_begin(w.embed, s.soft, s.x_in, **rope)
+            s.h.copy_(s.x_in)
         pools = [[kv.layer_pool(d, li) for d in range(kv.n_depths)] for li in range(nL)]
-        xn = K.rms_norm(s.h, w.layers[0].ln1, cfg.rms_norm_eps, out=s.xn)
+        if fuse_norm_lora:
+            xn = K.rms_norm_lora(s.h, w.layers[0].ln1, cfg.rms_norm_eps, s.gate, w.layers[0].a_qkv, out=s.xn,
+                                 t_out=s.t_qkv)[0]
+        else:
+            xn = K.rms_norm(s.h, w.layers[0].ln1, cfg.rms_norm_eps, out=s.xn)
         self._xn_wait = None       # set by _row_parallel when xn is a tensor-parallel broadcast in flight
         push = tp is not None and os.environ.get("TAH_B200_TP_PULL", "0") != "1"
         for li, L in enumerate(w.layers):
             if li in tl:
                 j = tl.index(li)
                 s.taps[:, j * H:(j + 1) * H].copy_(s.h if tp is None else tp.gather_rows(s.h, B))
-            if lora:
+            if lora and not fuse_norm_lora:
                 K.lora_a_rows(xn, L.a_qkv, s.gate, out=s.t_qkv, tp_wait=self._xn_wait)
-                K.gemm(xn, L.w_qkv, x2=s.t_qkv, w2=L.b_qkv, out=s.qkv, tp_wait=self._xn_wait)
+            kw = dict(x2=s.t_qkv, w2=L.b_qkv) if lora else {}
+            if fuse_qkv:
+                K.gemm_qkv(xn, L.w_qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, cfg.rms_norm_eps, cfg.rope_theta, q_out=s.q,
+                           caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size,
+                           tp_wait=self._xn_wait, rope_cs=s.rope_cs, **kw)
             else:
-                K.gemm(xn, L.w_qkv, out=s.qkv, tp_wait=self._xn_wait)
-            K.qk_norm_rope_kv(s.qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
-                              q_out=s.q, caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size)
+                K.gemm(xn, L.w_qkv, out=s.qkv, tp_wait=self._xn_wait, **kw)
+                K.qk_norm_rope_kv(s.qkv, L.q_norm, L.k_norm, s.pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
+                                  q_out=s.q, caches=pools[li], cache_sel=s.depth, slot=s.slot, page_size=self.page_size)
             K.decode_attn(s.q, pools[li], kv.page_table, kv.len, s.depth, nq, nkv, hd, self.page_size, scale, out=s.o,
                           n_split=s.attn_split, ws=s.attn_ws)
             xn = self._row_parallel(s.o, L.w_o, L.a_o if lora else None, L.b_o, s.t_o, s.gate, s.h, L.ln2, s.xn, B,
-                                    push=push)
-            if lora:
+                                    push=push, next_lora=(L.a_gu, s.t_gu) if fuse_norm_lora else None)
+            if lora and not fuse_norm_lora:
                 K.lora_a_rows(xn, L.a_gu, s.gate, out=s.t_gu, tp_wait=self._xn_wait)
+            if lora:
                 K.gemm(xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
             else:
                 K.gemm(xn, L.w_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
             next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
+            nxt_lora = (w.layers[li + 1].a_qkv, s.t_qkv) if fuse_norm_lora and li + 1 < nL else None
             xn = self._row_parallel(s.act, L.w_down, L.a_down if lora else None, L.b_down, s.t_down, s.gate, s.h,
-                                    next_ln, s.xn, B, push=push, final=li + 1 == nL)
+                                    next_ln, s.xn, B, push=push, final=li + 1 == nL, next_lora=nxt_lora)
         # xn is now the final-norm output of every row
         if cfg.num_hidden_layers in tl:
             j = tl.index(cfg.num_hidden_layers)
@@ -531,7 +566,8 @@ class TaHEngine:
         B = input_ids.shape[0]
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         ev[0].record()
-        last_logits, lens, _ = self.prefill(input_ids, attention_mask, max_new_tokens)
+        with nvtx_range("engine/prefill"):
+            last_logits, lens, _ = self.prefill(input_ids, attention_mask, max_new_tokens)
         sampling = None
         if do_sample:
             if temperature <= 0:
@@ -573,25 +609,31 @@ class TaHEngine:
             if on_tick is not None:
                 on_tick(ticks, s)
         run = self._tick_runner(s, sampling)
-        while ticks < limit:
-            run()
-            ticks += 1
-            if on_tick is not None:
-                on_tick(ticks, s)
-            if ticks % sync_every == 0 or ticks == limit:
-                done = bool(((s.finished != 0) | (s.n_out >= max_new_tokens)).all())
-                if done:
-                    break
+        with nvtx_range("engine/decode"):
+            while ticks < limit:
+                run()
+                ticks += 1
+                if on_tick is not None:
+                    on_tick(ticks, s)
+                if ticks % sync_every == 0 or ticks == limit:
+                    done = bool(((s.finished != 0) | (s.n_out >= max_new_tokens)).all())
+                    if done:
+                        break
         ev[2].record()
         torch.cuda.synchronize()
         K.check_status(dev)
         n_out = s.n_out.tolist()
         out = s.out_tokens.tolist()
         iters = (s.iter_sum.float() / s.n_out.clamp(min=1).float()).tolist()
-        return GenerationResult(tokens=[row[:n] for row, n in zip(out, n_out)], iter_counts=iters, ticks=ticks,
-                                tokens_emitted=int(s.tokens_done.item()), prefill_ms=ev[0].elapsed_time(ev[1]),
-                                decode_ms=ev[1].elapsed_time(ev[2]),
-                                extra={"graph_captures": self.graph_captures, "graph_reuses": self.graph_reuses})
+        res = GenerationResult(tokens=[row[:n] for row, n in zip(out, n_out)], iter_counts=iters, ticks=ticks,
+                               tokens_emitted=int(s.tokens_done.item()), prefill_ms=ev[0].elapsed_time(ev[1]),
+                               decode_ms=ev[1].elapsed_time(ev[2]),
+                               extra={"graph_captures": self.graph_captures, "graph_reuses": self.graph_reuses})
+        self.last_counters = dict(engine_counters(self, res), graph_captures=self.graph_captures,
+                                  graph_reuses=self.graph_reuses, rows=B)
+        if self.metrics is not None:
+            self.metrics.log(self.last_counters, step=self._calls)
+        return res
 
     def _tick_runner(self, s, sampling):
         if not self.use_cuda_graph:

@@ -5,7 +5,8 @@ tokenizer, tp_size) -> (model, infer)`` with ``infer(list[str]) -> list[(text, s
 per-sample time is the batch time divided by the batch size.
 
 * ``tah`` - this framework's paged-KV engine (left-padded prompts, ``do_sample = temperature > 0``).
-  Unlike the reference, ``tp_size > 1`` is honoured when the job runs under ``torchrun``.
+  Unlike the reference, ``tp_size > 1`` is honoured: one tensor-parallel engine over ``tp_size`` GPUs, either the
+  ranks of a ``torchrun`` job or follower processes spawned by the job (:mod:`tah_b200.evaluate.tp_group`).
 * ``hf`` - a plain HuggingFace ``generate`` on the base model (needs the checkpoint's HF weights).
 * ``sglang`` - only if the optional package is importable.
 """
@@ -43,6 +44,9 @@ def warmup(infer: InferFn, n: int = 1) -> None:
 def cleanup(model, backend: str) -> None:
     if backend == "sglang" and hasattr(model, "shutdown"):
         model.shutdown()
+    group = getattr(model, "_tp_group", None)
+    if group is not None:
+        group.close()                             # stop the follower ranks of a tensor-parallel engine
     del model
     gc.collect()
     if torch.cuda.is_available():
@@ -54,7 +58,30 @@ def _dtype(config: Dict):
     return getattr(torch, name)
 
 
+def _setup_tah_tp(config: Dict, model_path: str, tokenizer, tp_size: int):
+    from tah_b200.evaluate.tp_group import TPEngineGroup
+    group = TPEngineGroup(model_path, config, tp_size)
+    model = group.model
+    model._tp_group = group                       # cleanup() closes the group
+    tokenizer.padding_side = "left"
+    temperature = float(config.get("temperature", 0.0))
+    gen_kw = dict(max_new_tokens=int(config.get("max_new_tokens", 1024)), do_sample=temperature > 0,
+                  temperature=temperature if temperature > 0 else 1.0, top_p=float(config.get("top_p", 1.0)),
+                  top_k=int(config.get("top_k", 0)), min_p=float(config.get("min_p", 0.0)),
+                  eos_token_id=getattr(tokenizer, "eos_token_id", None))
+
+    def infer(prompts: List[str]) -> List[Tuple[str, float]]:
+        enc = tokenizer(prompts, return_tensors="pt", padding=True)
+        res, secs = time_inference(group.generate, enc["input_ids"], enc.get("attention_mask"), **gen_kw)
+        texts = [tokenizer.decode(t) if t else "" for t in res.tokens]
+        return [(t, secs / max(1, len(prompts))) for t in texts]
+
+    return model, infer
+
+
 def setup_tah(config: Dict, model_path: str, tokenizer, tp_size: int = 1):
+    if tp_size and tp_size > 1:
+        return _setup_tah_tp(config, model_path, tokenizer, tp_size)
     from tah_b200 import TaHConfig, TaHForCausalLM
     from tah_b200.model.utils import TaHForCasualLM_generate
     fields = TaHConfig.__dataclass_fields__

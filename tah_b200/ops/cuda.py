@@ -147,6 +147,39 @@ def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
     return plan_gemm(M, F, K, R, dual)[1]
 
 
+_pending_gemm_wait = None
+
+
+def set_pending_gemm_wait(desc) -> None:
+    """The next :func:`gemm` / :func:`gemm_qkv` call without a ``tp_wait`` of its own takes ``desc = (flags,
+    targets)``: its TMA producer waits for those landing flags before the first load.  Used by parameter-sharded
+    training, where the first GEMM of a layer consumes the all-gather of the layer's weights."""
+    global _pending_gemm_wait
+    _pending_gemm_wait = desc
+
+
+def clear_pending_gemm_wait() -> bool:
+    """Drop a pending wait; returns True if one was still pending (nobody consumed it)."""
+    global _pending_gemm_wait
+    had = _pending_gemm_wait is not None
+    _pending_gemm_wait = None
+    return had
+
+
+def _take_pending_wait(tp_wait):
+    global _pending_gemm_wait
+    if tp_wait is None and _pending_gemm_wait is not None:
+        tp_wait, _pending_gemm_wait = _pending_gemm_wait, None
+    return tp_wait
+
+
+def wait_flags(flags: torch.Tensor, targets: torch.Tensor) -> None:
+    """Stream-ordered bounded wait (one tiny kernel) until ``flags[q] >= targets[q]`` for every q: gates kernels
+    that cannot wait themselves, e.g. library GEMMs reading a gather buffer that peers fill."""
+    _rc(lib().tahb_wait_flags(_p(flags), _p(targets), c_int(flags.numel()), _p(status_word(flags.device)), _stream()),
+        "tahb_wait_flags")
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
@@ -164,6 +197,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     ``tp_wait = (flags, targets)`` makes the kernel wait for the broadcast rows of ``x``."""
     _check_bf16_2d(x, "x")
     _check_bf16_2d(w, "w")
+    tp_wait = _take_pending_wait(tp_wait)
     M, K = x.shape
     F = w.shape[0] // 2 if swiglu else w.shape[0]
     if w.shape[1] != K:
@@ -225,6 +259,96 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.T
     _rc(lib().tahb_rmsnorm(_p(x), _p(w), _p(out), c_int(x.shape[0]), c_int(x.shape[1]), c_ll(x.stride(0)),
                            c_ll(out.stride(0)), c_float(eps), _stream()), "tahb_rmsnorm")
     return out
+
+
+def rms_norm_lora(x: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, A: torch.Tensor,
+                  out: Optional[torch.Tensor] = None, t_out: Optional[torch.Tensor] = None):
+    """RMSNorm of every row and, in the same launch, ``t[r] = gate[r] ? y[r] @ A^T : 0`` (the LoRA-A product of the
+    rows at depth >= 1 of a decode tick).  Returns ``(y, t)``."""
+    _check_bf16_2d(x, "x")
+    M, H = x.shape
+    R = A.shape[0]
+    if out is None:
+        out = torch.empty_like(x)
+    if t_out is None:
+        t_out = torch.empty(M, R, dtype=torch.bfloat16, device=x.device)
+    if A.shape[1] != H or not A.is_contiguous():
+        raise ValueError("rms_norm_lora: A must be a contiguous [R, H] matrix")
+    _rc(lib().tahb_rmsnorm_lora(_p(x), _p(w), _p(out), c_int(M), c_int(H), c_ll(x.stride(0)), c_ll(out.stride(0)),
+                                c_float(eps), _p(gate), _p(A), _p(t_out), c_int(R), c_ll(t_out.stride(0)), _stream()),
+        "tahb_rmsnorm_lora")
+    return out, t_out
+
+
+def rope_table(pos: torch.Tensor, hd: int, theta: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``[M, hd]`` bf16 RoPE table of a pass: ``cos`` of the ``hd/2`` frequencies at ``pos[t]``, then ``sin``."""
+    M = pos.shape[0]
+    if out is None:
+        out = torch.empty(M, hd, dtype=torch.bfloat16, device=pos.device)
+    _rc(lib().tahb_rope_table(_p(pos), _p(out), c_int(M), c_int(hd), c_float(theta), _stream()), "tahb_rope_table")
+    return out
+
+
+def set_peer_wait_limit_ns(ns: int) -> int:
+    """How long kernels wait for a flag that a peer GPU advances before they give up (status 4); 0 = default
+    (2 s).  Returns the previous limit."""
+    fn = lib().tahb_set_peer_wait_limit_ns
+    fn.restype = ctypes.c_ulonglong
+    return int(fn(ctypes.c_ulonglong(int(ns))))
+
+
+class _QkvEpilogue(ctypes.Structure):
+    _fields_ = [("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("q_out", c_void_p), ("k_dense", c_void_p),
+                ("v_dense", c_void_p), ("kv_cache", c_void_p * 4), ("cache_sel", c_void_p), ("slot", c_void_p),
+                ("pos", c_void_p), ("rope_cs", c_void_p), ("n_caches", c_int), ("nq", c_int), ("nkv", c_int), ("page_size", c_int),
+                ("eps", c_float), ("theta", c_float)]
+
+
+def gemm_qkv(x: torch.Tensor, w: torch.Tensor, q_w, k_w, pos, nq: int, nkv: int, eps: float, theta: float, *,
+             x2: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = None, q_out=None, k_dense=None,
+             v_dense=None, caches: Sequence[torch.Tensor] = (), cache_sel=None, slot=None, page_size: int = 16,
+             tp_wait=None, splits: Optional[int] = None, bn: int = 0, rope_cs: Optional[torch.Tensor] = None):
+    """QKV projection (``x @ w^T`` + LoRA K-extension) whose epilogue applies the per-head QK RMSNorm and RoPE and
+    writes q to ``q_out`` and K / V into the paged cache slots (and / or ``k_dense`` / ``v_dense``): the fused form
+    of :func:`gemm` followed by :func:`qk_norm_rope_kv`, for head_dim 128 (one 128-feature tile = one head)."""
+    _check_bf16_2d(x, "x")
+    _check_bf16_2d(w, "w")
+    M, K = x.shape
+    F = w.shape[0]
+    if F != (nq + 2 * nkv) * 128:
+        raise ValueError("gemm_qkv needs head_dim 128 and w of (nq + 2 nkv) * 128 rows")
+    R = 0
+    if x2 is not None:
+        _check_bf16_2d(x2, "x2")
+        _check_bf16_2d(w2, "w2")
+        R = x2.shape[1]
+    if q_out is None:
+        q_out = torch.empty(M, nq * 128, dtype=torch.bfloat16, device=x.device)
+    if splits is None and bn == 0:
+        bn, splits = plan_gemm(M, F, K, R, False)
+    elif splits is None:
+        splits = 1
+    e = _QkvEpilogue()
+    e.q_norm_w, e.k_norm_w, e.q_out = q_w.data_ptr(), k_w.data_ptr(), q_out.data_ptr()
+    e.k_dense = 0 if k_dense is None else k_dense.data_ptr()
+    e.v_dense = 0 if v_dense is None else v_dense.data_ptr()
+    for i in range(4):
+        e.kv_cache[i] = caches[i].data_ptr() if i < len(caches) else 0
+    e.cache_sel = 0 if cache_sel is None else cache_sel.data_ptr()
+    e.slot = 0 if slot is None else slot.data_ptr()
+    e.pos = pos.data_ptr()
+    e.rope_cs = 0 if rope_cs is None else rope_cs.data_ptr()     # [M, 128] table from rope_table(), else computed in place
+    e.n_caches, e.nq, e.nkv, e.page_size, e.eps, e.theta = len(caches), nq, nkv, page_size, eps, theta
+    if tp_wait is not None:
+        flags, targets = tp_wait
+        wait = (_p(flags), _p(targets), c_int(flags.numel()))
+    else:
+        wait = (None, None, c_int(0))
+    _rc(lib().tahb_gemm_qkv(_p(w), _p(x), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R), c_ll(w.stride(0)),
+                            c_ll(x.stride(0)), c_ll(w2.stride(0) if w2 is not None else 0),
+                            c_ll(x2.stride(0) if x2 is not None else 0), c_int(splits), c_int(bn),
+                            _p(status_word(x.device)), _stream(), *wait, ctypes.byref(e)), "tahb_gemm_qkv")
+    return q_out
 
 
 def _ptr_array(tensors: Sequence[Optional[torch.Tensor]]):
@@ -549,6 +673,22 @@ def push_reduce_norm_bcast(slot, cnt, cnt_target, xout_ptrs, mc_xout: int, xflag
         "tahb_push_reduce_norm_bcast")
 
 
+def tp_topk_merge(xval_ptrs, xidx_ptrs, arrive_ptrs, epoch, vals, idx, out_val, out_idx, buf_rows: int, k: int, rank: int,
+                  world: int, vocab_lo: int):
+    """Exchange sorted per-shard top-``k`` candidates with the peers of a tensor-parallel group through
+    symmetric memory and merge them (``tp_topk_merge_kernel``).  ``buf_rows``: the row capacity the exchange
+    buffers were laid out for."""
+    n = len(xval_ptrs)
+    arr = lambda ptrs: (c_void_p * n)(*ptrs)
+    rows = vals.shape[0]
+    if rows != buf_rows:
+        raise ValueError("tp_topk_merge: the exchange buffers are laid out for a fixed number of rows")
+    _rc(lib().tahb_tp_topk_merge(arr(xval_ptrs), arr(xidx_ptrs), arr(arrive_ptrs), _p(epoch), _p(vals), _p(idx),
+                                 _p(out_val), _p(out_idx), _p(status_word(vals.device)), c_int(rows), c_int(k),
+                                 c_int(vals.stride(0)), c_int(out_idx.stride(0)), c_int(rank), c_int(world),
+                                 c_int(vocab_lo), _stream()), "tahb_tp_topk_merge")
+
+
 def shard_gather_push(shard, dst_ptrs, mc_dst: int, landed_ptrs, ready_ptrs, target, state, rank: int, world: int,
                       grid: int):
     """Store this rank's parameter shard into every rank's gather buffer and advance the landing flags
@@ -570,9 +710,10 @@ class TickStateBinding:
         self.ptrs = _ptr_array(tensors)
         self.ints = (c_int * len(ints))(*ints)
 
-    def tick_begin(self, E, soft, x_in):
-        _rc(lib().tahb_tick_begin(self.ptrs, self.ints, _p(E), _p(soft), _p(x_in), c_int(E.shape[1]), _stream()),
-            "tahb_tick_begin")
+    def tick_begin(self, E, soft, x_in, rope_cs=None, hd: int = 0, theta: float = 0.0):
+        """``rope_cs`` (optional ``[rows, hd]`` bf16): also write the RoPE cos | sin row of every row's position."""
+        _rc(lib().tahb_tick_begin(self.ptrs, self.ints, _p(E), _p(soft), _p(x_in), c_int(E.shape[1]), _p(rope_cs),
+                                  c_int(hd), c_float(theta), _stream()), "tahb_tick_begin")
 
     def tick_end(self, need_soft, next_tok):
         _rc(lib().tahb_tick_end(self.ptrs, self.ints, _p(need_soft), _p(next_tok), _stream()), "tahb_tick_end")

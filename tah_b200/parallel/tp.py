@@ -161,8 +161,51 @@ class TensorParallel:
         dist.all_gather_into_tensor(out, mine, group=self.group)
         return out[:M]
 
+    # ---- vocabulary-parallel arg-max / top-k merge: candidates exchanged by peer stores, merged locally -----
+    def _merge_buffers(self, rows: int):
+        """Symmetric exchange buffers for :meth:`merge_topk` (values / indices ``[2][world][rows][128]``, one
+        arrival word per row) and the local per-row epoch counters."""
+        cache = self.__dict__.setdefault("_merge", {})         # one set of buffers per row count
+        st = cache.get(rows)
+        if st is not None:
+            return st
+        import torch.distributed._symmetric_memory as symm_mem
+        n = 2 * self.world_size * rows * 128
+        xv = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        xi = symm_mem.empty(n, dtype=torch.int32, device=self.device)
+        ar = symm_mem.empty(rows, dtype=torch.int32, device=self.device)
+        ar.zero_()
+        hv, hi, ha = (symm_mem.rendezvous(t, self.group) for t in (xv, xi, ar))
+        st = dict(rows=rows, keep=(xv, xi, ar, hv, hi, ha), xval=[int(p) for p in hv.buffer_ptrs],
+                  xidx=[int(p) for p in hi.buffer_ptrs], arrive=[int(p) for p in ha.buffer_ptrs],
+                  epoch=torch.zeros(rows, dtype=torch.int32, device=self.device))
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        cache[rows] = st
+        return st
+
+    def prepare_merge(self, rows: int) -> None:
+        """Allocate the merge buffers ahead of a CUDA-graph capture (allocation is a collective)."""
+        self._merge_buffers(rows)
+
+    def merge_topk(self, vals: torch.Tensor, idx: torch.Tensor, vocab_lo: int, k: int):
+        """Sorted global top-k (value desc, index asc) from every rank's sorted per-shard list (``vals`` fp32
+        ``[B, k]``, ``idx`` int32 local indices): one kernel per rank that stores the candidates into every peer's
+        exchange buffer, waits for theirs and merges (``tp_topk_merge_kernel`` in ``csrc/comm.cu``).  No NCCL."""
+        B = vals.shape[0]
+        st = self._merge_buffers(B)
+        out_v = torch.empty(B, k, dtype=torch.float32, device=vals.device)
+        out_i = torch.empty(B, k, dtype=torch.int32, device=vals.device)
+        K.tp_topk_merge(st["xval"], st["xidx"], st["arrive"], st["epoch"], vals, idx, out_v, out_i, st["rows"], k,
+                        self.rank, self.world_size, vocab_lo)
+        return out_v, out_i
+
     def merge_argmax(self, best_val: torch.Tensor, best_idx: torch.Tensor, vocab_lo: int) -> torch.Tensor:
-        """Global argmax from per-shard (value, local index): lowest global index wins ties."""
+        """Global arg-max from per-shard (value, local index); the lowest global index wins ties."""
+        return self.merge_topk(best_val.view(-1, 1), best_idx.view(-1, 1), vocab_lo, 1)[1].view(-1)
+
+    # NCCL forms of the two merges: the baseline the kernel is tested against
+    def merge_argmax_nccl(self, best_val: torch.Tensor, best_idx: torch.Tensor, vocab_lo: int) -> torch.Tensor:
         pack = torch.stack([best_val.float(), (best_idx + vocab_lo).float()], dim=-1)      # [B, 2]
         allp = torch.empty(self.world_size, *pack.shape, dtype=pack.dtype, device=pack.device)
         dist.all_gather_into_tensor(allp, pack.contiguous(), group=self.group)
@@ -171,8 +214,7 @@ class TensorParallel:
         cand = torch.where(vals == top, idx, torch.full_like(idx, float("inf")))
         return cand.min(dim=0).values.to(torch.int32)
 
-    def merge_topk(self, vals: torch.Tensor, idx: torch.Tensor, vocab_lo: int, k: int):
-        """Sorted global top-k from per-shard sorted top-k lists (``vals`` fp32 [B, k], ``idx`` int32)."""
+    def merge_topk_nccl(self, vals: torch.Tensor, idx: torch.Tensor, vocab_lo: int, k: int):
         gv = self.all_gather_cat(vals, dim=-1)
         gi = self.all_gather_cat((idx + vocab_lo).to(torch.int32), dim=-1)
         # order by value desc, index asc (the order the single-GPU kernel produces): stable sorts

@@ -126,9 +126,13 @@ class ZeroAdamW:
             off += k
 
     @torch.no_grad()
-    def step(self, grad_scale: float = 1.0, lr: Optional[float] = None) -> torch.Tensor:
+    def step(self, grad_scale: float = 1.0, lr: Optional[float] = None,
+             extra_norm_sq: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One update.  ``grad_scale`` multiplies the rank-averaged gradient (e.g. 1 for losses already
-        normalised over the accumulation window).  Returns the global gradient norm (device tensor)."""
+        normalised over the accumulation window).  ``extra_norm_sq`` (optional device scalar): this rank's
+        share of the squared gradient norm of parameters managed elsewhere (parameter-sharded units); it joins
+        the all-reduce, so clipping uses the norm over both sets.  Returns the global gradient norm (device
+        tensor); ``self.norm_sq`` holds its square."""
         self._collect_stray_grads()
         self.step_count += 1
         lr = self.lr if lr is None else lr
@@ -136,11 +140,11 @@ class ZeroAdamW:
         bc1, bc2 = 1.0 - b1 ** self.step_count, 1.0 - b2 ** self.step_count
         scale = grad_scale / self.world
         if self.cuda:
-            return self._step_cuda(scale, lr, b1, b2, bc1, bc2)
-        return self._step_torch(scale, lr, b1, b2, bc1, bc2)
+            return self._step_cuda(scale, lr, b1, b2, bc1, bc2, extra_norm_sq)
+        return self._step_torch(scale, lr, b1, b2, bc1, bc2, extra_norm_sq)
 
     # ---- CUDA: fused kernels over peer memory -------------------------------------------------
-    def _step_cuda(self, scale, lr, b1, b2, bc1, bc2):
+    def _step_cuda(self, scale, lr, b1, b2, bc1, bc2, extra_norm_sq=None):
         import ctypes
         from tah_b200.ops import cuda as K
         lib = K.lib()
@@ -163,6 +167,8 @@ class ZeroAdamW:
                 raise RuntimeError(f"tahb_zero_step phase {phase} failed (code {rc})")
 
         launch(0)
+        if extra_norm_sq is not None:
+            self.norm_sq += extra_norm_sq.to(self.norm_sq.dtype)
         if self.world > 1:
             dist.all_reduce(self.norm_sq, group=self.group)
         launch(1)
@@ -170,14 +176,17 @@ class ZeroAdamW:
         return self.last_grad_norm
 
     # ---- CPU / generic: PyTorch statement of the same algorithm --------------------------------
-    def _step_torch(self, scale, lr, b1, b2, bc1, bc2):
+    def _step_torch(self, scale, lr, b1, b2, bc1, bc2, extra_norm_sq=None):
         g_full = self.flat_grad.float()
         if self.world > 1:
             dist.all_reduce(g_full, group=self.group)
         g = g_full[self.lo:self.hi] * scale
         nsq = (g * g).sum().reshape(1)
+        if extra_norm_sq is not None:
+            nsq = nsq + extra_norm_sq.to(nsq.dtype).reshape(1)
         if self.world > 1:
             dist.all_reduce(nsq, group=self.group)
+        self.norm_sq = nsq
         norm = nsq.sqrt()
         if self.max_grad_norm > 0:
             g = g * torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)

@@ -30,6 +30,8 @@ import torch.distributed as dist
 from tah_b200.model.loss import fixed_cross_entropy  # noqa: F401  (re-exported like the reference module)
 from tah_b200.parallel.zero import ZeroAdamW
 from tah_b200.train.schedule import lr_factor
+from tah_b200.utils.failure import RankFailure, RankHeartbeat, StepTimeout, StepWatchdog
+from tah_b200.utils.observe import MetricsSink, nvtx_range
 
 
 @dataclass
@@ -67,6 +69,15 @@ class TaHTrainingArguments:
     dataloader_drop_last: bool = False
     ddp_find_unused_parameters: bool = False
     remove_unused_columns: bool = False
+    # parallel strategy: "zero2" (replicated bf16 parameters, sharded fp32 state) or "zero3" (parameters sharded too)
+    strategy: str = "zero2"
+    # failure detection (multi-rank jobs): every rank bumps a heartbeat counter in the rendezvous store; before each
+    # optimizer step the peers' counters are checked and a rank whose counter stood still for heartbeat_timeout_s is
+    # reported as a RankFailure; a step that runs longer than step_timeout_s (> 0) raises StepTimeout
+    heartbeat_interval_s: float = 1.0
+    heartbeat_timeout_s: float = 60.0
+    step_timeout_s: float = 0.0
+    metrics_file: Optional[str] = None          # JSONL sink for per-step counters (default <output_dir>/metrics.jsonl)
 
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "TaHTrainingArguments":
@@ -126,6 +137,8 @@ class CustomTaHTrainer:
         self.optimizer: Optional[ZeroAdamW] = None
         self._log_file = None
         self._wandb = None
+        self.heartbeat: Optional[RankHeartbeat] = None
+        self.metrics: Optional[MetricsSink] = None
 
     # ---- callbacks ------------------------------------------------------------------------------
     def add_callback(self, cb):
@@ -180,10 +193,19 @@ class CustomTaHTrainer:
 
     # ---- optimizer ------------------------------------------------------------------------------
     def create_optimizer(self):
+        """``strategy: zero2`` - replicated bf16 parameters, sharded fp32 state (:class:`ZeroAdamW`);
+        ``strategy: zero3`` - parameters sharded as well: the model is cut into units whose weights are gathered
+        layer by layer (:mod:`tah_b200.parallel.fsdp`).  One process falls back to the first form."""
         a = self.args
-        self.optimizer = ZeroAdamW(self.model.parameters(), group=None, lr=a.learning_rate,
-                                   betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                                   weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm or 0.0)
+        kw = dict(lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                  weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm or 0.0)
+        if str(a.strategy).lower() in ("zero3", "fsdp") and self.dist_on and self.world > 1:
+            from tah_b200.parallel.fsdp import FsdpAdamW, shard_model
+            if getattr(self.model, "_fsdp", None) is None:
+                shard_model(self.model, dist.group.WORLD, self.model.device)
+            self.optimizer = FsdpAdamW(self.model, **kw)
+        else:
+            self.optimizer = ZeroAdamW(self.model.parameters(), group=None, **kw)
         return self.optimizer
 
     def _lr_at(self, step: int) -> float:
@@ -218,6 +240,43 @@ class CustomTaHTrainer:
         accum = a.gradient_accumulation_steps
         loss_window, t0 = [], time.time()
         start_epoch = self.state.global_step // spe
+        self._start_failure_detection()
+        if self.rank == 0 and self.metrics is None:
+            os.makedirs(a.output_dir, exist_ok=True)
+            self.metrics = MetricsSink(a.metrics_file or os.path.join(a.output_dir, "metrics.jsonl"), self._wandb)
+        try:
+            return self._train_loop(a, spe, accum, loss_window, t0, start_epoch)
+        except (RankFailure, StepTimeout) as exc:
+            # a peer is gone or a collective stalled: say so in the log and stop cleanly; the job is restarted from
+            # the last checkpoint with resume_from_checkpoint
+            self._emit_log({"event": type(exc).__name__, "detail": str(exc)})
+            raise
+        finally:
+            if self.heartbeat is not None:
+                self.heartbeat.stop()
+            if self.metrics is not None:
+                self.metrics.close()
+                self.metrics = None
+
+    def _start_failure_detection(self):
+        a = self.args
+        if not self.dist_on or self.world < 2 or a.heartbeat_interval_s <= 0 or self.heartbeat is not None:
+            return
+        try:
+            store = dist.distributed_c10d._get_default_store()
+        except Exception:
+            return
+        self.heartbeat = RankHeartbeat(dist.PrefixStore("tah_b200_hb", store), self.rank, self.world,
+                                       interval_s=a.heartbeat_interval_s).start()
+
+    def _check_device_status(self):
+        """Raise KernelTimeout if a kernel of this step gave up on a bounded wait (reads the status word)."""
+        dev = self.model.device
+        if dev.type == "cuda":
+            from tah_b200.ops import cuda as K
+            K.check_status(dev)
+
+    def _train_loop(self, a, spe, accum, loss_window, t0, start_epoch):
         for epoch in range(start_epoch, int(math.ceil(a.num_train_epochs)) if a.max_steps <= 0 else 10 ** 9):
             micro = list(self._loader(self.train_dataset, a.per_device_train_batch_size, True, epoch))
             skip = (self.state.global_step - epoch * spe) * accum if epoch == start_epoch else 0
@@ -226,14 +285,32 @@ class CustomTaHTrainer:
                 n_items = sum(int((b["labels"][..., 1:] != -100).sum()) for b in window if "labels" in b)
                 n_items = max(n_items, 1)
                 step_loss = 0.0
-                for b in window:
-                    b = self._to_device(b)
-                    out = self.model(**b, num_items_in_batch=n_items)
-                    out.loss.backward()
-                    step_loss += float(out.loss.detach())
-                lr = self._lr_at(self.state.global_step)
-                gnorm = self.optimizer.step(grad_scale=1.0, lr=lr)
-                self.optimizer.zero_grad()
+                if self.heartbeat is not None:
+                    self.heartbeat.check_peers(a.heartbeat_timeout_s)      # before launching kernels that wait on peers
+                t_step = time.perf_counter()
+                n_tok = 0
+                with StepWatchdog(a.step_timeout_s if a.step_timeout_s > 0 else 10 ** 9), \
+                        nvtx_range(f"train/step{self.state.global_step}"):
+                    for b in window:
+                        b = self._to_device(b)
+                        n_tok += int(b["input_ids"].numel()) if "input_ids" in b else 0
+                        with nvtx_range("train/forward"):
+                            out = self.model(**b, num_items_in_batch=n_items)
+                        with nvtx_range("train/backward"):
+                            out.loss.backward()
+                        step_loss += float(out.loss.detach())
+                    lr = self._lr_at(self.state.global_step)
+                    with nvtx_range("train/optimizer"):
+                        gnorm = self.optimizer.step(grad_scale=1.0, lr=lr)
+                    self.optimizer.zero_grad()
+                    self._check_device_status()
+                if self.metrics is not None:
+                    dt = time.perf_counter() - t_step
+                    rec = {"step_s": round(dt, 4), "tokens": n_tok, "tokens_per_s": round(n_tok * self.world / max(dt, 1e-9), 1),
+                           "loss": step_loss}
+                    if self.model.device.type == "cuda":
+                        rec["peak_mem_gb"] = round(torch.cuda.max_memory_allocated(self.model.device) / 2 ** 30, 2)
+                    self.metrics.log(rec, step=self.state.global_step)
                 self.state.global_step += 1
                 self.state.epoch = self.state.global_step / spe
                 loss_window.append(step_loss)
@@ -284,11 +361,18 @@ class CustomTaHTrainer:
     def _save(self, output_dir: Optional[str] = None, state_dict=None):
         output_dir = output_dir or self.args.output_dir
         os.makedirs(output_dir, exist_ok=True)
-        if self.rank == 0:
+        fsdp = getattr(self.model, "_fsdp", None)
+        if fsdp is not None:
+            # parameter-sharded model: every rank takes part in gathering the full 16-bit weights, rank 0 writes
+            with fsdp.materialized():
+                if self.rank == 0:
+                    print(f"Saving TaH model to: {output_dir}")
+                    self.model.save_pretrained(output_dir)
+        elif self.rank == 0:
             print(f"Saving TaH model to: {output_dir}")
             self.model.save_pretrained(output_dir)
-            if self.tokenizer is not None and hasattr(self.tokenizer, "save_pretrained"):
-                self.tokenizer.save_pretrained(output_dir)
+        if self.rank == 0 and self.tokenizer is not None and hasattr(self.tokenizer, "save_pretrained"):
+            self.tokenizer.save_pretrained(output_dir)
 
     def save_model(self, output_dir: Optional[str] = None):
         self._save(output_dir)

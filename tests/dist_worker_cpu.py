@@ -62,6 +62,52 @@ def case_trainer(out):
     out.update(losses=[h["loss"] for h in tr.state.log_history if "loss" in h], steps=tr.state.global_step)
 
 
+def case_fsdp(out):
+    """Parameter-sharded training step (ZeRO-3 schedule on gloo) == ZeroAdamW step on the same data, and the
+    per-rank parameter storage is 1/world of the large matrices."""
+    from tah_b200.parallel.fsdp import FsdpAdamW, shard_model
+    from tah_b200.parallel.zero import ZeroAdamW
+    from tests.helpers import tiny_tah
+    rank, world = dist.get_rank(), dist.get_world_size()
+    g = torch.Generator().manual_seed(3)
+    batches = []
+    for _ in range(3):
+        ids = torch.randint(0, 1024, (world, 2, 24), generator=g)
+        hard = (torch.rand(world, 2, 24, generator=g) < 0.3).long() + 1
+        batches.append((ids, hard))
+    losses = {}
+    params = {}
+    for mode in ("zero2", "zero3"):
+        model = tiny_tah(seed=0)
+        model.train()
+        if mode == "zero3":
+            st = shard_model(model, dist.group.WORLD, torch.device("cpu"), min_shard_numel=1 << 12)
+            opt = FsdpAdamW(model, lr=1e-3, weight_decay=0.01, max_grad_norm=1.0)
+            out.update(units=len(st.units), sharded_bytes=st.sharded_param_bytes(),
+                       local_shard_bytes=sum(u.shard_param.numel() * u.shard_param.element_size() for u in st.units))
+        else:
+            opt = ZeroAdamW(model.parameters(), lr=1e-3, weight_decay=0.01, max_grad_norm=1.0)
+        ls = []
+        for ids, hard in batches:
+            for micro in range(2):                      # two micro-batches per step: gradient accumulation
+                o = model(ids[rank, micro:micro + 1], labels=ids[rank, micro:micro + 1], iter_count_labels=hard[rank, micro:micro + 1])
+                (o.loss / 2).backward()
+                ls.append(float(o.loss))
+            opt.step()
+            opt.zero_grad()
+        losses[mode] = ls
+        if mode == "zero3":
+            with model._fsdp.materialized():
+                params[mode] = {n: p.detach().clone() for n, p in model.named_parameters()}
+            out.update(stats=model._fsdp.stats)
+        else:
+            params[mode] = {n: p.detach().clone() for n, p in model.named_parameters()}
+    err = max(float((params["zero2"][n] - params["zero3"][n]).abs().max()) for n in params["zero2"])
+    dl = max(abs(a - b) for a, b in zip(losses["zero2"], losses["zero3"]))
+    out.update(param_err=err, loss_err=dl, losses=losses["zero3"])
+    assert err < 2e-5 and dl < 1e-4, (err, dl)
+
+
 def case_heartbeat(out):
     """Rank 1 leaves between steps; rank 0 learns of it from the store before its next collective."""
     from tah_b200.utils.failure import RankFailure, RankHeartbeat

@@ -41,6 +41,18 @@ def test_trainer_loss_curve_is_world_size_invariant(tmp_path):
     assert abs(a[0] - b[0]) < 1e-4 and abs(a[1] - b[1]) < 5e-3
 
 
+def test_parameter_sharded_step_matches_replicated_step(tmp_path):
+    """ZeRO-3 schedule (gather per layer and pass, re-gather in backward, per-unit reduce-scatter, sharded AdamW)
+    on two gloo ranks gives the parameters and losses of the ZeRO-2 optimizer on the same data."""
+    res, ranks = _run("fsdp", 2, tmp_path, 29716, timeout=400)
+    assert res.returncode == 0, res.stderr[-3000:]
+    r = ranks[0]
+    assert r["param_err"] < 2e-5 and r["loss_err"] < 1e-4
+    assert r["units"] == 5 and r["local_shard_bytes"] * 2 == r["sharded_bytes"]
+    # every layer is gathered in both passes, forward and backward, and reduce-scattered once per micro-batch
+    assert r["stats"]["reduce_scatters"] == 5 * 6 and r["stats"]["gathers"] >= 4 * 3 * 6
+
+
 def test_heartbeat_detects_a_rank_that_left(tmp_path):
     res, ranks = _run("heartbeat", 2, tmp_path, 29714, timeout=120)
     assert ranks[0]["detected"] == [1] and ranks[0]["seconds"] < 8 and ranks[1]["left"] is True

@@ -203,3 +203,22 @@ def test_fast_forward_gives_valid_state_at_a_deeper_context():
             n = (int(eng.kv.len[d][r]) + eng.page_size - 1) // eng.page_size
             used += eng.kv.page_table[d][r, :n].tolist()
         assert len(used) == len(set(used))
+
+
+def test_engine_with_head_dim_128_uses_fused_kernels_and_matches_unfused(monkeypatch):
+    """head_dim 128 takes the fused QKV epilogue (and the fused norm + LoRA-A launch); the unfused chain gives
+    the same tokens."""
+    from tah_b200.engine import TaHEngine
+    B, T, n_new = 4, 16, 20
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16, head_dim=128, num_attention_heads=2, num_key_value_heads=1).cuda().eval()
+    ids = torch.randint(0, 1024, (B, T), generator=torch.Generator().manual_seed(2)).cuda()
+    outs = []
+    for no_fuse in ("0", "1"):
+        monkeypatch.setenv("TAH_B200_NO_FUSE", no_fuse)
+        eng = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, use_cuda_graph=True, deep_fraction=1.0)
+        eng.hard_override = eng.make_bernoulli_override(B, (0.3,), seed=5)
+        res = eng.generate(ids, None, max_new_tokens=n_new, do_sample=False)
+        outs.append((res.tokens, eng.kernel_launches_per_tick))
+    assert outs[0][1] < outs[1][1]                                         # fewer launches per tick
+    same = sum(a == b for ra, rb in zip(outs[0][0], outs[1][0]) for a, b in zip(ra, rb))
+    assert same >= 0.9 * B * n_new, same

@@ -185,7 +185,29 @@ def test_code_sanitize_and_evaluate(tmp_path):
     samples.write_text(json.dumps({"task_id": "t/0", "solution": code}) + "\n" +
                        json.dumps({"task_id": "t/0", "solution": "def add1(x):\n    return x"}) + "\n")
     res = codeeval.evaluate("toy", str(samples), problems_path=str(problems), parallel=2, ks=(1, 2))
-    assert abs(res["pass_at_k"]["pass@1"] - 0.5) < 1e-9 and res["pass_at_k"]["pass@2"] == 1.0
+    assert abs(res["pass_at_k"]["base"]["pass@1"] - 0.5) < 1e-9 and res["pass_at_k"]["base"]["pass@2"] == 1.0
+    # a second call loads the stored result file instead of re-running
+    again = codeeval.evaluate("toy", str(samples), problems_path=str(problems), parallel=2, ks=(1, 2))
+    assert again["pass_at_k"] == res["pass_at_k"]
+
+
+def test_code_evaluate_against_canonical_ground_truth(tmp_path, monkeypatch):
+    """Problems in the base/plus-input shape: expected outputs come from the canonical solution (cached on
+    disk); a solution that is right on the base inputs only passes 'base' but not 'plus'."""
+    monkeypatch.setattr(codeeval, "CACHE_DIR", str(tmp_path / "cache"))
+    pb = {"task_id": "t/0", "entry_point": "absdiff", "prompt": "def absdiff(a, b):\n",
+          "canonical_solution": "    return abs(a - b)\n", "base_input": [[3, 1], [5, 2]], "plus_input": [[1, 4], [2.0, 2.5]],
+          "atol": 1e-6}
+    problems = tmp_path / "p.jsonl"
+    problems.write_text(json.dumps(pb) + "\n")
+    samples = tmp_path / "s.jsonl"
+    samples.write_text(json.dumps({"task_id": "t/0", "solution": "def absdiff(a, b):\n    return abs(a - b)"}) + "\n" +
+                       json.dumps({"task_id": "t/0", "completion": "    return a - b\n"}) + "\n")
+    res = codeeval.evaluate("toy", str(samples), problems_path=str(problems), parallel=2, ks=(1,))
+    assert res["pass_at_k"]["base"]["pass@1"] == 1.0
+    assert abs(res["pass_at_k"]["plus"]["pass@1"] - 0.5) < 1e-9
+    assert res["eval"]["t/0"][1]["plus_status"] == "fail" and res["eval"]["t/0"][1]["plus_fail_tests"]
+    assert len(os.listdir(tmp_path / "cache")) == 1
 
 
 def test_download_retries_with_backoff(monkeypatch):
@@ -209,3 +231,44 @@ def test_labeller_helpers():
     assert label._categorize_masks([1, 2, 151667, 3, 4]) == [0, 0, 1, 1, 1]
     mm = label._calculate_mismatch(torch.tensor([5, 6, 7, 8]), torch.tensor([1, 5, 9, 7]))
     assert mm.tolist() == [0, 1, 0, 0]                                # pred[i] vs real[i+1]; last stays 0
+
+
+def test_label_selection_token_table_and_grouping(tmp_path):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "script", "preparation"))
+    import label
+    path = tmp_path / "d.jsonl"
+    path.write_text("".join(json.dumps({"question": f"q{i}", "answer": f"a{i}"}) + "\n" for i in range(10)))
+    assert [s["question"] for s in label.load_samples(str(path), (2, 7))] == ["q2", "q3", "q4", "q5", "q6"]
+    sub = label.load_samples(str(path), None, 4)
+    assert len(sub) == 4 and sub == label.load_samples(str(path), None, 4)          # seeded sub-sample
+    (tmp_path / "d.json").write_text(json.dumps([{"question": "x", "answer": "y"}]))
+    assert len(label.load_samples(str(tmp_path / "d.json"))) == 1
+    assert label.gpu_ranges(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    rows = [{"data_id": 7, "real_token": [1, 2, 3], "predictions": [2, 9, 9], "mask": [0, 1, 1], "mismatch": [0, 1, 0],
+             "entropy": [0.1, 0.2, 0.3]},
+            {"data_id": 3, "real_token": [4, 5], "predictions": [5, 5], "mask": [1, 1], "mismatch": [0, 0],
+             "entropy": [0.4, 0.5]}]
+    table = label.token_table(rows, save_entropy=True, save_ce=False)
+    assert set(table) == {"predictions", "small_token", "data_id", "mask", "real_token", "mismatch", "entropy"}
+    assert table["small_token"] == [0, 1, 2, 0, 1] and table["data_id"] == [7, 7, 7, 3, 3]
+    samples = label.samples_from_token_table(table, lambda ids: " ".join(map(str, ids)))
+    assert [s["data_id"] for s in samples] == [3, 7]
+    assert samples[1] == {"data_id": 7, "real_text": "1 2 3", "real_token": [1, 2, 3], "mask": [0, 1, 1],
+                          "mismatch": [0, 1, 0], "entropy": [0.1, 0.2, 0.3]}
+    assert label.label_statistics(samples) == {"samples": 2, "tokens": 5, "mismatch": 1, "assistant_tokens": 4,
+                                               "assistant_mismatch": 1}
+    args = label.build_parser().parse_args(["--dataset_path", "d", "--test_model_list", "a", "b", "--output_path", "o",
+                                            "--index_range", "0", "5", "--is_cutoff", "True", "--save_ce"])
+    assert args.test_model_list == ["a", "b"] and args.is_cutoff is True and args.index_range == [0, 5] and args.top_k == -1
+
+
+def test_prune_reads_calibration_from_a_saved_dataset(tmp_path):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "script", "preparation"))
+    import prune
+    from datasets import Dataset
+    Dataset.from_dict({"real_text": ["alpha", "", "beta", "gamma"], "n": [1, 2, 3, 4]}).save_to_disk(str(tmp_path / "ds"))
+    assert prune.read_calibration_texts(str(tmp_path / "ds"), "real_text", 2) == ["alpha", "beta"]
+    with pytest.raises(KeyError):
+        prune.read_calibration_texts(str(tmp_path / "ds"), "text", 2)
+    (tmp_path / "c.txt").write_text("one\n\ntwo\n")
+    assert prune.read_calibration_texts(str(tmp_path / "c.txt")) == ["one", "two"]

@@ -128,6 +128,71 @@ def test_qk_norm_rope_and_paged_write(hd, nq, nkv):
     assert torch.equal(cache[pg, 1, :, off], vd.view(M, nkv, hd))
 
 
+@pytest.mark.parametrize("M,nq,nkv,R,bn,splits", [(37, 16, 8, 0, 0, None), (256, 16, 8, 192, 0, None), (300, 4, 2, 64, 128, 2),
+                                                   (256, 2, 1, 64, 128, 1), (200, 16, 8, 0, 256, 4), (16, 4, 4, 64, 16, 1)])
+def test_gemm_qkv_fused_epilogue_equals_gemm_then_qk_norm_rope(M, nq, nkv, R, bn, splits):
+    """QKV GEMM with the QK-norm / RoPE / KV-write epilogue == plain GEMM followed by the separate kernel
+    (bit for bit: both round the projection to bf16 first), and both match the fp32 statement."""
+    Kc = _cuda()
+    from tah_b200.models.qwen3 import apply_rope, rope_cos_sin
+    from tah_b200.ops import torch_ref
+    hd, K, page = 128, 512, 16
+    F = (nq + 2 * nkv) * hd
+    x, w = _rand(M, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    x2 = _rand(M, R, seed=3) if R else None
+    w2 = _rand(F, R, scale=0.05, seed=4) if R else None
+    qw, kw = (_rand(hd, seed=5).float() * 0.1 + 1).bfloat16(), (_rand(hd, seed=6).float() * 0.1 + 1).bfloat16()
+    pos = torch.randint(0, 5000, (M,), device="cuda", dtype=torch.int32)
+    n_pages = (M + page - 1) // page + 2
+    slot = torch.randperm(n_pages * page, device="cuda")[:M].to(torch.int32)
+    slot[M // 2] = -1                                                   # a row that must not touch the cache
+    sel = (torch.arange(M, device="cuda") % 2).to(torch.int32)
+    outs = []
+    for fused in (False, True, "table"):
+        caches = [torch.zeros(n_pages, 2, nkv, page, hd, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        kd = torch.zeros(M, nkv * hd, dtype=torch.bfloat16, device="cuda")
+        vd = torch.zeros_like(kd)
+        if fused:
+            table = Kc.rope_table(pos, hd, 1e6) if fused == "table" else None      # cos | sin computed once per pass
+            q = Kc.gemm_qkv(x, w, qw, kw, pos, nq, nkv, 1e-6, 1e6, x2=x2, w2=w2, k_dense=kd, v_dense=vd, caches=caches,
+                            cache_sel=sel, slot=slot, page_size=page, bn=bn, splits=splits, rope_cs=table)
+        else:
+            qkv = Kc.gemm(x, w, x2=x2, w2=w2, bn=bn, splits=splits)
+            q = Kc.qk_norm_rope_kv(qkv, qw, kw, pos, nq, nkv, hd, 1e-6, 1e6, k_dense=kd, v_dense=vd, caches=caches,
+                                   cache_sel=sel, slot=slot, page_size=page)
+        Kc.check_status()
+        outs.append((q, kd, vd, caches))
+    (q0, k0, v0, c0), (q1, k1, v1, c1), (q2, k2, v2, c2) = outs
+    assert torch.equal(q0, q1) and torch.equal(k0, k1) and torch.equal(v0, v1)
+    assert torch.equal(c0[0], c1[0]) and torch.equal(c0[1], c1[1])
+    assert torch.equal(q0, q2) and torch.equal(k0, k2) and torch.equal(c0[0], c2[0]) and torch.equal(c0[1], c2[1])
+    assert float(c1[0].abs().sum()) > 0 and float(c1[1].abs().sum()) > 0
+    ref = x.float() @ w.float().t() + (x2.float() @ w2.float().t() if R else 0)
+    qr, kr, vr = ref.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
+    cos, sin = rope_cos_sin(pos[None].long(), hd, 1e6, torch.float32)
+    q_ref = apply_rope(torch_ref.rms_norm(qr.view(1, M, nq, hd), qw.float(), 1e-6), cos, sin)[0]
+    _close(q1.view(M, nq, hd), q_ref, atol=6e-2, rtol=3e-2)
+    _close(v1, vr, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,H,R", [(9, 2048, 192), (256, 2048, 128), (33, 1024, 72), (5, 2560, 64)])
+def test_rmsnorm_lora_fused(M, H, R):
+    """RMSNorm + gated LoRA-A in one launch against the two separate kernels and the fp32 statement."""
+    Kc = _cuda()
+    from tah_b200.ops import torch_ref
+    x, w = _rand(M, H, seed=1), (_rand(H, seed=2).float() * 0.1 + 1).to(torch.bfloat16)
+    A = _rand(R, H, scale=H ** -0.5, seed=3)
+    gate = (torch.rand(M, device="cuda") < 0.3).to(torch.int32)
+    gate[0] = 1
+    t = torch.full((M, R + 8), 5.0, dtype=torch.bfloat16, device="cuda")
+    y, _ = Kc.rms_norm_lora(x, w, 1e-6, gate, A, t_out=t[:, :R])
+    y_ref = torch_ref.rms_norm(x, w, 1e-6)
+    _close(y, y_ref, atol=1e-2, rtol=1e-2)
+    assert torch.equal(Kc.lora_a_rows(y, A, gate), t[:, :R].contiguous())        # same bits as the separate kernel
+    _close(t[:, :R], (y.float() @ A.float().t()) * gate[:, None], atol=2e-2, rtol=2e-2)
+    assert (t[:, R:] == 5.0).all() and (t[gate == 0][:, :R] == 0).all()
+
+
 def _paged_setup(rows, lens, nkv, hd, page, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     max_pages = (max(lens) + page - 1) // page + 1

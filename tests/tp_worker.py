@@ -52,13 +52,16 @@ def main():
             lo, hi = tp.rows_of(M)
             e1 = (h[lo:hi].float() - h_ref[lo:hi].float()).abs().max().item()
             e2 = (xn.float() - xn_ref.float()).abs().max().item()
-            # the sum of `world` N(0,1) partials reaches ~4 sqrt(world): allow two bf16 ulps at that size
-            # (the in-switch reduction does not promise the reference's summation order)
-            tol = 0.07 if world <= 2 else 0.26
-            good = e1 < tol and e2 < tol
+            # the reference sums in fp32 and rounds once; the kernel (or the switch) may sum in another order, so
+            # allow two bf16 ulps at the largest magnitude of each tensor: h reaches ~4 sqrt(world), the
+            # normalised rows stay O(1)
+            tol_h = float(h_ref.float().abs().max()) * 2.0 ** -7
+            tol_x = max(0.03, float(xn_ref.float().abs().max()) * 2.0 ** -7)
+            good = e1 <= tol_h and e2 <= tol_x
             ok = ok and good
             if rank == 0:
-                print(f"fused_reduce_norm multicast={use_mc} iter={it}: max err h {e1:.4f} xn {e2:.4f} {'ok' if good else 'BAD'}")
+                print(f"fused_reduce_norm multicast={use_mc} iter={it}: max err h {e1:.4f} (tol {tol_h:.4f}) xn {e2:.4f} "
+                      f"(tol {tol_x:.4f}) {'ok' if good else 'BAD'}")
         dist.barrier()
 
     # ---- push path: GEMM epilogue = reduce-scatter by peer stores, owner kernel, flag-waiting consumer ----
@@ -101,6 +104,28 @@ def main():
             if rank == 0:
                 print(f"push path multicast={use_mc} iter={it}: max err h {e1:.4f} consumer {e2:.4f} xn {e3:.4f} {'ok' if good else 'BAD'}")
             dist.barrier()
+
+    # ---- vocabulary-parallel top-k / arg-max merge by peer stores (no NCCL) against the NCCL + sort form ----
+    tp = TensorParallel(dist.group.WORLD, dev, use_multicast=False)
+    for rows, k in ((16, 100), (64, 20), (16, 1), (16, 100)):
+        for it in range(3):
+            g = torch.Generator(device=dev).manual_seed(500 * it + rank)
+            shard = torch.randn(rows, 4096, generator=g, device=dev).to(torch.bfloat16)
+            shard[:, :8] = 3.0                                    # ties inside and across shards
+            vals, idx = K.topk_rows(shard, k)
+            lo = rank * 4096
+            mv, mi = tp.merge_topk(vals, idx, lo, k)
+            rv, ri = tp.merge_topk_nccl(vals, idx, lo, k)
+            torch.cuda.synchronize()
+            K.check_status(dev)
+            good = torch.equal(mv, rv) and torch.equal(mi, ri)
+            if k == 1:
+                am = tp.merge_argmax(vals[:, 0].contiguous(), idx[:, 0].contiguous(), lo)
+                good = good and torch.equal(am, tp.merge_argmax_nccl(vals[:, 0], idx[:, 0], lo))
+            ok = ok and good
+            if rank == 0 and (it == 0 or not good):
+                print(f"topk merge rows={rows} k={k} iter={it}: {'ok' if good else 'BAD'}")
+    dist.barrier()
 
     # ---- sharded parameters: all-gather by push on a side stream, consumed by the GEMM through flags ----
     from tah_b200.parallel.fsdp import ShardedWeightStore
