@@ -25,7 +25,9 @@ copy of the 256 new token ids per tick).
 ``vs_eager`` compares with the same model run through plain PyTorch ops (the restated reference: cuBLAS GEMMs,
 SDPA with a materialised duo-causal mask, unfused LoRA, ``torch.cat`` KV cache, token-by-token Python loop) at
 the same batch and prompt, over its first decode steps (its cheapest context).  ``train`` is the SFT step of the
-same model (CE + decider BCE, second iteration on every token, sequence 8192, sharded AdamW) on the same GPUs.
+same model (CE + decider BCE, second iteration on every token, sequence 8192; on 2+ GPUs parameters, gradients and
+optimizer state sharded - ZeRO-3 / FSDP with the layer-wise gather consumed by the first GEMM - on one GPU the same
+step with the fused AdamW) on the same GPUs.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|eager]
 """
@@ -306,8 +308,9 @@ def run_ours(args):
     train = None
     if not args.no_train:
         import bench_train
+        strategy = args.train_strategy if args.train_strategy != "auto" else ("zero3" if world > 1 else "zero2")
         ta = argparse.Namespace(seq=8192, accum=1, hard_rate=None, train_model=MODEL, decider="oracle-mlp",
-                                lora_rank=LORA_R, strategy=args.train_strategy, checkpoint=False)
+                                lora_rank=LORA_R, strategy=strategy, checkpoint=False)
         try:
             train = bench_train.run(ta, steps=2, warmup=1)
         except Exception as exc:
@@ -510,7 +513,8 @@ def main():
     ap.add_argument("--ref-batch", type=int, default=0)
     ap.add_argument("--no-eager", action="store_true", help="skip the eager anchor")
     ap.add_argument("--no-train", action="store_true", help="skip the training sub-record")
-    ap.add_argument("--train-strategy", default="zero2", choices=["zero2", "zero3"])
+    ap.add_argument("--train-strategy", default="auto", choices=["auto", "zero2", "zero3"],
+                    help="training sub-record: zero3 = parameters sharded too (FSDP); auto = zero3 on 2+ GPUs")
     ap.add_argument("--e2e-new-tokens", type=int, default=0, help="new tokens of the end-to-end call (0 = the workload's)")
     # the defaults are the headline configuration (batch 256 x prompt 256 -> 2048 new tokens on the
     # 28-layer model); the flags below select the other serving configurations, e.g.

@@ -317,6 +317,88 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, __nv_bfloat16* __
 }
 
 // ---------------------------------------------------------------------------------------------
+// LayerNorm over the last dimension (bf16 in / out, fp32 statistics): y = (x - mean) * rstd * w + b.
+// One warp per row (D <= 4096, D % 8 == 0); with `dot_w` the normalised row is not stored but reduced
+// against dot_w (+ dot_b) into z[r] (fp32): the output layer LayerNorm -> Linear(D, 1) of the decider.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) layernorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                        const __nv_bfloat16* __restrict__ w,
+                                                        const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                        const __nv_bfloat16* __restrict__ dot_w,
+                                                        const __nv_bfloat16* __restrict__ dot_b, float* __restrict__ z,
+                                                        int M, int D, long long ldx, long long ldy, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= M) return;
+  const int nvec = D / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
+  constexpr int VPT = 16;                      // D <= 32 * 8 * 16 = 4096
+  uint4 v[VPT];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      v[i] = xr[idx];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); sum += f.x + f.y; }
+    }
+  }
+  const float mean = warp_sum(sum) / (float)D;
+  float var = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        var += (f.x - mean) * (f.x - mean) + (f.y - mean) * (f.y - mean);
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(var) / (float)D + eps);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = lane + i * 32;
+    if (idx < nvec) {
+      const uint4 wv = reinterpret_cast<const uint4*>(w)[idx];
+      const uint4 bv = reinterpret_cast<const uint4*>(b)[idx];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]), g = __bfloat1622float2(wh[j]), c = __bfloat1622float2(bh[j]);
+        oh[j] = __floats2bfloat162_rn((f.x - mean) * rstd * g.x + c.x, (f.y - mean) * rstd * g.y + c.y);
+      }
+      if (dot_w == nullptr) {
+        reinterpret_cast<uint4*>(y + (size_t)r * ldy)[idx] = o;
+      } else {
+        const uint4 dv = reinterpret_cast<const uint4*>(dot_w)[idx];
+        const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 yn = __bfloat1622float2(oh[j]), d = __bfloat1622float2(dh[j]);
+          acc += yn.x * d.x + yn.y * d.y;
+        }
+      }
+    }
+  }
+  if (dot_w != nullptr) {
+    acc = warp_sum(acc);
+    if (lane == 0) z[r] = bf16_round(acc + (dot_b != nullptr ? __bfloat162float(dot_b[0]) : 0.f));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Embedding gather: out[r] = E[tok[r]]  (tok < 0 -> zeros)
 // ---------------------------------------------------------------------------------------------
 __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ E, const int* __restrict__ tok,
@@ -632,6 +714,19 @@ extern "C" int tahb_qk_norm_rope_kv(const void* qkv, const void* q_w, const void
   if (hd == 128) e = launch_chain(qk_norm_rope_kv_kernel<128>, dim3(blocks), dim3(128), 0, stream, p);
   else if (hd == 64) e = launch_chain(qk_norm_rope_kv_kernel<64>, dim3(blocks), dim3(128), 0, stream, p);
   else return -2;
+  return e == cudaSuccess ? 0 : -3;
+}
+
+// y = LayerNorm(x) * w + b per row; or, with dot_w, z[r] = bf16(LayerNorm(x[r]) . dot_w + dot_b) (fp32 out).
+extern "C" int tahb_layernorm(const void* x, const void* w, const void* b, void* y, const void* dot_w, const void* dot_b,
+                              float* z, int M, int D, long long ldx, long long ldy, float eps, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (D % 8 || D > 4096) return -1;
+  cudaError_t e = launch_chain(layernorm_kernel, dim3((M + 3) / 4), dim3(128), 0, stream,
+                               reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+                               reinterpret_cast<const __nv_bfloat16*>(b), reinterpret_cast<__nv_bfloat16*>(y),
+                               reinterpret_cast<const __nv_bfloat16*>(dot_w), reinterpret_cast<const __nv_bfloat16*>(dot_b),
+                               z, M, D, ldx, ldy, eps);
   return e == cudaSuccess ? 0 : -3;
 }
 

@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <stdio.h>
 
+#include "attn_common.cuh"
 #include "common.cuh"
 
 namespace tahb {
@@ -48,6 +49,13 @@ struct GemmParams {
   int pair;     // DUAL kernels only. 0: SwiGLU of the two accumulators.  1: the accumulators are two plain
                 // output tiles (features f0.. and up_off + f0..) that share the CTA's activation tile, which
                 // halves the activation bytes a CTA pulls per unit of work (requires the staged/TMA output path)
+  int act;      // epilogue activation on the (non-dual) output: 0 none, 1 GELU (erf form) of the bf16-rounded value
+  // Operand majors (backward GEMMs read their operands transposed, straight from the row-major tensors):
+  //   a_mn: the 128-row operand is stored [reduction, feature] (feature contiguous): dgrad reads W[F, K] as
+  //         W^T, wgrad reads X[T, K] as X^T;   b_mn: the column operand is stored [reduction, column]
+  //         (wgrad reads dY[T, F] as dY^T).  Such tiles are loaded as 64 x 64 boxes and described to the tensor
+  //         core as MN-major.  0 = K-major (the reduction index is contiguous), the forward layout.
+  int a_mn, b_mn;
   int* status;
   // Tensor-parallel reduce-scatter by push (row-parallel GEMMs): instead of writing `out`, the tile
   // is stored into the symmetric slot buffer of the rank that owns its token rows,
@@ -105,6 +113,8 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float* v) {
   else tmem_ld16(taddr, v);
 }
 
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+
 template <bool DUAL>
 __device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, float a, float u) {
   float y;
@@ -112,7 +122,8 @@ __device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, flo
     y = bf16_round(silu(bf16_round(a))) * bf16_round(u);
   } else {
     y = a;
-    if (p.residual != nullptr) y = bf16_round(a) + __bfloat162float(p.residual[(size_t)t * p.ld_res + f]);
+    if (p.act == 1) y = gelu_erf(bf16_round(a));
+    if (p.residual != nullptr) y = bf16_round(y) + __bfloat162float(p.residual[(size_t)t * p.ld_res + f]);
   }
   p.out[(size_t)t * p.ld_out + f] = __float2bfloat16_rn(y);
 }
@@ -120,13 +131,14 @@ __device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, flo
 // Epilogue value into the shared staging tile; with `add_res` the slot already holds the residual
 // element (brought in by a TMA load).
 template <bool DUAL>
-__device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u, bool add_res) {
+__device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u, bool add_res, int act = 0) {
   float y;
   if constexpr (DUAL) {
     y = bf16_round(silu(bf16_round(a))) * bf16_round(u);
   } else {
     y = a;
-    if (add_res) y = bf16_round(a) + __bfloat162float(*slot);
+    if (act == 1) y = gelu_erf(bf16_round(a));
+    if (add_res) y = bf16_round(y) + __bfloat162float(*slot);
   }
   *slot = __float2bfloat16_rn(y);
 }
@@ -202,68 +214,97 @@ __device__ __forceinline__ void qkv_epilogue(const GemmParams& p, const __nv_bfl
       inv[i] = exp2f(-(2.0f * (float)j / 128.0f) * p.log2_theta);
     }
   }
-  for (int r = w4; r < n_tok; r += 4) {
-    const int t = ta + r;
-    if (t >= p.M) break;
-    const uint2 raw = *reinterpret_cast<const uint2*>(stg + r * 128 + lane * 4);
-    const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float x[4];
-    {
+  // Four tokens per warp and step, written phase by phase: only four warps run here, so the latency of a
+  // token's dependent chain (reduction, shuffles, roundings) is hidden by the other three tokens' chains.
+  constexpr int U = 4;
+  for (int r0 = w4; r0 < n_tok; r0 += 4 * U) {
+    int rr[U];
+    bool live[U];
+    uint2 raw[U], outv[U];
+    float x[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      rr[u] = r0 + 4 * u;
+      live[u] = rr[u] < n_tok && ta + rr[u] < p.M;
+      raw[u] = live[u] ? *reinterpret_cast<const uint2*>(stg + rr[u] * 128 + lane * 4) : make_uint2(0u, 0u);
+      const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
       const float2 a = __bfloat1622float2(rh[0]), b = __bfloat1622float2(rh[1]);
-      x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+      x[u][0] = a.x; x[u][1] = a.y; x[u][2] = b.x; x[u][3] = b.y;
+      outv[u] = raw[u];
     }
-    uint2 outv = raw;
     if (is_q || is_k) {
-      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
-      ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss / 128.0f + p.qk_eps);
-      float n[4], partner[4], y[4];
+      float ss[U];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) n[i] = bf16_round(wv[i] * bf16_round(x[i] * rstd));
+      for (int u = 0; u < U; ++u) ss[u] = x[u][0] * x[u][0] + x[u][1] * x[u][1] + x[u][2] * x[u][2] + x[u][3] * x[u][3];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, n[i], 16);
-      float cv[4], sv[4];
-      if (table) {
-        // lane l owns dims 4l .. 4l+3, whose frequency index is 4 (l mod 16) ..: cos there, sin 64 further
-        const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(s_cs + r * 16) + (lane & 15) * 4;
-        const uint2 cr = *reinterpret_cast<const uint2*>(row), sr = *reinterpret_cast<const uint2*>(row + 64);
-        const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&cr);
-        const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&sr);
-        const float2 c0 = __bfloat1622float2(ch[0]), c1 = __bfloat1622float2(ch[1]);
-        const float2 s0 = __bfloat1622float2(sh[0]), s1 = __bfloat1622float2(sh[1]);
-        cv[0] = c0.x; cv[1] = c0.y; cv[2] = c1.x; cv[3] = c1.y;
-        sv[0] = s0.x; sv[1] = s0.y; sv[2] = s1.x; sv[3] = s1.y;
-      } else {
-        const float posf = (float)p.pos[t];
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], o);
+      }
+      float n[U][4], partner[U][4];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float rstd = rsqrtf(ss[u] / 128.0f + p.qk_eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) n[u][i] = bf16_round(wv[i] * bf16_round(x[u][i] * rstd));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) partner[u][i] = __shfl_xor_sync(0xffffffffu, n[u][i], 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float cv[4], sv[4];
+        if (table) {
+          // lane l owns dims 4l .. 4l+3, whose frequency index is 4 (l mod 16) ..: cos there, sin 64 further
+          const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(s_cs + (live[u] ? rr[u] : 0) * 16) + (lane & 15) * 4;
+          const uint2 cr = *reinterpret_cast<const uint2*>(row), sr = *reinterpret_cast<const uint2*>(row + 64);
+          const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&cr);
+          const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&sr);
+          const float2 c0 = __bfloat1622float2(ch[0]), c1 = __bfloat1622float2(ch[1]);
+          const float2 s0 = __bfloat1622float2(sh[0]), s1 = __bfloat1622float2(sh[1]);
+          cv[0] = c0.x; cv[1] = c0.y; cv[2] = c1.x; cv[3] = c1.y;
+          sv[0] = s0.x; sv[1] = s0.y; sv[2] = s1.x; sv[3] = s1.y;
+        } else {
+          const float posf = live[u] ? (float)p.pos[ta + rr[u]] : 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float ang = posf * inv[i];
+            cv[i] = bf16_round(cosf(ang));
+            sv[i] = bf16_round(sinf(ang));
+          }
+        }
+        float y[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float ang = posf * inv[i];
-          cv[i] = bf16_round(cosf(ang));
-          sv[i] = bf16_round(sinf(ang));
+          const float rot = upper ? partner[u][i] : -partner[u][i];
+          y[i] = bf16_round(bf16_round(n[u][i] * cv[i]) + bf16_round(rot * sv[i]));
         }
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0], y[1]), o1 = __floats2bfloat162_rn(y[2], y[3]);
+        outv[u].x = *reinterpret_cast<uint32_t*>(&o0);
+        outv[u].y = *reinterpret_cast<uint32_t*>(&o1);
       }
+    }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float rot = upper ? partner[i] : -partner[i];
-        y[i] = bf16_round(bf16_round(n[i] * cv[i]) + bf16_round(rot * sv[i]));
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      const int t = ta + rr[u];
+      if (is_q) {
+        *reinterpret_cast<uint2*>(p.q_out + ((size_t)t * p.nq + h) * 128 + lane * 4) = outv[u];
+        continue;
       }
-      __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0], y[1]), o1 = __floats2bfloat162_rn(y[2], y[3]);
-      outv.x = *reinterpret_cast<uint32_t*>(&o0);
-      outv.y = *reinterpret_cast<uint32_t*>(&o1);
-    }
-    if (is_q) {
-      *reinterpret_cast<uint2*>(p.q_out + ((size_t)t * p.nq + h) * 128 + lane * 4) = outv;
-      continue;
-    }
-    const int kvh = is_k ? h - p.nq : h - p.nq - p.nkv;
-    __nv_bfloat16* dense = is_k ? p.k_dense : p.v_dense;
-    if (dense != nullptr) *reinterpret_cast<uint2*>(dense + ((size_t)t * p.nkv + kvh) * 128 + lane * 4) = outv;
-    const int sl = s_slot[r];
-    if (sl >= 0) {
-      __nv_bfloat16* cache = p.kv_cache[s_sel[r]];
-      const int page = sl / p.page_size, off = sl % p.page_size;
-      *reinterpret_cast<uint2*>(cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * 128 +
-                                lane * 4) = outv;
+      const int kvh = is_k ? h - p.nq : h - p.nq - p.nkv;
+      __nv_bfloat16* dense = is_k ? p.k_dense : p.v_dense;
+      if (dense != nullptr) *reinterpret_cast<uint2*>(dense + ((size_t)t * p.nkv + kvh) * 128 + lane * 4) = outv[u];
+      const int sl = s_slot[rr[u]];
+      if (sl >= 0) {
+        const int sel = s_sel[rr[u]];
+        __nv_bfloat16* cache = sel == 0 ? p.kv_cache[0] : sel == 1 ? p.kv_cache[1] : sel == 2 ? p.kv_cache[2] : p.kv_cache[3];
+        const int page = sl / p.page_size, off = sl % p.page_size;
+        *reinterpret_cast<uint2*>(cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off) * 128 +
+                                  lane * 4) = outv[u];
+      }
     }
   }
 }
@@ -342,16 +383,27 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const CUtensorMap* mw = ext ? &tm_w2 : &tm_w;
         const CUtensorMap* mx = ext ? &tm_x2 : &tm_x;
         uint8_t* st = smem + s * C::STAGE_BYTES;
-        tma_load_2d(st, mw, x, f0, &full_bar[s]);
+        if (p.a_mn) {                       // [64 reduction rows][64 features] boxes, 8 KiB each
+          tma_load_2d(st, mw, f0, x, &full_bar[s]);
+          tma_load_2d(st + 8192, mw, f0 + 64, x, &full_bar[s]);
+        } else {
+          tma_load_2d(st, mw, x, f0, &full_bar[s]);
+        }
         if constexpr (DUAL) tma_load_2d(st + C::W_TILE, mw, x, p.up_off + f0, &full_bar[s]);
-        tma_load_2d(st + C::W_BYTES, mx, x, t0, &full_bar[s]);
+        if (p.b_mn) {
+#pragma unroll
+          for (int j = 0; j < (BN >= 64 ? BN / 64 : 1); ++j)
+            tma_load_2d(st + C::W_BYTES + j * 8192, mx, t0 + j * 64, x, &full_bar[s]);
+        } else {
+          tma_load_2d(st + C::W_BYTES, mx, x, t0, &full_bar[s]);
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(128, BN);
+      const uint32_t idesc = umma_idesc_bf16(128, BN) | (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % C::NS;
         const uint32_t ph = (i / C::NS) & 1;
@@ -361,9 +413,12 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t b_addr = a_addr + C::W_BYTES;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t db = umma_desc_sw128(b_addr + k * 32);
+          // K-major: 16 reduction elements = 32 bytes along the swizzled row; MN-major: 16 reduction rows of
+          // 128 bytes = 2048 bytes, the next 64 features / columns 8192 bytes further
+          const uint64_t db = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, 8192) : umma_desc_sw128(b_addr + k * 32);
+          const uint64_t da = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, 8192) : umma_desc_sw128(a_addr + k * 32);
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), db, idesc, acc);
+          umma_bf16(tmem_base, da, db, idesc, acc);
           if constexpr (DUAL) umma_bf16(tmem_base + BN, umma_desc_sw128(a_addr + C::W_TILE + k * 32), db, idesc, acc);
         }
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
@@ -408,7 +463,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         } else if (p.tma_out) {
 #pragma unroll
           for (int j = 0; j < C::CHUNK; ++j)
-            stage_one<DUAL>(stg + (c0 + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
+            stage_one<DUAL>(stg + (c0 + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma, p.act);
         } else if (f < p.F) {
 #pragma unroll
           for (int j = 0; j < C::CHUNK; ++j) {
@@ -523,7 +578,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
         } else if (p.tma_out) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) stage_one<DUAL>(stg + (c + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
+          for (int j = 0; j < 16; ++j) stage_one<DUAL>(stg + (c + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma, p.act);
         } else if (f < p.F) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -594,6 +649,21 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+// MN-major operand of a [reduction_rows, mn_cols] row-major bf16 matrix: 64 x 64 boxes, 128-byte swizzle.
+static int make_map_mn(CUtensorMap* m, const void* base, long long red_rows, long long mn_cols, long long ld) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
+  cuuint64_t dims[2] = {(cuuint64_t)mn_cols, (cuuint64_t)red_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, 64u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;
 }
@@ -672,15 +742,21 @@ struct GemmTpArgs {
 static int gemm_impl(const void* W, const void* X, void* out, const void* residual, const void* W2,
                      const void* X2, int M, int F, int K, int R, long long ldw, long long ldx, long long ldo,
                      long long ldr, long long ldw2, long long ldx2, int dual, int up_off, int splits, int bn,
-                     int* status, cudaStream_t stream, const GemmTpArgs& tp, const TahbQkvEpilogue* qkv = nullptr) {
+                     int* status, cudaStream_t stream, const GemmTpArgs& tp, const TahbQkvEpilogue* qkv = nullptr,
+                     int a_mn = 0, int b_mn = 0, int k_rows = 0) {
   if (M <= 0 || F <= 0) return 0;
+  // transposed operands: W is then [K, F] (ldw = its row pitch), X is [K, M]; no LoRA extension, no dual
+  if ((a_mn || b_mn) && (dual == 1 || dual == 2 || R > 0 || qkv != nullptr || tp.push_world > 0)) return -27;
+  if (a_mn && F % 128) return -27;
   const bool push = tp.push_world > 0;
   if (qkv != nullptr && (dual != 0 || residual != nullptr || push || F != (qkv->nq + 2 * qkv->nkv) * 128 ||
                          qkv->n_caches > 4 || qkv->q_out == nullptr || qkv->pos == nullptr))
     return -26;
   // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 2 = pair: two plain
-  // output tiles per CTA (features f and F/2 + f) sharing the activation tile
+  // output tiles per CTA (features f and F/2 + f) sharing the activation tile, 3 = one accumulator + GELU
   const bool pair = dual == 2;
+  const int act = dual == 3 ? 1 : 0;          // dual == 3: one accumulator with a GELU epilogue
+  if (dual == 3) dual = 0;
   const int F_full = F;
   if (pair) {
     if (F % 256) return -24;
@@ -691,14 +767,17 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
     return -23;
   if (K % 64 || R % 64 || K <= 0) return -20;
   if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (b_mn && bn < 64) bn = 64;               // MN-major column tiles come in 64-wide boxes
   if (splits < 1) splits = 1;
   const int kb = K / 64 + R / 64;
   while (splits > 1 && (splits > kb || bn % splits || (bn / splits) % 16)) splits >>= 1;
   const long long w_rows = dual ? (long long)up_off + F : F;
   CUtensorMap mw, mx, mw2, mx2;
   int rc;
-  if ((rc = make_map(&mw, W, w_rows, K, ldw, 128, true))) return rc;
-  if ((rc = make_map(&mx, X, M, K, ldx, bn, true))) return rc;
+  // k_rows: true reduction length of MN-major operands (K is rounded up to whole k-blocks; TMA zero-fills the rest)
+  const long long kr = k_rows > 0 ? k_rows : K;
+  if ((rc = a_mn ? make_map_mn(&mw, W, kr, F, ldw) : make_map(&mw, W, w_rows, K, ldw, 128, true))) return rc;
+  if ((rc = b_mn ? make_map_mn(&mx, X, kr, M, ldx) : make_map(&mx, X, M, K, ldx, bn, true))) return rc;
   if (R > 0) {
     if ((rc = make_map(&mw2, W2, w_rows, R, ldw2, 128, true))) return rc;
     if ((rc = make_map(&mx2, X2, M, R, ldx2, bn, true))) return rc;
@@ -738,6 +817,9 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
     p.rope_cs = nullptr;
   }
   p.pair = pair ? 1 : 0;
+  p.act = act;
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
   p.push_ld = F_full;
   p.push_world = tp.push_world;
   p.push_rank = tp.push_rank;
@@ -811,4 +893,17 @@ extern "C" int tahb_gemm_qkv(const void* W, const void* X, const void* W2, const
   if (qkv == nullptr) return -26;
   return gemm_impl(W, X, nullptr, nullptr, W2, X2, M, F, K, R, ldw, ldx, 0, 0, ldw2, ldx2, 0, 0, splits, bn, status,
                    stream, tp, qkv);
+}
+
+// out[M, F] (+= residual) = op(X) op(W)^T with transposed operands, for the backward GEMMs:
+//   a_mn: W is stored [K, F] row-major (row pitch ldw) instead of [F, K];
+//   b_mn: X is stored [K, M] row-major (row pitch ldx) instead of [M, K].
+// K (the reduction length) may be any multiple of 8; rows past it read as zeros.  F % 128 == 0 with a_mn.
+extern "C" int tahb_gemm_t(const void* W, const void* X, void* out, const void* residual, int M, int F, int K,
+                           long long ldw, long long ldx, long long ldo, long long ldr, int a_mn, int b_mn, int splits,
+                           int bn, int* status, cudaStream_t stream) {
+  const int Kp = (K + 63) / 64 * 64;          // the tail k-block of MN-major operands is zero-filled by TMA
+  if (Kp != K && !(a_mn && b_mn)) return -20; // a K-major operand needs whole k-blocks
+  return gemm_impl(W, X, out, residual, nullptr, nullptr, M, F, Kp, 0, ldw, ldx, ldo, ldr, 0, 0, 0, 0, splits, bn,
+                   status, stream, GemmTpArgs(), nullptr, a_mn, b_mn, K);
 }

@@ -37,6 +37,7 @@ struct ZeroParams {
   long long lo, hi;                           // this rank's element range (multiples of 8)
   int rank, world;
   float grad_scale, lr, beta1, beta2, eps, weight_decay, bc1, bc2, max_norm;
+  long long nodecay_from;                     // flat elements at or beyond this index get no weight decay
   int accumulate;                             // reduce phase: gshard += (instead of =) and no norm (several
                                               // reduce-scatters - passes, micro-batches - feed one update)
 };
@@ -202,7 +203,8 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(const ZeroParams 
       m[j] = p.beta1 * m[j] + (1.f - p.beta1) * gj;
       v[j] = p.beta2 * v[j] + (1.f - p.beta2) * gj * gj;
       const float upd = (m[j] / p.bc1) / (sqrtf(v[j] / p.bc2) + p.eps);
-      w[j] = w[j] * (1.f - p.lr * p.weight_decay) - p.lr * upd;
+      const float wd = (p.lo + i * 8 + j >= p.nodecay_from) ? 0.f : p.weight_decay;
+      w[j] = w[j] * (1.f - p.lr * wd) - p.lr * upd;
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(w[2 * j], w[2 * j + 1]);
@@ -245,6 +247,11 @@ static void fill(ZeroParams& p, void* const* grad, void* const* param, void* mc_
   p.lo = lo; p.hi = hi; p.rank = rank; p.world = world;
 }
 
+// Flat index from which the NEXT tahb_zero_step launch applies no weight decay (norm gains, biases and the like
+// are laid out behind the decayed parameters); reset after that launch.
+static long long g_nodecay_from = 0x7fffffffffffffffLL;
+extern "C" void tahb_zero_set_nodecay_from(long long index) { g_nodecay_from = index; }
+
 // phase 0: reduce-scatter of the gradient shard [lo, hi) + scaling + squared norm (atomicAdd into *norm_sq,
 // which the caller zeroes before the launch and all-reduces afterwards).  phase 1: AdamW + parameter broadcast.
 // phase 2: as phase 0 but the scaled sum is ADDED to gshard and no norm is taken (parameter-sharded training
@@ -260,6 +267,8 @@ extern "C" int tahb_zero_step(int phase, void* const* grad, void* const* param, 
   p.grad_scale = grad_scale; p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps;
   p.weight_decay = weight_decay; p.bc1 = bc1; p.bc2 = bc2; p.max_norm = max_norm;
   p.accumulate = phase == 2 ? 1 : 0;
+  p.nodecay_from = g_nodecay_from;
+  g_nodecay_from = 0x7fffffffffffffffLL;      // one-shot: applies to this launch only
   if (grid < 1) grid = 1;
   if (phase == 0 || phase == 2) zero_reduce_norm_kernel<<<grid, 256, 0, stream>>>(p);
   else zero_adamw_bcast_kernel<<<grid, 256, 0, stream>>>(p);

@@ -100,10 +100,79 @@ class TaHEngine:
         """Decider logits ``z`` (fp32 ``[n]``) from tapped hidden states / sorted top-k values."""
         _, inner = self._decider()
         if isinstance(inner, MLPIterDecider):
-            return inner.score(taps, topk_vals.to(taps.dtype)).float()
+            return self._score_mlp(inner, taps, topk_vals)
         if isinstance(inner, SimpleMLPIterDecider):
             return self._score_simple_mlp(inner, taps)
         return None
+
+    def _mlp_decider_plan(self, dec: MLPIterDecider, device):
+        """Kernel-ready weights of the learned decider (reference ``tah/model/iter_decider.py:194-301``), or None
+        when a shape or option is outside what the kernel chain covers (then the module runs)."""
+        plan = getattr(self, "_mlp_plan", None)
+        if plan is not None and plan["dec"] is dec:
+            return plan["w"]
+        H, k = dec.hidden_states_size, dec.topk
+        lin = [dec.logits_projection, dec.combined_projection, dec.backbone.input_projection, dec.backbone.output_layer[1]]
+        ok = (not dec.normalize_input and k <= 128 and H % 64 == 0 and all(m.weight.dtype == torch.bfloat16 for m in lin)
+              and all(isinstance(b.dim_change, torch.nn.Identity) for b in dec.backbone.blocks)
+              and all(m.weight.shape[1] % 64 == 0 and m.weight.shape[0] % 8 == 0 for m in lin[1:3])
+              and dec.backbone.output_layer[1].weight.shape[0] == 1
+              and all(b.mlp[0].weight.shape[0] % 64 == 0 and b.mlp[0].weight.shape[1] % 64 == 0 for b in dec.backbone.blocks))
+        w = None
+        if ok:
+            bf = lambda t: t.detach().to(device=device, dtype=torch.bfloat16).contiguous()
+
+            def bias_ext(m):              # the bias enters the fp32 accumulation as a K-extension: ones column x bias
+                e = torch.zeros(m.weight.shape[0], 64, dtype=torch.bfloat16, device=device)
+                if m.bias is not None:
+                    e[:, 0] = m.bias.detach()
+                return e
+
+            lp = torch.zeros(H, 128, dtype=torch.bfloat16, device=device)
+            lp[:, :k] = dec.logits_projection.weight.detach()
+            ones = torch.zeros(max(self.max_rows, 4096), 64, dtype=torch.bfloat16, device=device)
+            ones[:, 0] = 1
+            out_ln, out_lin = dec.backbone.output_layer[0], dec.backbone.output_layer[1]
+            w = dict(k=k, H=H, ones=ones, lp=lp, lp_b=bias_ext(dec.logits_projection),
+                     cp=bf(dec.combined_projection.weight), cp_b=bias_ext(dec.combined_projection),
+                     ip=bf(dec.backbone.input_projection.weight), ip_b=bias_ext(dec.backbone.input_projection),
+                     blocks=[dict(ln_w=bf(b.layer_norm.weight), ln_b=bf(b.layer_norm.bias), eps=b.layer_norm.eps,
+                                  w1=bf(b.mlp[0].weight), b1=bias_ext(b.mlp[0]), w2=bf(b.mlp[3].weight), b2=bias_ext(b.mlp[3]))
+                             for b in dec.backbone.blocks],
+                     oln_w=bf(out_ln.weight), oln_b=bf(out_ln.bias), oeps=out_ln.eps,
+                     ow=bf(out_lin.weight[0]), ob=bf(out_lin.bias) if out_lin.bias is not None else None)
+        self._mlp_plan = {"dec": dec, "w": w}
+        return w
+
+    def _score_mlp(self, dec: MLPIterDecider, taps: torch.Tensor, topk_vals: torch.Tensor) -> torch.Tensor:
+        """The learned decider as a kernel chain: ``Linear(topk -> H)`` on the sorted top-k values written next to
+        the tapped hidden states, the combined and input projections, the residual blocks ``x + W2 gelu(W1 LN(x))``
+        (LayerNorm kernel; tcgen05 GEMMs with the bias as a K-extension, GELU / residual epilogues) and the output
+        layer ``LayerNorm -> Linear(d, 1)`` as one reduction kernel.  ``taps``: ``[M, n_taps*H]`` or, with room for
+        the projection, ``[M, (n_taps+1)*H]``."""
+        w = self._mlp_decider_plan(dec, taps.device) if taps.is_cuda and taps.dtype == torch.bfloat16 else None
+        n_taps = max(1, len(dec.hidden_states_layer_nums))
+        if w is None or taps.shape[0] > w["ones"].shape[0]:
+            hid = taps[:, :n_taps * dec.hidden_states_size]
+            return dec.score(hid, topk_vals[:, :dec.topk].to(hid.dtype)).float()
+        M, H, k = taps.shape[0], w["H"], w["k"]
+        feats = taps
+        if taps.shape[1] == n_taps * H:
+            feats = torch.empty(M, (n_taps + 1) * H, dtype=torch.bfloat16, device=taps.device)
+            feats[:, :n_taps * H].copy_(taps)
+        tv = getattr(self, "_mlp_tv", None)
+        if tv is None or tv.shape[0] < M:
+            tv = self._mlp_tv = torch.zeros(max(M, self.max_rows), 128, dtype=torch.bfloat16, device=taps.device)
+        tv[:M, :k].copy_(topk_vals[:, :k])
+        ones = w["ones"][:M]
+        K.gemm(tv[:M], w["lp"], x2=ones, w2=w["lp_b"], out=feats[:, n_taps * H:])
+        x = K.gemm(feats, w["cp"], x2=ones, w2=w["cp_b"])
+        x = K.gemm(x, w["ip"], x2=ones, w2=w["ip_b"])
+        for b in w["blocks"]:
+            n = K.layer_norm(x, b["ln_w"], b["ln_b"], b["eps"])
+            u = K.gemm(n, b["w1"], x2=ones, w2=b["b1"], gelu=True)
+            x = K.gemm(u, b["w2"], x2=ones, w2=b["b2"], residual=x, out=x)
+        return K.layer_norm_dot(x, w["oln_w"], w["oln_b"], w["ow"], w["ob"], w["oeps"])
 
     def _score_simple_mlp(self, dec: SimpleMLPIterDecider, taps: torch.Tensor) -> torch.Tensor:
         """The two-layer decider as kernels: tcgen05 GEMM for the first layer (its bias enters the fp32
@@ -207,19 +276,31 @@ class TaHEngine:
     # prefill
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()
-    def prefill(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor], max_new_tokens: int):
+    def prefill(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor], max_new_tokens: int,
+                row_ids: Optional[torch.Tensor] = None):
+        """Prefill a batch of prompts.  ``row_ids`` (optional ``[B]``): admit these prompts into those rows of the
+        existing cache (their pages must have been released with ``kv.free_rows``) while the other rows keep their
+        state; without it the cache is (re)built for exactly this batch."""
         cfg, w, dev = self.cfg, self.w, self.device
         B, T = input_ids.shape
         valid = attention_mask[:, -T:].bool() if attention_mask is not None else torch.ones(B, T, dtype=torch.bool, device=dev)
         lens = valid.sum(1)
         max_total = int(lens.max()) + max_new_tokens + 1
-        if self.kv is None or self.kv.rows != B or self.kv.max_pages[0] * self.page_size < max_total:
+        if row_ids is not None:
+            if self.kv is None or self.kv.max_pages[0] * self.page_size < max_total:
+                raise RuntimeError("admission needs an existing KV cache whose rows can hold prompt + new tokens")
+            row_ids = row_ids.to(dev)
+        elif self.kv is None or self.kv.rows != B or self.kv.max_pages[0] * self.page_size < max_total:
             geo = CacheGeometry(cfg.num_hidden_layers, w.nkv, cfg.head_dim, self.page_size)
             self.kv = None
             torch.cuda.empty_cache()
             self.kv = PagedKVCache(geo, B, max(max_total, 1), self.max_iter, self.deep_fraction, dev)
             self._states.clear()          # captured ticks point into the old pools
-        self.kv.reset()
+        if row_ids is None:
+            self.kv.reset()
+        assign = (lambda d, c: self.kv.assign_prefill(d, c)) if row_ids is None else \
+                 (lambda d, c: self.kv.assign_rows(d, row_ids, c))
+        self._prefill_rows = row_ids
         if self.tp is not None:
             self.tp.allocate(cfg.hidden_size, max(int(valid.sum()), B))
         rows_idx, cols_idx = valid.nonzero(as_tuple=True)
@@ -230,7 +311,7 @@ class TaHEngine:
         seq = rows_idx.to(torch.int32)
 
         # ---- pass 0 -------------------------------------------------------------------------
-        slots0 = self.kv.assign_prefill(0, lens)
+        slots0 = assign(0, lens)
         x = K.embed_gather(w.embed, ids)
         taps = {}
         base0 = seq_start[rows_idx].contiguous()
@@ -264,7 +345,7 @@ class TaHEngine:
             n1 = cur_idx.numel()
             rows1 = seq[cur_idx].long()
             cnt1 = torch.bincount(rows1, minlength=B)
-            slots1 = self.kv.assign_prefill(depth, cnt1)
+            slots1 = assign(depth, cnt1)
             val = torch.zeros(n1, self.topk, dtype=torch.float32, device=dev)
             idx = torch.zeros(n1, self.topk, dtype=torch.int32, device=dev)
             self._topk(cur_cum, self.topk, None, val, idx)
@@ -276,11 +357,26 @@ class TaHEngine:
             counts = [c[cur_idx].contiguous() for c in prev_counts] + [(rank1 + 1).contiguous()]
             # shallower segments (1..depth-1) index into the packed arrays of those passes: their
             # (base, count) were computed against those arrays when the passes ran
+            learned = self.hard_override is None and isinstance(self._decider()[1], (MLPIterDecider, SimpleMLPIterDecider))
+            taps1 = {} if learned and depth + 1 < self.max_iter else None
             with nvtx_range(f"prefill/pass{depth}"):
-                hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts, cnt1)
+                hn1, kv1 = self._packed_pass(x1, pos1, depth, slots1, seg_k, seg_v, bases, counts, cnt1, taps_out=taps1)
             logits1 = self._lm_head(hn1)
             cum1 = cur_cum + logits1
-            want_more = (extra[cur_idx] > depth) & (depth + 1 < self.max_iter)
+            if taps1 is not None:
+                # a learned decider is asked again after every pass, on this pass's hidden states and the cumulative
+                # logits, as the model's forward and the decode tick do (reference tah_model.py:625-645)
+                inner = self._decider()[1]
+                tl = self._tap_layers()
+                tcat = torch.cat([taps1[i] for i in tl], dim=-1) if tl else None
+                tv = None
+                if isinstance(inner, MLPIterDecider):
+                    tv = torch.zeros(n1, inner.topk, dtype=torch.float32, device=dev)
+                    self._topk(cum1, inner.topk, None, tv, torch.zeros(n1, inner.topk, dtype=torch.int32, device=dev))
+                z1 = self._score(tcat, tv)
+                want_more = torch.sigmoid(z1) > self._thr
+            else:
+                want_more = (extra[cur_idx] > depth) & (depth + 1 < self.max_iter)
             fin = ~want_more
             lastfin = fin & is_last[cur_idx]
             final_last_logits[rows1[lastfin]] = cum1[lastfin]
@@ -323,7 +419,8 @@ class TaHEngine:
                 zs.append(self._score(tcat, tv))
             z = torch.cat(zs)
         if self.hard_override is not None:
-            return self.hard_override[seq.long(), pos.long()].to(torch.int32)
+            rows = seq.long() if getattr(self, "_prefill_rows", None) is None else self._prefill_rows[seq.long()]
+            return self.hard_override[rows, pos.long()].to(torch.int32)
         if isinstance(decider, BernoulliIterDecider):
             raise RuntimeError("BernoulliIterDecider needs engine.hard_override (see make_bernoulli_override)")
         if z is None:
@@ -376,7 +473,8 @@ class TaHEngine:
         s.topv = torch.zeros(B, self.topk, dtype=torch.float32, device=dev)
         s.topi = i32(B, self.topk)
         tl = self._tap_layers()
-        s.taps = bf(B, max(1, len(tl)) * H)
+        # the learned decider's Linear(topk -> H) output is written behind the tapped hidden states
+        s.taps = bf(B, (max(1, len(tl)) + (1 if self._needs_topk_for_decider() else 0)) * H)
         s.z = torch.zeros(B, dtype=torch.float32, device=dev)
         kv = self.kv
         pad = lambda lst: list(lst) + [lst[0]] * (4 - len(lst))
@@ -527,6 +625,18 @@ class TaHEngine:
     # ------------------------------------------------------------------------------------------
     # generate
     # ------------------------------------------------------------------------------------------
+    BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024)
+
+    def bucket_rows(self, n: int) -> int:
+        """Row count of the batch bucket that serves ``n`` requests (the engine keeps one set of tick buffers and
+        one captured graph per bucket); exact under tensor parallelism or when bucketing is switched off."""
+        if self.tp is not None or os.environ.get("TAH_B200_NO_BUCKETS", "0") == "1" or self.hard_override is not None:
+            return n
+        for b in self.BUCKETS:
+            if b >= n:
+                return b
+        return n
+
     def _tick_state(self, B: int, max_new: int, sampling: Optional[dict], eos_token_id: Optional[int]):
         """Tick buffers + captured graph for this (rows, max_new, sampling, eos, hard mask) shape.  A repeat call
         with the same shape clears the scheduler state and replays the graph captured by the first one."""
@@ -563,7 +673,15 @@ class TaHEngine:
         input_ids = input_ids.to(dev)
         if attention_mask is not None:
             attention_mask = attention_mask.to(dev)
-        B = input_ids.shape[0]
+        B_user = input_ids.shape[0]
+        B = self.bucket_rows(B_user)
+        if B != B_user:
+            # batch bucket: pad with copies of the first prompt (their output is dropped), so that batch sizes of one
+            # bucket share tick buffers and the captured graph
+            pad = B - B_user
+            input_ids = torch.cat([input_ids, input_ids[:1].expand(pad, -1)], 0)
+            if attention_mask is not None:
+                attention_mask = torch.cat([attention_mask, attention_mask[:1].expand(pad, -1)], 0)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         ev[0].record()
         with nvtx_range("engine/prefill"):
@@ -616,7 +734,7 @@ class TaHEngine:
                 if on_tick is not None:
                     on_tick(ticks, s)
                 if ticks % sync_every == 0 or ticks == limit:
-                    done = bool(((s.finished != 0) | (s.n_out >= max_new_tokens)).all())
+                    done = bool(((s.finished != 0) | (s.n_out >= max_new_tokens))[:B_user].all())
                     if done:
                         break
         ev[2].record()
@@ -625,8 +743,10 @@ class TaHEngine:
         n_out = s.n_out.tolist()
         out = s.out_tokens.tolist()
         iters = (s.iter_sum.float() / s.n_out.clamp(min=1).float()).tolist()
+        out, n_out, iters = out[:B_user], n_out[:B_user], iters[:B_user]
         res = GenerationResult(tokens=[row[:n] for row, n in zip(out, n_out)], iter_counts=iters, ticks=ticks,
-                               tokens_emitted=int(s.tokens_done.item()), prefill_ms=ev[0].elapsed_time(ev[1]),
+                               tokens_emitted=int(s.tokens_done.item()) if B == B_user else int(sum(n_out)),
+                               prefill_ms=ev[0].elapsed_time(ev[1]),
                                decode_ms=ev[1].elapsed_time(ev[2]),
                                extra={"graph_captures": self.graph_captures, "graph_reuses": self.graph_reuses})
         self.last_counters = dict(engine_counters(self, res), graph_captures=self.graph_captures,
@@ -634,6 +754,124 @@ class TaHEngine:
         if self.metrics is not None:
             self.metrics.log(self.last_counters, step=self._calls)
         return res
+
+    # ------------------------------------------------------------------------------------------
+    # serving: request admission into free rows, pages returned on completion
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def serve(self, prompts: Sequence[torch.Tensor], *, max_new_tokens: int = 128, rows: Optional[int] = None,
+              eos_token_id: Optional[int] = None, do_sample: bool = False, temperature: float = 1.0, top_p: float = 1.0,
+              top_k: int = 0, min_p: float = 0.0, seed: Optional[int] = None, check_every: int = 16):
+        """Continuous batching over a queue of requests (1-D token id tensors of any lengths).
+
+        ``rows`` batch rows decode in lock step (one captured tick graph for that row count).  Every
+        ``check_every`` ticks the host looks at the rows: a row whose request finished (EOS or ``max_new_tokens``)
+        hands back its tokens, its KV pages of every depth return to the device free stacks, and the next queued
+        request is admitted into the row - its prompt is prefilled into freshly assigned pages while the other rows
+        keep their state - so the batch stays full while requests of different lengths come and go.  Returns the
+        generated token lists in request order and a statistics dict (ticks, admissions, peak pages in use)."""
+        dev = self.device
+        if self.tp is not None:
+            raise NotImplementedError("serve() runs on one GPU; use generate() under tensor parallelism")
+        n_req = len(prompts)
+        B = min(rows or self.max_rows, n_req, self.max_rows)
+        longest = max(int(p.numel()) for p in prompts)
+        sampling = None
+        if do_sample:
+            sampling = dict(temperature=float(temperature), top_p=float(top_p), min_p=float(min_p), top_k=int(top_k))
+            if seed is None:
+                seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+
+        def pad_batch(ps):
+            T = max(int(p.numel()) for p in ps)
+            ids = torch.zeros(len(ps), T, dtype=torch.long, device=dev)
+            mask = torch.zeros(len(ps), T, dtype=torch.long, device=dev)
+            for i, p in enumerate(ps):
+                ids[i, T - p.numel():] = p.to(dev)
+                mask[i, T - p.numel():] = 1
+            return ids, mask
+
+        def first_tokens(logits, lens):
+            if sampling is None:
+                return self._argmax(logits)
+            k = sampling["top_k"]
+            if 0 < k <= 128:
+                val = torch.zeros(logits.shape[0], k, dtype=torch.float32, device=dev)
+                idx = torch.zeros(logits.shape[0], k, dtype=torch.int32, device=dev)
+                self._topk(logits, k, None, val, idx)
+                return K.sample_topk(val, idx, temperature, top_p, min_p, int(seed), step=lens.to(torch.int32) - 1)
+            return K.sample_full(logits.contiguous(), temperature, k, top_p, min_p, int(seed), step=lens.to(torch.int32) - 1)
+
+        # the cache is sized for the longest request in every row
+        ids, mask = pad_batch(prompts[:B])
+        if self.kv is not None and (self.kv.rows != B or self.kv.max_pages[0] * self.page_size < longest + max_new_tokens + 1):
+            self.kv = None
+        if self.kv is None:
+            geo = CacheGeometry(self.cfg.num_hidden_layers, self.w.nkv, self.cfg.head_dim, self.page_size)
+            torch.cuda.empty_cache()
+            self.kv = PagedKVCache(geo, B, longest + max_new_tokens + 1, self.max_iter, self.deep_fraction, dev)
+            self._states.clear()
+        logits, lens, _ = self.prefill(ids, mask, max_new_tokens)
+        self._calls += 1
+        s = self._tick_state(B, max_new_tokens, sampling, eos_token_id)
+        if sampling is not None:
+            s.seed_dev.fill_(int(seed) & (2 ** 62 - 1))
+        s.pos.copy_(lens.to(torch.int32) - 1)
+        s.need_soft.zero_()
+        s.binding.tick_end(s.need_soft, first_tokens(logits, lens))
+        s.cur_iters.zero_()
+        owner = list(range(B))                       # request index held by each row (-1 = idle)
+        next_req = B
+        results: List[Optional[List[int]]] = [None] * n_req
+        stats = {"ticks": 0, "admitted": B, "rows": B, "peak_pages": [0] * self.kv.n_depths, "pages_released": 0}
+        if self.use_cuda_graph and s.graph is None:
+            self._tick(s, sampling)                  # lazy one-time kernel setup outside capture
+            stats["ticks"] += 1
+        run = self._tick_runner(s, sampling)
+        budget = (n_req // B + 2) * (max_new_tokens * self.max_iter + check_every + 1)
+        while any(o >= 0 for o in owner) and stats["ticks"] < budget:
+            for _ in range(check_every):
+                run()
+            stats["ticks"] += check_every
+            done = ((s.finished != 0) | (s.n_out >= max_new_tokens)).tolist()
+            for d in range(self.kv.n_depths):
+                stats["peak_pages"][d] = max(stats["peak_pages"][d], self.kv.pages_in_use(d))
+            fin = [r for r in range(B) if done[r] and owner[r] >= 0]
+            if not fin:
+                continue
+            n_out = s.n_out.tolist()
+            toks = s.out_tokens[fin].tolist()
+            for r, row_toks in zip(fin, toks):
+                results[owner[r]] = row_toks[:n_out[r]]
+                owner[r] = -1
+            rows_t = torch.tensor(fin, device=dev)
+            stats["pages_released"] += self.kv.free_rows(rows_t)
+            take = min(len(fin), n_req - next_req)
+            if take:
+                rows_new = rows_t[:take]
+                ids, mask = pad_batch(prompts[next_req:next_req + take])
+                logits, lens, _ = self.prefill(ids, mask, max_new_tokens, row_ids=rows_new)
+                first = first_tokens(logits, lens).to(torch.int32)
+                # what tick_end does for a row that emits its first token
+                hit_eos = (first == eos_token_id) if eos_token_id is not None else torch.zeros_like(first, dtype=torch.bool)
+                s.out_tokens[rows_new] = 0
+                s.out_tokens[rows_new, 0] = torch.where(hit_eos, torch.zeros_like(first), first)
+                s.n_out[rows_new] = (~hit_eos).to(torch.int32)
+                s.finished[rows_new] = hit_eos.to(torch.int32)
+                s.tokens_done += int((~hit_eos).sum())
+                s.tok[rows_new], s.depth[rows_new] = first, 0
+                s.pos[rows_new] = lens.to(torch.int32)
+                s.cur_iters[rows_new], s.iter_sum[rows_new], s.need_soft[rows_new] = 0, 0, 0
+                for j in range(take):
+                    owner[fin[j]] = next_req + j
+                next_req += take
+                stats["admitted"] += take
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        if any(r is None for r in results):
+            raise RuntimeError("serve(): tick budget exhausted before every request finished")
+        stats["tokens"] = sum(len(r) for r in results)
+        return results, stats
 
     def _tick_runner(self, s, sampling):
         if not self.use_cuda_graph:

@@ -89,3 +89,55 @@ class PagedKVCache:
         j = torch.arange(int(counts.sum()), device=dev) - start[row_of_entry]
         pg = self.page_table[depth][row_of_entry, (j // ps)].long()
         return (pg * ps + j % ps).to(torch.int32)
+
+    def assign_rows(self, depth: int, rows: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+        """Like :meth:`assign_prefill` for a subset of rows (request admission while other rows keep decoding):
+        ``rows [n]`` get ``counts [n]`` entries each; the other rows' lengths and pages are untouched.  The rows
+        must be empty at this depth (see :meth:`free_rows`).  Returns the slots of the entries, row-major."""
+        ps = self.page_size
+        dev = self.len[depth].device
+        rows = rows.to(device=dev, dtype=torch.int64)
+        counts = counts.to(device=dev, dtype=torch.int64)
+        need = (counts + ps - 1) // ps
+        total = int(need.sum())
+        free = int(self.free_count[depth])
+        if total > free or int(need.max() if need.numel() else 0) > self.max_pages[depth]:
+            raise RuntimeError(f"KV pool of depth {depth} too small: need {total} pages, {free} free")
+        first = torch.cumsum(need, 0) - need
+        which = torch.repeat_interleave(torch.arange(rows.numel(), device=dev), need)
+        rank = torch.arange(total, device=dev)
+        page_ids = self.free_stack[depth][(free - 1 - rank).long()]
+        col = rank - first[which]
+        self.page_table[depth][rows[which], col] = page_ids
+        self.free_count[depth].fill_(free - total)
+        self.len[depth][rows] = counts.to(torch.int32)
+        which_e = torch.repeat_interleave(torch.arange(rows.numel(), device=dev), counts)
+        start = torch.cumsum(counts, 0) - counts
+        j = torch.arange(int(counts.sum()), device=dev) - start[which_e]
+        pg = self.page_table[depth][rows[which_e], (j // ps)].long()
+        return (pg * ps + j % ps).to(torch.int32)
+
+    def free_rows(self, rows: torch.Tensor) -> int:
+        """Return every page of ``rows`` (all depths) to the free stacks and clear their lengths.  Call between
+        ticks.  Returns the number of pages released."""
+        ps = self.page_size
+        released = 0
+        for d in range(self.n_depths):
+            dev = self.len[d].device
+            r = rows.to(device=dev, dtype=torch.int64)
+            n = (self.len[d][r].to(torch.int64) + ps - 1) // ps
+            total = int(n.sum())
+            if total:
+                which = torch.repeat_interleave(r, n)
+                first = torch.cumsum(n, 0) - n
+                col = torch.arange(total, device=dev) - torch.repeat_interleave(first, n)
+                pages = self.page_table[d][which, col]
+                free = int(self.free_count[d])
+                self.free_stack[d][free:free + total] = pages
+                self.free_count[d].fill_(free + total)
+                released += total
+            self.len[d][r] = 0
+        return released
+
+    def pages_in_use(self, depth: int) -> int:
+        return self.n_pages[depth] - int(self.free_count[depth])

@@ -20,6 +20,7 @@ means are taken over the same sets as in the reference.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -55,9 +56,18 @@ class NextTokenPredLoss(LossFunc):
         super().__init__()
 
     def final_loss_func(self, logits, labels_shifted, iter_count=None, training=True, **kwargs):
-        flat = logits.reshape(-1, logits.shape[-1]).float()
-        return fixed_cross_entropy(flat, labels_shifted.reshape(-1).to(flat.device),
-                                   num_items_in_batch=kwargs.get("num_items_in_batch"))
+        flat = logits.reshape(-1, logits.shape[-1])
+        labels = labels_shifted.reshape(-1).to(flat.device)
+        n_items = kwargs.get("num_items_in_batch")
+        if flat.is_cuda and flat.dtype == torch.bfloat16:
+            from tah_b200.ops import autograd_ops
+            if autograd_ops.cross_entropy_sum_ok(flat):
+                # one kernel over the bf16 logits (fp32 math): no fp32 copy of the [B*T, V] tensor
+                total = autograd_ops.cross_entropy_sum(flat, labels)
+                if n_items is None:
+                    return total / (labels != -100).sum().clamp(min=1)
+                return total / n_items
+        return fixed_cross_entropy(flat.float(), labels, num_items_in_batch=n_items)
 
 
 class IterDeciderLoss(LossFunc):
@@ -92,18 +102,30 @@ class IterDeciderLoss(LossFunc):
         w = has_label.float()
         n = w.sum()
         z = continue_logits.float()
-        target = (labels > iter_depth).float()
-        pw = None if self.pos_weight is None else torch.tensor(self.pos_weight, device=z.device)
-        per = F.binary_cross_entropy_with_logits(z, target, pos_weight=pw, reduction="none")
-        denom = n.clamp(min=1.0)
-        mean_bce = (per * w).sum() / denom                    # BCE averaged over contributing tokens
         thr = iter_decider_threshold
-        if isinstance(thr, torch.Tensor):
-            thr = thr.detach().float()
-        with torch.no_grad():
-            pred = (torch.sigmoid(z) > thr).float()
-            self._correct += ((pred == target).float() * w).sum()
-            self._total += n
+        if z.is_cuda and os.environ.get("TAH_B200_FORCE_TORCH", "0") != "1":
+            # BCE terms, labelled count and accuracy counter in one kernel (and one for the backward)
+            from tah_b200.ops import autograd_ops
+            thr_f = float(thr.detach().float()) if isinstance(thr, torch.Tensor) else float(thr)
+            bsum, n, correct = autograd_ops.bce_sum(z, labels, int(iter_depth), 1.0 if self.pos_weight is None
+                                                    else float(self.pos_weight), thr_f)
+            denom = n.clamp(min=1.0)
+            mean_bce = bsum / denom
+            with torch.no_grad():
+                self._correct += correct
+                self._total += n
+        else:
+            target = (labels > iter_depth).float()
+            pw = None if self.pos_weight is None else torch.tensor(self.pos_weight, device=z.device)
+            per = F.binary_cross_entropy_with_logits(z, target, pos_weight=pw, reduction="none")
+            denom = n.clamp(min=1.0)
+            mean_bce = (per * w).sum() / denom                # BCE averaged over contributing tokens
+            if isinstance(thr, torch.Tensor):
+                thr = thr.detach().float()
+            with torch.no_grad():
+                pred = (torch.sigmoid(z) > thr).float()
+                self._correct += ((pred == target).float() * w).sum()
+                self._total += n
         # every contributing token receives mean_bce / n, so that the final
         # sum over tokens reproduces the per-pass mean
         share = (mean_bce / denom) * w

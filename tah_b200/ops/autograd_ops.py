@@ -6,6 +6,7 @@ of 64); the backward passes are written out explicitly here.  Inputs the kernels
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -18,6 +19,35 @@ from tah_b200.ops import torch_ref
 def _gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 64 == 0
             and w.shape[0] % 8 == 0 and x.numel() > 0)
+
+
+def _own_bwd() -> bool:
+    return os.environ.get("TAH_B200_BWD_GEMM", "tcgen05") != "cublas"
+
+
+def _dgrad(g2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``g2 [T, F] @ w [F, K] -> [T, K]`` (data gradient of ``y = x w^T``) on the tcgen05 GEMM: ``w`` is read
+    transposed from its row-major storage (MN-major operand), no transposed copy is made."""
+    if (_own_bwd() and g2.is_cuda and g2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 128 == 0
+            and g2.shape[1] % 64 == 0 and g2.numel() > 0):
+        return K.gemm_t(g2 if g2.is_contiguous() else g2.contiguous(), w if w.is_contiguous() else w.contiguous(), w_t=True)
+    return g2 @ w
+
+
+def _wgrad(g2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+    """``g2^T [F, T] @ x2 [T, K] -> [F, K]`` (weight gradient): both operands are read transposed from their
+    token-major storage, the reduction runs over the tokens.  When ``K`` cannot sit on the 128 tensor-memory lanes
+    but ``F`` can, the transposed product is computed and returned as a view."""
+    ok = (_own_bwd() and g2.is_cuda and g2.dtype == torch.bfloat16 and x2.dtype == torch.bfloat16 and g2.numel() > 0
+          and g2.shape[1] % 8 == 0 and x2.shape[1] % 8 == 0)
+    if ok:
+        g2 = g2 if g2.is_contiguous() else g2.contiguous()
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        if x2.shape[1] % 128 == 0:
+            return K.gemm_t(g2, x2, x_t=True, w_t=True)
+        if g2.shape[1] % 128 == 0:
+            return K.gemm_t(x2, g2, x_t=True, w_t=True).t()
+    return g2.t() @ x2
 
 
 class _Linear(torch.autograd.Function):
@@ -36,9 +66,9 @@ class _Linear(torch.autograd.Function):
         gx = gw = None
         g2 = gy.reshape(-1, gy.shape[-1])
         if ctx.needs_input_grad[0]:
-            gx = (g2 @ w).view_as(x)
+            gx = _dgrad(g2, w).view_as(x)
         if ctx.needs_input_grad[1]:
-            gw = g2.t() @ x.reshape(-1, x.shape[-1])
+            gw = _wgrad(g2, x.reshape(-1, x.shape[-1]))
         return gx, gw
 
 
@@ -66,10 +96,16 @@ class _LoRALinear(torch.autograd.Function):
         x2, w, t2, bd = ctx.saved_tensors
         xs, ts = ctx.shapes
         g2 = gy.reshape(-1, gy.shape[-1])
-        gx = (g2 @ w).view(xs) if ctx.needs_input_grad[0] else None
-        gw = g2.t() @ x2 if ctx.needs_input_grad[1] else None
-        gt = (g2 @ bd).view(ts) if ctx.needs_input_grad[2] else None
-        gbd = g2.t() @ t2 if ctx.needs_input_grad[3] else None
+        gx = _dgrad(g2, w).view(xs) if ctx.needs_input_grad[0] else None
+        gw = _wgrad(g2, x2) if ctx.needs_input_grad[1] else None
+        gt = None
+        if ctx.needs_input_grad[2]:
+            # rank-sized output: the K-major form on a transposed copy of the small block-diagonal B
+            if _own_bwd() and g2.shape[1] % 64 == 0 and bd.shape[1] % 8 == 0:
+                gt = K.gemm(g2 if g2.is_contiguous() else g2.contiguous(), bd.t().contiguous()).view(ts)
+            else:
+                gt = (g2 @ bd).view(ts)
+        gbd = _wgrad(g2, t2) if ctx.needs_input_grad[3] else None
         return gx, gw, gt, gbd
 
 
@@ -77,7 +113,7 @@ def lora_linear(x, w, xa, lora_A, lora_B: List[torch.Tensor], adapted: Sequence[
                 r: int, scaling: float):
     R = len(adapted) * r
     if _gemm_ok(x, w) and R % 64 == 0 and lora_A.dtype == torch.bfloat16:
-        t = F.linear(xa, lora_A)
+        t = linear(xa, lora_A)
         bd = w.new_zeros(w.shape[0], R)
         off = [0]
         for sz in out_splits:
@@ -174,6 +210,55 @@ class _SwiGLU(torch.autograd.Function):
     def backward(ctx, gy):
         (g2,) = ctx.saved_tensors
         return K.swiglu_bwd(g2, gy.reshape(-1, gy.shape[-1]).contiguous()).view(ctx.shape)
+
+
+class _CrossEntropySum(torch.autograd.Function):
+    """Sum over rows of the cross entropy of bf16 logits, one kernel forward (online log-sum-exp in fp32, no fp32
+    copy of the logits) and one backward that writes ``(softmax - onehot) * g`` in bf16."""
+
+    @staticmethod
+    def forward(ctx, logits, labels):
+        loss, lse = K.ce_fwd(logits, labels)
+        ctx.save_for_backward(logits, labels, lse)
+        return loss.sum()
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, labels, lse = ctx.saved_tensors
+        return K.ce_bwd(logits, labels, lse, g.reshape(1).float().contiguous()), None
+
+
+def cross_entropy_sum_ok(logits: torch.Tensor) -> bool:
+    return (logits.is_cuda and logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1
+            and logits.stride(0) % 8 == 0 and logits.data_ptr() % 16 == 0 and logits.numel() > 0
+            and os.environ.get("TAH_B200_FORCE_TORCH", "0") != "1")
+
+
+def cross_entropy_sum(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """``sum_r CE(logits[r], labels[r])`` over rows whose label is not -100 (fp32 scalar)."""
+    return _CrossEntropySum.apply(logits, labels.to(torch.int64).contiguous())
+
+
+class _BceSum(torch.autograd.Function):
+    """(weighted BCE-with-logits sum, labelled count, correct decisions) of the decider logits in one launch."""
+
+    @staticmethod
+    def forward(ctx, z, labels, depth, pos_weight, thr):
+        ctx.save_for_backward(z, labels)
+        ctx.args = (depth, pos_weight, thr)
+        out = K.bce_logits(z, labels, depth, pos_weight, thr)
+        ctx.mark_non_differentiable(out[1:])
+        return out[0], out[1], out[2]
+
+    @staticmethod
+    def backward(ctx, g, _gn, _gc):
+        z, labels = ctx.saved_tensors
+        depth, pos_weight, thr = ctx.args
+        return K.bce_logits(z, labels, depth, pos_weight, thr, g=g.reshape(1).float().contiguous()), None, None, None, None
+
+
+def bce_sum(z: torch.Tensor, labels: torch.Tensor, depth: int, pos_weight: float, thr: float):
+    return _BceSum.apply(z.float().contiguous(), labels.to(torch.int64).contiguous(), int(depth), float(pos_weight), float(thr))
 
 
 def swiglu(gate_up):

@@ -183,9 +183,11 @@ def wait_flags(flags: torch.Tensor, targets: torch.Tensor) -> None:
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
-         bn: int = 0, tp_push=None, tp_wait=None, pair: Optional[bool] = None) -> torch.Tensor:
+         bn: int = 0, tp_push=None, tp_wait=None, pair: Optional[bool] = None, gelu: bool = False) -> torch.Tensor:
     """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
     weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
+
+    ``gelu``: the epilogue applies the erf GELU to the bf16-rounded output (before an optional residual add).
 
     ``pair``: every CTA computes two 128-feature output tiles (features ``f`` and ``F/2 + f``) from one
     activation tile, which cuts the activation bytes pulled per output (off unless asked for: it was not
@@ -228,7 +230,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
             c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
             c_ll(residual.stride(0) if residual is not None else 0),
             c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
-            c_int(1 if swiglu else 2 if pair else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+            c_int(1 if swiglu else 2 if pair else 3 if gelu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
             _p(status_word(x.device)), _stream())
     if tp_push is None and tp_wait is None:
         rc = lib().tahb_gemm(*args)
@@ -246,6 +248,46 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
             wait = (None, None, c_int(0))
         rc = lib().tahb_gemm_tp(*args, *push, *wait)
     _rc(rc, "tahb_gemm")
+    return out
+
+
+def gemm_t(x: torch.Tensor, w: torch.Tensor, *, x_t: bool = False, w_t: bool = False, out: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None, splits: Optional[int] = None, bn: int = 0) -> torch.Tensor:
+    """GEMM with operands read transposed straight from their row-major storage (the backward GEMMs):
+
+    * ``w_t``: ``w`` is ``[K, F]`` (instead of ``[F, K]``); * ``x_t``: ``x`` is ``[K, M]`` (instead of ``[M, K]``);
+
+    ``out[M, F] = op(x) @ op(w)^T (+ residual)``.  Data gradient of ``y = x W^T``: ``gemm_t(dy, W, w_t=True)``; weight
+    gradient: ``gemm_t(dy, x, x_t=True, w_t=True, residual=grad, out=grad)`` (reduction over the tokens, any count).
+    Same tcgen05 kernel as :func:`gemm`; the transposed tiles are described to the tensor core as MN-major."""
+    _check_bf16_2d(x, "x")
+    _check_bf16_2d(w, "w")
+    if x_t:
+        Kx, M = x.shape
+    else:
+        M, Kx = x.shape
+    if w_t:
+        Kw, F = w.shape
+    else:
+        F, Kw = w.shape
+    if Kx != Kw:
+        raise ValueError(f"reduction mismatch: x {tuple(x.shape)} (x_t={x_t}) w {tuple(w.shape)} (w_t={w_t})")
+    if not (x_t or w_t):
+        return gemm(x, w, out=out, residual=residual, splits=splits, bn=bn)
+    if out is None:
+        out = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
+    if residual is not None:
+        _check_bf16_2d(residual, "residual")
+    if splits is None and bn == 0:
+        bn, splits = plan_gemm(M, F, (Kx + 63) // 64 * 64, 0, False)
+        if x_t:
+            bn = max(bn, 64)
+    elif splits is None:
+        splits = 1
+    _rc(lib().tahb_gemm_t(_p(w), _p(x), _p(out), _p(residual), c_int(M), c_int(F), c_int(Kx), c_ll(w.stride(0)),
+                          c_ll(x.stride(0)), c_ll(out.stride(0)), c_ll(residual.stride(0) if residual is not None else 0),
+                          c_int(1 if w_t else 0), c_int(1 if x_t else 0), c_int(splits), c_int(bn),
+                          _p(status_word(x.device)), _stream()), "tahb_gemm_t")
     return out
 
 
@@ -278,6 +320,28 @@ def rms_norm_lora(x: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tens
                                 c_float(eps), _p(gate), _p(A), _p(t_out), c_int(R), c_ll(t_out.stride(0)), _stream()),
         "tahb_rmsnorm_lora")
     return out, t_out
+
+
+def layer_norm(x, w, b, eps: float = 1e-5, out=None):
+    """LayerNorm over the last dimension of bf16 ``x [M, D]`` (fp32 statistics)."""
+    _check_bf16_2d(x, "x")
+    M, D = x.shape
+    if out is None:
+        out = torch.empty(M, D, dtype=torch.bfloat16, device=x.device)
+    _rc(lib().tahb_layernorm(_p(x), _p(w), _p(b), _p(out), None, None, None, c_int(M), c_int(D), c_ll(x.stride(0)),
+                             c_ll(out.stride(0)), c_float(eps), _stream()), "tahb_layernorm")
+    return out
+
+
+def layer_norm_dot(x, w, b, dot_w, dot_b, eps: float = 1e-5, out=None):
+    """``z[r] = bf16(LayerNorm(x[r]) . dot_w + dot_b)`` as fp32: LayerNorm followed by ``Linear(D, 1)``."""
+    _check_bf16_2d(x, "x")
+    M, D = x.shape
+    if out is None:
+        out = torch.empty(M, dtype=torch.float32, device=x.device)
+    _rc(lib().tahb_layernorm(_p(x), _p(w), _p(b), None, _p(dot_w), _p(dot_b), _p(out), c_int(M), c_int(D),
+                             c_ll(x.stride(0)), c_ll(0), c_float(eps), _stream()), "tahb_layernorm")
+    return out
 
 
 def rope_table(pos: torch.Tensor, hd: int, theta: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -569,6 +633,44 @@ def attn_bwd_dkv(q, dout, k, v, count, items, nq, nkv, hd, scale, lse, dsum, dk=
                                 c_int(nq), c_int(nkv), c_int(hd), c_float(scale), _p(lse), _p(dsum),
                                 _p(status_word(q.device)), _stream()), "tahb_attn_bwd_dkv")
     return dk, dv
+
+
+# -------------------------------------------------------------------------------------------
+# losses
+# -------------------------------------------------------------------------------------------
+def ce_fwd(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100):
+    """Per-row cross entropy of bf16 ``logits [rows, V]`` in fp32 without an fp32 copy: returns ``(loss, lse)``."""
+    _check_bf16_2d(logits, "logits")
+    rows, V = logits.shape
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    _rc(lib().tahb_ce_fwd(_p(logits), _p(labels), _p(loss), _p(lse), c_int(rows), c_int(V), c_ll(logits.stride(0)),
+                          c_int(ignore_index), _stream()), "tahb_ce_fwd")
+    return loss, lse
+
+
+def ce_bwd(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, gscale: torch.Tensor, ignore_index: int = -100):
+    """``dlogits = (softmax(logits) - onehot(labels)) * gscale[0]`` in bf16 (zero rows where the label is ignored)."""
+    rows, V = logits.shape
+    d = torch.empty(rows, V, dtype=torch.bfloat16, device=logits.device)
+    _rc(lib().tahb_ce_bwd(_p(logits), _p(labels), _p(lse), _p(gscale), _p(d), c_int(rows), c_int(V),
+                          c_ll(logits.stride(0)), c_ll(d.stride(0)), c_int(ignore_index), _stream()), "tahb_ce_bwd")
+    return d
+
+
+def bce_logits(z: torch.Tensor, labels: torch.Tensor, depth: int, pos_weight: float, thr: float, g=None):
+    """Forward (``g`` None): fp32 ``[3]`` = (sum of BCE terms over labelled tokens, their count, correct threshold
+    decisions).  Backward (``g`` = upstream gradient scalar tensor): ``dz``."""
+    n = z.shape[0]
+    if g is None:
+        out = torch.zeros(3, dtype=torch.float32, device=z.device)
+        _rc(lib().tahb_bce_logits(_p(z), _p(labels), c_int(depth), c_float(pos_weight), c_float(thr), c_int(n), _p(out),
+                                  None, None, _stream()), "tahb_bce_logits")
+        return out
+    dz = torch.empty(n, dtype=torch.float32, device=z.device)
+    _rc(lib().tahb_bce_logits(_p(z), _p(labels), c_int(depth), c_float(pos_weight), c_float(thr), c_int(n), None, _p(g),
+                              _p(dz), _stream()), "tahb_bce_logits")
+    return dz
 
 
 # -------------------------------------------------------------------------------------------

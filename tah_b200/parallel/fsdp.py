@@ -498,12 +498,13 @@ class FsdpAdamW:
     replicated parameters go through :class:`ZeroAdamW`; one global gradient norm clips both."""
 
     def __init__(self, model, lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
-                 max_grad_norm: float = 0.0, use_multicast: bool = True):
+                 max_grad_norm: float = 0.0, use_multicast: bool = True, no_decay=None):
         self.state: FsdpState = model._fsdp
         st = self.state
         small = [p for p in model.parameters() if p.requires_grad and id(p) not in st.sharded_ids]
         self.small = ZeroAdamW(small, group=st.group if st.world > 1 else None, lr=lr, betas=betas, eps=eps,
-                               weight_decay=weight_decay, max_grad_norm=max_grad_norm, use_multicast=use_multicast) if small else None
+                               weight_decay=weight_decay, max_grad_norm=max_grad_norm, use_multicast=use_multicast,
+                               no_decay=no_decay) if small else None
         self.lr, self.betas, self.eps, self.weight_decay, self.max_grad_norm = lr, betas, eps, weight_decay, max_grad_norm
         self.step_count = 0
         self.last_grad_norm: Optional[torch.Tensor] = None

@@ -29,8 +29,14 @@ MAX_GRID = 148
 class ZeroAdamW:
     def __init__(self, params: Iterable[torch.nn.Parameter], group=None, lr: float = 1e-4, betas=(0.9, 0.999),
                  eps: float = 1e-8, weight_decay: float = 0.01, max_grad_norm: float = 0.0,
-                 use_multicast: bool = True):
-        self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
+                 use_multicast: bool = True, no_decay: Optional[Iterable[torch.nn.Parameter]] = None):
+        """``no_decay``: parameters that take no weight decay (norm gains, biases, thresholds; the HuggingFace
+        trainer the reference builds on excludes LayerNorm and bias parameters from decay).  They are laid out
+        behind the decayed ones in the flat buffers, so the kernel needs one boundary index."""
+        skip = {id(p) for p in (no_decay or [])}
+        ps = [p for p in params if p.requires_grad]
+        self.params: List[torch.nn.Parameter] = [p for p in ps if id(p) not in skip] + [p for p in ps if id(p) in skip]
+        self.decay_numel = sum(p.numel() for p in ps if id(p) not in skip)
         if not self.params:
             raise ValueError("no trainable parameters")
         self.group = group
@@ -62,6 +68,9 @@ class ZeroAdamW:
                 p.grad = self.flat_grad[off:off + k].view_as(p)
                 off += k
         self.flat_grad.zero_()
+        if self.dist_on and self.world > 1:
+            # every rank starts from rank 0's values, whatever its local initialisation seed was
+            dist.broadcast(self.flat_param, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         self.master = self.flat_param[self.lo:self.hi].float().clone()
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
@@ -156,6 +165,8 @@ class ZeroAdamW:
         self.norm_sq.zero_()
 
         def launch(phase):
+            if phase == 1:
+                lib.tahb_zero_set_nodecay_from(cll(self.decay_numel))
             rc = lib.tahb_zero_step(ci(phase), arr(self.grad_ptrs), arr(self.param_ptrs), cvp(self.mc_grad),
                                     cvp(self.mc_param), cvp(self.gshard.data_ptr()), cvp(self.master.data_ptr()),
                                     cvp(self.m.data_ptr()), cvp(self.v.data_ptr()), cvp(self.norm_sq.data_ptr()),
@@ -193,7 +204,8 @@ class ZeroAdamW:
         self.m.mul_(b1).add_(g, alpha=1 - b1)
         self.v.mul_(b2).addcmul_(g, g, value=1 - b2)
         upd = (self.m / bc1) / ((self.v / bc2).sqrt() + self.eps)
-        self.master.mul_(1 - lr * self.weight_decay).add_(upd, alpha=-lr)
+        decay = (torch.arange(self.lo, self.hi, device=self.master.device) < self.decay_numel).to(self.master.dtype)
+        self.master.mul_(1 - lr * self.weight_decay * decay).add_(upd, alpha=-lr)
         new = self.master.to(self.dtype)
         if self.world > 1:
             parts = [torch.empty_like(new) for _ in range(self.world)]

@@ -199,13 +199,15 @@ class CustomTaHTrainer:
         a = self.args
         kw = dict(lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                   weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm or 0.0)
+        no_decay = [p for n, p in self.model.named_parameters()
+                    if p.dim() < 2 or n.endswith("bias") or "norm" in n.lower() or n.endswith("threshold")]
         if str(a.strategy).lower() in ("zero3", "fsdp") and self.dist_on and self.world > 1:
             from tah_b200.parallel.fsdp import FsdpAdamW, shard_model
             if getattr(self.model, "_fsdp", None) is None:
                 shard_model(self.model, dist.group.WORLD, self.model.device)
-            self.optimizer = FsdpAdamW(self.model, **kw)
+            self.optimizer = FsdpAdamW(self.model, no_decay=no_decay, **kw)
         else:
-            self.optimizer = ZeroAdamW(self.model.parameters(), group=None, **kw)
+            self.optimizer = ZeroAdamW(self.model.parameters(), group=None, no_decay=no_decay, **kw)
         return self.optimizer
 
     def _lr_at(self, step: int) -> float:

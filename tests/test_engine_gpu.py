@@ -222,3 +222,68 @@ def test_engine_with_head_dim_128_uses_fused_kernels_and_matches_unfused(monkeyp
     assert outs[0][1] < outs[1][1]                                         # fewer launches per tick
     same = sum(a == b for ra, rb in zip(outs[0][0], outs[1][0]) for a, b in zip(ra, rb))
     assert same >= 0.9 * B * n_new, same
+
+
+def test_learned_mlp_decider_kernel_chain_matches_module_and_drives_the_engine():
+    """``MLPIterDecider`` (tapped hidden states + sorted top-k logits -> residual MLP) as the engine's kernel chain
+    against the PyTorch module, and a generation driven by it (no override)."""
+    from tah_b200.engine import TaHEngine
+    H = 256
+    kw = dict(topk=100, hidden_states_size=H, hidden_states_layer_nums=[1, 3, 4], hidden_dims=[128, 128, 128],
+              expansion_factor=4, dropout_rate=0.1, threshold=0.5)
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16, decider="MLPIterDecider", decider_kwargs=kw).cuda().eval()
+    dec = model.iter_decider.cuda().to(torch.bfloat16).eval()
+    with torch.no_grad():
+        for n, p in dec.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(std=0.2)
+    eng = TaHEngine(model, max_rows=8, max_seq_len=64, use_cuda_graph=True, deep_fraction=1.0)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    taps = (torch.randn(37, 3 * H, generator=g, device="cuda") * 1.5).to(torch.bfloat16)
+    topv = torch.sort(torch.randn(37, 100, generator=g, device="cuda") * 3, dim=-1, descending=True).values
+    z = eng._score_mlp(dec, taps, topv)
+    assert eng._mlp_decider_plan(dec, taps.device) is not None               # the kernel chain ran, not the module
+    with torch.no_grad():
+        ref = dec.score(taps, topv.to(torch.bfloat16)).float()
+    torch.testing.assert_close(z, ref, atol=0.15, rtol=0.05)
+    assert ((z > 0) == (ref > 0)).float().mean().item() > 0.9
+    ids = torch.randint(0, 1024, (4, 12), generator=torch.Generator().manual_seed(1)).cuda()
+    res = eng.generate(ids, None, max_new_tokens=12, do_sample=False)
+    assert all(len(t) == 12 for t in res.tokens)
+    assert 1.0 <= sum(res.iter_counts) / len(res.iter_counts) <= 2.0
+    eng.use_cuda_graph = False
+    res2 = eng.generate(ids, None, max_new_tokens=12, do_sample=False)
+    assert res.tokens == res2.tokens
+
+
+def test_serve_admits_requests_into_freed_rows_and_matches_generate():
+    """Continuous batching: six requests of different lengths through two rows.  Every request's tokens equal
+    those of a plain generate() of that request alone, pages are returned and reused, and the batch bucket of a
+    3-request generate() is the 4-row graph."""
+    from tah_b200.engine import TaHEngine
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16, decider="SimpleMLPIterDecider",
+                     decider_kwargs=dict(hidden_states_size=256, inner_size=64, threshold=0.5)).cuda().eval()
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 1024, (n,), generator=g) for n in (9, 21, 14, 30, 5, 17)]
+    n_new = 12
+    eng = TaHEngine(model, max_rows=8, max_seq_len=64, use_cuda_graph=True, deep_fraction=1.0)
+    served, stats = eng.serve(prompts, max_new_tokens=n_new, rows=2, check_every=4)
+    assert stats["admitted"] == 6 and stats["pages_released"] > 0 and len(served) == 6
+    assert all(len(t) == n_new for t in served)
+    solo = TaHEngine(model, max_rows=8, max_seq_len=64, use_cuda_graph=True, deep_fraction=1.0)
+    for p, got in zip(prompts, served):
+        want = solo.generate(p[None].cuda(), None, max_new_tokens=n_new, do_sample=False).tokens[0]
+        agree = sum(a == b for a, b in zip(got, want))
+        assert agree >= n_new - 2, (got, want)              # rows are independent; bf16 ties may flip a late token
+    # everything was returned: both pools are empty again apart from the rows that finished last
+    assert eng.kv.pages_in_use(0) <= 2 * eng.kv.max_pages[0]
+    # batch buckets: 3 requests run in the 4-row bucket and reuse its graph on the next call
+    three = torch.stack([torch.randint(0, 1024, (10,), generator=g) for _ in range(3)]).cuda()
+    a = solo.generate(three, None, max_new_tokens=6, do_sample=False)
+    caps = solo.graph_captures
+    b = solo.generate(three[:3], None, max_new_tokens=6, do_sample=False)
+    four = torch.cat([three, three[:1]], 0)
+    c = solo.generate(four, None, max_new_tokens=6, do_sample=False)
+    assert solo.bucket_rows(3) == 4 and len(a.tokens) == 3 and a.tokens == b.tokens
+    assert solo.graph_captures == caps                     # the 3- and the 4-request calls share one captured graph
+    assert c.tokens[:3] == a.tokens

@@ -193,6 +193,63 @@ def test_rmsnorm_lora_fused(M, H, R):
     assert (t[:, R:] == 5.0).all() and (t[gate == 0][:, :R] == 0).all()
 
 
+@pytest.mark.parametrize("M,D", [(5, 512), (256, 512), (33, 256), (7, 2048)])
+def test_layernorm_and_layernorm_dot(M, D):
+    Kc = _cuda()
+    x = _rand(M, D, seed=1, scale=2.0)
+    w, b = (_rand(D, seed=2).float() * 0.2 + 1).bfloat16(), (_rand(D, seed=3).float() * 0.2).bfloat16()
+    y = Kc.layer_norm(x, w, b, 1e-5)
+    ref = torch.nn.functional.layer_norm(x.float(), (D,), w.float(), b.float(), 1e-5)
+    _close(y, ref, atol=2e-2, rtol=2e-2)
+    dw, db = _rand(D, seed=4, scale=D ** -0.5), _rand(1, seed=5)
+    z = Kc.layer_norm_dot(x, w, b, dw, db, 1e-5)
+    zref = ref.to(torch.bfloat16).float() @ dw.float() + db.float()
+    _close(z, zref, atol=3e-2, rtol=3e-2)
+
+
+def test_gemm_gelu_epilogue_and_bias_extension():
+    """``gelu(x W^T + b)`` and ``res + (u W^T + b)``: the two GEMMs of a decider block."""
+    Kc = _cuda()
+    M, K, F = 200, 512, 2048
+    x, w = _rand(M, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    bias = _rand(F, seed=3, scale=0.3)
+    ones = torch.zeros(M, 64, dtype=torch.bfloat16, device="cuda")
+    ones[:, 0] = 1
+    bext = torch.zeros(F, 64, dtype=torch.bfloat16, device="cuda")
+    bext[:, 0] = bias
+    y = Kc.gemm(x, w, x2=ones, w2=bext, gelu=True)
+    ref = torch.nn.functional.gelu((x.float() @ w.float().t() + bias.float()).to(torch.bfloat16).float())
+    _close(y, ref, atol=2e-2, rtol=2e-2)
+    w2 = _rand(K, F, scale=F ** -0.5, seed=4)
+    res = _rand(M, K, seed=5)
+    out = res.clone()
+    Kc.gemm(y, w2, residual=out, out=out)
+    _close(out, res.float() + (y.float() @ w2.float().t()).to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("T,F,K", [(300, 512, 256), (8192, 2048, 2048), (1000, 4096, 2048), (77, 192, 2048), (130, 2048, 64)])
+def test_backward_gemms_with_transposed_operands(T, F, K):
+    """Data and weight gradients of ``y = x w^T`` on the tcgen05 GEMM reading its operands transposed in place
+    (MN-major tiles), against fp32 matmuls; the weight gradient also in accumulate-into-grad form."""
+    Kc = _cuda()
+    from tah_b200.ops import autograd_ops as ao
+    x, w = _rand(T, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    gy = _rand(T, F, seed=3, scale=F ** -0.5)
+    if K % 128 == 0:
+        gx = Kc.gemm_t(gy, w, w_t=True)
+        _close(gx, gy.float() @ w.float(), atol=3e-2, rtol=3e-2)
+    gw = ao._wgrad(gy, x)
+    ref = gy.float().t() @ x.float()
+    assert gw.shape == (F, K)
+    _close(gw, ref, atol=max(3e-2, 2e-2 * float(ref.abs().max())), rtol=3e-2)
+    if K % 128 == 0:
+        acc0 = _rand(F, K, seed=4, scale=0.1)
+        acc = acc0.clone()
+        Kc.gemm_t(gy, x, x_t=True, w_t=True, residual=acc, out=acc)
+        _close(acc, acc0.float() + ref.to(torch.bfloat16).float(), atol=max(4e-2, 2e-2 * float(ref.abs().max())), rtol=3e-2)
+    Kc.check_status()
+
+
 def _paged_setup(rows, lens, nkv, hd, page, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     max_pages = (max(lens) + page - 1) // page + 1
@@ -679,3 +736,72 @@ def test_training_step_kernel_path_matches_torch_path_multi_tile(monkeypatch):
         gb = dict(twin.simple_base_model.model.named_parameters())[name].grad.float().flatten()
         cos = torch.nn.functional.cosine_similarity(ga, gb, dim=0)
         assert float(cos) > 0.97, (name, float(cos))
+
+
+def test_peer_flag_wait_runs_out_and_reports_a_timeout():
+    """A consumer GEMM that waits for rows a peer would broadcast: nothing advances the landing flags, the wait
+    limit is 5 ms, so the kernel gives up, records the timeout code and returns; the host reads the status word
+    and raises.  Nothing traps or hangs, and the context stays usable."""
+    import time
+    Kc = _cuda()
+    x, w = _rand(64, 256, seed=1), _rand(256, 256, scale=256 ** -0.5, seed=2)
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    targets = torch.ones(2, dtype=torch.int32, device="cuda")
+    prev = Kc.set_peer_wait_limit_ns(5_000_000)
+    try:
+        torch.cuda.synchronize()
+        t0 = time.time()
+        Kc.gemm(x, w, tp_wait=(flags, targets))
+        Kc.wait_flags(flags, targets)
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 1.0                                   # two 5 ms limits, not the 2 s default
+        with pytest.raises(Kc.KernelTimeout, match="peer flag"):
+            Kc.check_status()
+    finally:
+        Kc.set_peer_wait_limit_ns(prev)
+    Kc.check_status()                                                   # the status word was cleared
+    flags.fill_(1)                                                      # the flags arrive: same launch succeeds
+    y = Kc.gemm(x, w, tp_wait=(flags, targets))
+    Kc.check_status()
+    _close(y, x.float() @ w.float().t(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("rows,V", [(37, 151936), (300, 1024), (5, 1000)])
+def test_fused_cross_entropy_forward_backward(rows, V):
+    """CE kernel on bf16 logits (fp32 math, no fp32 copy) against ``F.cross_entropy`` on the upcast logits."""
+    from tah_b200.ops import autograd_ops as ao
+    g = torch.Generator(device="cuda").manual_seed(1)
+    logits = (torch.randn(rows, V, generator=g, device="cuda") * 3).to(torch.bfloat16).requires_grad_(True)
+    labels = torch.randint(0, V, (rows,), generator=g, device="cuda")
+    labels[::5] = -100
+    assert ao.cross_entropy_sum_ok(logits)
+    loss = ao.cross_entropy_sum(logits, labels) / 7.0
+    loss.backward()
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels, ignore_index=-100, reduction="sum") / 7.0
+    ref.backward()
+    torch.testing.assert_close(loss.float(), ref, atol=1e-3, rtol=1e-4)
+    _close(logits.grad, ref_in.grad, atol=2e-3, rtol=2e-2)
+    assert float(logits.grad[::5].abs().max()) == 0.0
+
+
+def test_fused_bce_with_logits_forward_backward():
+    from tah_b200.ops import autograd_ops as ao
+    g = torch.Generator(device="cuda").manual_seed(2)
+    n = 5000
+    z = (torch.randn(n, generator=g, device="cuda") * 2).requires_grad_(True)
+    labels = torch.randint(1, 4, (n,), generator=g, device="cuda")
+    labels[::7] = -100
+    depth, pw, thr = 1, 5.4, 0.8
+    s, cnt, correct = ao.bce_sum(z, labels, depth, pw, thr)
+    (s / cnt).backward()
+    zr = z.detach().clone().requires_grad_(True)
+    w = (labels != -100).float()
+    y = (labels > depth).float()
+    per = torch.nn.functional.binary_cross_entropy_with_logits(zr, y, pos_weight=torch.tensor(pw, device="cuda"), reduction="none")
+    ref = (per * w).sum() / w.sum()
+    ref.backward()
+    torch.testing.assert_close(s / cnt, ref, atol=1e-4, rtol=1e-4)
+    assert float(cnt) == float(w.sum())
+    assert float(correct) == float((((torch.sigmoid(zr) > thr).float() == y).float() * w).sum())
+    torch.testing.assert_close(z.grad, zr.grad, atol=1e-6, rtol=1e-4)

@@ -337,3 +337,28 @@ def test_reference_import_names_resolve_to_this_package():
     from tah.train import CustomTaHDataCollator, CustomTaHTrainer, LoggerCallback, fixed_cross_entropy  # noqa: F401
     from tah.utils import preprocess_dataset  # noqa: F401
     from tah.evaluate.backends import cleanup, setup_backend, setup_hf, setup_sglang, setup_tah, time_inference, warmup  # noqa: F401
+
+
+def test_zero_adamw_no_decay_group_matches_torch_param_groups():
+    """Parameters named as no-decay (norm gains, biases) take no weight decay, like the two parameter groups of the
+    HuggingFace trainer the reference builds on."""
+    from tah_b200.parallel.zero import ZeroAdamW
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.LayerNorm(5), torch.nn.Linear(5, 3))
+    ref = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.LayerNorm(5), torch.nn.Linear(5, 3))
+    ref.load_state_dict(net.state_dict())
+    nd = [p for n, p in net.named_parameters() if p.dim() < 2]
+    opt = ZeroAdamW(net.parameters(), lr=1e-2, weight_decay=0.1, no_decay=nd)
+    rnd = {id(p) for n, p in ref.named_parameters() if p.dim() < 2}
+    ropt = torch.optim.AdamW([{"params": [p for p in ref.parameters() if id(p) not in rnd], "weight_decay": 0.1},
+                              {"params": [p for p in ref.parameters() if id(p) in rnd], "weight_decay": 0.0}], lr=1e-2)
+    for step in range(3):
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(step))
+        net(x).pow(2).mean().backward()
+        ref(x).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+        ropt.step()
+        ropt.zero_grad()
+    for (n, a), b in zip(net.named_parameters(), ref.parameters()):
+        torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5, msg=n)
