@@ -274,10 +274,29 @@ def topk_softmax_embed(logits, embedding_weight, topk: int):
     if logits.dtype != torch.bfloat16 or logits.dim() != 2 or k > 128 or logits.numel() == 0:
         return torch_ref.topk_softmax_embed(logits, embedding_weight, topk)
     _, idx = K.topk_rows(logits.detach().contiguous(), k)
-    idx = idx.long()
-    vals = logits.gather(-1, idx)
+    vals = logits.gather(-1, idx.long())
+    if embedding_weight.dtype == torch.bfloat16 and embedding_weight.is_contiguous() and embedding_weight.shape[1] % 8 == 0:
+        return _SoftEmbedMix.apply(vals.float(), embedding_weight, idx)
     probs = torch.softmax(vals, dim=-1)
-    return (probs.unsqueeze(-1) * embedding_weight[idx]).sum(-2).to(embedding_weight.dtype)
+    return (probs.unsqueeze(-1) * embedding_weight[idx.long()]).sum(-2).to(embedding_weight.dtype)
+
+
+class _SoftEmbedMix(torch.autograd.Function):
+    """``sum_k softmax(vals)_k E[idx_k]`` with the mix kernel forward and one kernel backward: no ``[rows, k, H]``
+    gather exists in either direction; the embedding gradient is scattered with vector reductions into an fp32
+    accumulator (reference ``tah/model/tah_model.py:57-75`` and its autograd)."""
+
+    @staticmethod
+    def forward(ctx, vals, E, idx):
+        ctx.save_for_backward(vals, E, idx)
+        return K.soft_embed_rows(vals.contiguous(), idx.contiguous(), E)
+
+    @staticmethod
+    def backward(ctx, dout):
+        vals, E, idx = ctx.saved_tensors
+        dE = torch.zeros(E.shape, dtype=torch.float32, device=E.device)
+        dval = K.soft_embed_bwd(dout.contiguous(), vals.contiguous(), idx.contiguous(), E, dE)
+        return dval.to(vals.dtype), dE.to(E.dtype) if ctx.needs_input_grad[1] else None, None
 
 
 def duo_attention(q, k, v, q_pos, kv_pos, kv_valid, q_depth=None, kv_depth=None):

@@ -658,6 +658,16 @@ def ce_bwd(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, gscale
     return d
 
 
+def soft_embed_bwd(dout: torch.Tensor, val: torch.Tensor, idx: torch.Tensor, E: torch.Tensor, dE: torch.Tensor):
+    """Backward of :func:`soft_embed_rows`: returns ``dval [rows, K]`` (fp32) and adds ``p_k * dout`` into the fp32
+    accumulator ``dE [V, H]`` at the rows ``idx``."""
+    rows, Kk = val.shape
+    dval = torch.empty(rows, Kk, dtype=torch.float32, device=val.device)
+    _rc(lib().tahb_soft_embed_bwd(_p(dout), _p(val), _p(idx), _p(E), _p(dval), _p(dE), c_int(rows), c_int(Kk),
+                                  c_int(E.shape[1]), c_ll(dout.stride(0)), _stream()), "tahb_soft_embed_bwd")
+    return dval
+
+
 def bce_logits(z: torch.Tensor, labels: torch.Tensor, depth: int, pos_weight: float, thr: float, g=None):
     """Forward (``g`` None): fp32 ``[3]`` = (sum of BCE terms over labelled tokens, their count, correct threshold
     decisions).  Backward (``g`` = upstream gradient scalar tensor): ``dz``."""

@@ -805,3 +805,23 @@ def test_fused_bce_with_logits_forward_backward():
     assert float(cnt) == float(w.sum())
     assert float(correct) == float((((torch.sigmoid(zr) > thr).float() == y).float() * w).sum())
     torch.testing.assert_close(z.grad, zr.grad, atol=1e-6, rtol=1e-4)
+
+
+def test_soft_embedding_mix_forward_backward_kernels():
+    """Top-k soft input (values -> softmax -> mix of embedding rows) through the kernel pair against the fp32
+    PyTorch statement, gradients to the logits and to the embedding rows included."""
+    from tah_b200.ops import autograd_ops as ao
+    g = torch.Generator(device="cuda").manual_seed(5)
+    n, V, H, k = 50, 4096, 512, 100
+    logits = (torch.randn(n, V, generator=g, device="cuda") * 2).to(torch.bfloat16).requires_grad_(True)
+    E = (torch.randn(V, H, generator=g, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    gout = torch.randn(n, H, generator=g, device="cuda").to(torch.bfloat16)
+    out = ao.topk_softmax_embed(logits, E, k)
+    out.backward(gout)
+    lf, Ef = logits.detach().float().requires_grad_(True), E.detach().float().requires_grad_(True)
+    vals, idx = torch.topk(lf, k, dim=-1)
+    ref = (torch.softmax(vals, -1).unsqueeze(-1) * Ef[idx]).sum(-2)
+    ref.backward(gout.float())
+    _close(out, ref, atol=3e-2, rtol=3e-2)
+    _close(logits.grad, lf.grad, atol=3e-2, rtol=5e-2)
+    _close(E.grad, Ef.grad, atol=3e-2, rtol=5e-2)
