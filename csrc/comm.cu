@@ -235,6 +235,12 @@ struct PushReduceParams {
   int M, H, rank, world, rpr;
   float eps;
   int add_residual, final_wait;
+  // Optional tap of the updated residual stream (a learned decider reads hidden states of chosen layers on every
+  // rank): the owner also stores its rows of h into every rank's tap buffer (row pitch tap_ld elements, pointers
+  // already at the tap's column), before the same fence and landing flags as the normalised rows.
+  __nv_bfloat16* tap[COMM_MAX_RANKS];
+  __nv_bfloat16* mc_tap;
+  long long tap_ld;                               // 0 = no tap
 };
 
 template <int VPT>
@@ -292,6 +298,14 @@ __global__ void __launch_bounds__(256) push_reduce_norm_bcast_kernel(const PushR
           ho2[j] = __floats2bfloat162_rn(x0, x1);
         }
         *reinterpret_cast<uint4*>(p.h + off + idx * 8) = ho;
+        if (p.tap_ld != 0) {
+          const size_t toff = (size_t)row * (size_t)p.tap_ld + idx * 8;
+          if (p.mc_tap != nullptr) {
+            multimem_st_v4(p.mc_tap + toff, ho);
+          } else {
+            for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.tap[q] + toff) = ho;
+          }
+        }
       }
     }
     ss = warp_sum(ss);
@@ -399,15 +413,22 @@ extern "C" int tahb_fused_reduce_residual_norm(void* const* partial, void* const
 
 // Push-based reduce + residual + RMSNorm + broadcast (see push_reduce_norm_bcast_kernel).
 // slot / cnt / cnt_target / xtarget / arrive / h are local; xout / xflag are arrays of `world`
-// pointers (peer addresses).  Rows are dealt out in blocks of `rpr`.
+// pointers (peer addresses).  Rows are dealt out in blocks of `rpr`.  `tap` (optional): `world` pointers to
+// the column of every rank's tap buffer that receives the updated residual rows (16-byte aligned, row pitch
+// tap_ld elements), `mc_tap` its multicast address or null.
 extern "C" int tahb_push_reduce_norm_bcast(const void* slot, void* cnt, void* cnt_target, void* const* xout,
                                            void* mc_xout, void* const* xflag, void* xtarget, void* arrive, void* h,
                                            const void* ln_w, int* status, int M, int H, int rank, int world, int rpr,
                                            float eps, int add_residual, int final_wait, int grid,
-                                           cudaStream_t stream) {
+                                           cudaStream_t stream, void* const* tap, void* mc_tap, long long tap_ld) {
   if (M <= 0) return 0;
   if (world < 1 || world > COMM_MAX_RANKS || H % 128 || rpr <= 0) return -1;
+  if (tap != nullptr && (tap_ld < H || tap_ld % 8)) return -1;
   PushReduceParams p;
+  for (int q = 0; q < COMM_MAX_RANKS; ++q)
+    p.tap[q] = tap != nullptr ? reinterpret_cast<__nv_bfloat16*>(tap[q < world ? q : 0]) : nullptr;
+  p.mc_tap = tap != nullptr ? reinterpret_cast<__nv_bfloat16*>(mc_tap) : nullptr;
+  p.tap_ld = tap != nullptr ? tap_ld : 0;
   p.slot = reinterpret_cast<const __nv_bfloat16*>(slot);
   p.cnt = reinterpret_cast<uint32_t*>(cnt);
   p.cnt_target = reinterpret_cast<uint32_t*>(cnt_target);

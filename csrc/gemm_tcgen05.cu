@@ -202,86 +202,94 @@ __device__ __forceinline__ void qkv_epilogue(const GemmParams& p, const __nv_bfl
   }
   named_bar_sync(1, 128);
   const __nv_bfloat16* nw = is_q ? p.q_norm_w : p.k_norm_w;
-  float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  // Packed bf16x2 arithmetic: a bf16 x bf16 product is exact in fp32, so __hmul2 rounds once exactly like the
+  // scalar statement bf16(float(a) * float(b)); this more than halves the instruction count of the loop, which
+  // only four warps execute.
+  __nv_bfloat162 w01 = __floats2bfloat162_rn(0.f, 0.f), w23 = w01;
   float inv[4] = {0.f, 0.f, 0.f, 0.f};
   const bool upper = lane >= 16;
   if (is_q || is_k) {
+    const uint2 wr = *reinterpret_cast<const uint2*>(nw + lane * 4);
+    w01 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x);
+    w23 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+    if (!table) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      wv[i] = __bfloat162float(nw[lane * 4 + i]);
-      const int d = lane * 4 + i;
-      const int j = upper ? d - 64 : d;
-      inv[i] = exp2f(-(2.0f * (float)j / 128.0f) * p.log2_theta);
+      for (int i = 0; i < 4; ++i) {
+        const int d = lane * 4 + i;
+        const int j = upper ? d - 64 : d;
+        inv[i] = exp2f(-(2.0f * (float)j / 128.0f) * p.log2_theta);
+      }
     }
   }
-  // Four tokens per warp and step, written phase by phase: only four warps run here, so the latency of a
-  // token's dependent chain (reduction, shuffles, roundings) is hidden by the other three tokens' chains.
+  const __nv_bfloat162 sgn = upper ? __floats2bfloat162_rn(1.f, 1.f) : __floats2bfloat162_rn(-1.f, -1.f);
+  // Four tokens per warp and step, written phase by phase: the latency of a token's dependent chain (reduction,
+  // shuffles) is hidden by the other three tokens' chains.
   constexpr int U = 4;
   for (int r0 = w4; r0 < n_tok; r0 += 4 * U) {
     int rr[U];
     bool live[U];
     uint2 raw[U], outv[U];
-    float x[U][4];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       rr[u] = r0 + 4 * u;
       live[u] = rr[u] < n_tok && ta + rr[u] < p.M;
       raw[u] = live[u] ? *reinterpret_cast<const uint2*>(stg + rr[u] * 128 + lane * 4) : make_uint2(0u, 0u);
-      const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
-      const float2 a = __bfloat1622float2(rh[0]), b = __bfloat1622float2(rh[1]);
-      x[u][0] = a.x; x[u][1] = a.y; x[u][2] = b.x; x[u][3] = b.y;
       outv[u] = raw[u];
     }
     if (is_q || is_k) {
-      float ss[U];
+      float x[U][4], ss[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) ss[u] = x[u][0] * x[u][0] + x[u][1] * x[u][1] + x[u][2] * x[u][2] + x[u][3] * x[u][3];
+      for (int u = 0; u < U; ++u) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u].y));
+        x[u][0] = a.x; x[u][1] = a.y; x[u][2] = b.x; x[u][3] = b.y;
+        ss[u] = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
         for (int u = 0; u < U; ++u) ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], o);
       }
-      float n[U][4], partner[U][4];
+      __nv_bfloat162 n01[U], n23[U];
+      uint32_t p01[U], p23[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const float rstd = rsqrtf(ss[u] / 128.0f + p.qk_eps);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) n[u][i] = bf16_round(wv[i] * bf16_round(x[u][i] * rstd));
+        n01[u] = __hmul2(w01, __floats2bfloat162_rn(x[u][0] * rstd, x[u][1] * rstd));
+        n23[u] = __hmul2(w23, __floats2bfloat162_rn(x[u][2] * rstd, x[u][3] * rstd));
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) partner[u][i] = __shfl_xor_sync(0xffffffffu, n[u][i], 16);
+        p01[u] = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&n01[u]), 16);
+        p23[u] = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&n23[u]), 16);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        float cv[4], sv[4];
+        __nv_bfloat162 c01, c23, s01, s23;
         if (table) {
           // lane l owns dims 4l .. 4l+3, whose frequency index is 4 (l mod 16) ..: cos there, sin 64 further
           const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(s_cs + (live[u] ? rr[u] : 0) * 16) + (lane & 15) * 4;
           const uint2 cr = *reinterpret_cast<const uint2*>(row), sr = *reinterpret_cast<const uint2*>(row + 64);
-          const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&cr);
-          const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&sr);
-          const float2 c0 = __bfloat1622float2(ch[0]), c1 = __bfloat1622float2(ch[1]);
-          const float2 s0 = __bfloat1622float2(sh[0]), s1 = __bfloat1622float2(sh[1]);
-          cv[0] = c0.x; cv[1] = c0.y; cv[2] = c1.x; cv[3] = c1.y;
-          sv[0] = s0.x; sv[1] = s0.y; sv[2] = s1.x; sv[3] = s1.y;
+          c01 = *reinterpret_cast<const __nv_bfloat162*>(&cr.x); c23 = *reinterpret_cast<const __nv_bfloat162*>(&cr.y);
+          s01 = *reinterpret_cast<const __nv_bfloat162*>(&sr.x); s23 = *reinterpret_cast<const __nv_bfloat162*>(&sr.y);
         } else {
           const float posf = live[u] ? (float)p.pos[ta + rr[u]] : 0.f;
+          float cv[4], sv[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float ang = posf * inv[i];
-            cv[i] = bf16_round(cosf(ang));
-            sv[i] = bf16_round(sinf(ang));
+            cv[i] = cosf(ang);
+            sv[i] = sinf(ang);
           }
+          c01 = __floats2bfloat162_rn(cv[0], cv[1]); c23 = __floats2bfloat162_rn(cv[2], cv[3]);
+          s01 = __floats2bfloat162_rn(sv[0], sv[1]); s23 = __floats2bfloat162_rn(sv[2], sv[3]);
         }
-        float y[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float rot = upper ? partner[u][i] : -partner[u][i];
-          y[i] = bf16_round(bf16_round(n[u][i] * cv[i]) + bf16_round(rot * sv[i]));
-        }
-        __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0], y[1]), o1 = __floats2bfloat162_rn(y[2], y[3]);
+        // y = bf16( bf16(n c) + bf16(+-partner s) ): the products in packed bf16, the sum in fp32, one rounding
+        const float2 a01 = __bfloat1622float2(__hmul2(n01[u], c01)), a23 = __bfloat1622float2(__hmul2(n23[u], c23));
+        const float2 b01 = __bfloat1622float2(__hmul2(__hmul2(*reinterpret_cast<__nv_bfloat162*>(&p01[u]), sgn), s01));
+        const float2 b23 = __bfloat1622float2(__hmul2(__hmul2(*reinterpret_cast<__nv_bfloat162*>(&p23[u]), sgn), s23));
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(a01.x + b01.x, a01.y + b01.y);
+        __nv_bfloat162 o1 = __floats2bfloat162_rn(a23.x + b23.x, a23.y + b23.y);
         outv[u].x = *reinterpret_cast<uint32_t*>(&o0);
         outv[u].y = *reinterpret_cast<uint32_t*>(&o1);
       }

@@ -46,6 +46,16 @@ class GenerationResult:
     extra: dict = field(default_factory=dict)
 
 
+def _fusions(default: str):
+    """Kernel fusions selected by ``TAH_B200_FUSE``: "1" = all, "0" = none, or a comma list of "qkv" (QK-norm, RoPE
+    and the K/V write in the QKV GEMM's epilogue) and "lora" (LoRA-A of the gated rows inside the RMSNorm launch);
+    unset = ``default`` (the packed prefill pass fuses "qkv", the decode tick nothing)."""
+    v = os.environ.get("TAH_B200_FUSE", default)
+    if v == "1":
+        return {"qkv", "lora"}
+    return {t for t in v.split(",") if t in ("qkv", "lora")}
+
+
 class TaHEngine:
     def __init__(self, model, max_rows: int = 64, max_seq_len: int = 2048, page_size: int = 16,
                  deep_fraction: float = 0.25, use_cuda_graph: bool = True, tp=None):
@@ -232,7 +242,7 @@ class TaHEngine:
         t_down = bf(n, w.r_down) if lora else None
         tap_layers = self._tap_layers()
         tensor_core_attn = hd in (64, 128) and os.environ.get("TAH_B200_NAIVE_PREFILL", "0") != "1"
-        fuse_qkv = hd == 128 and os.environ.get("TAH_B200_NO_FUSE", "0") not in ("1", "qkv")
+        fuse_qkv = hd == 128 and "qkv" in _fusions("qkv")
         if tensor_core_attn:
             tile_q0, tile_qn = K.attn_tiles(seq_counts)
         rope_cs = K.rope_table(pos, hd, cfg.rope_theta) if fuse_qkv else None     # once per pass, shared by the layers
@@ -474,7 +484,15 @@ class TaHEngine:
         s.topi = i32(B, self.topk)
         tl = self._tap_layers()
         # the learned decider's Linear(topk -> H) output is written behind the tapped hidden states
-        s.taps = bf(B, (max(1, len(tl)) + (1 if self._needs_topk_for_decider() else 0)) * H)
+        tap_w = (max(1, len(tl)) + (1 if self._needs_topk_for_decider() else 0)) * H
+        s.tap_buf = None
+        if self.tp is not None and any(0 < li < cfg.num_hidden_layers for li in tl) and B % (16 * self.tp.world_size) == 0:
+            # tensor parallel: the owner kernels of the push path store the tapped residual rows into this
+            # symmetric buffer on every rank (no collective call inside the tick)
+            s.tap_buf = self.tp.alloc_taps(B, tap_w)
+            s.taps = s.tap_buf.tensor
+        else:
+            s.taps = bf(B, tap_w)
         s.z = torch.zeros(B, dtype=torch.float32, device=dev)
         kv = self.kv
         pad = lambda lst: list(lst) + [lst[0]] * (4 - len(lst))
@@ -486,14 +504,16 @@ class TaHEngine:
         s.tensors = tensors
         return s
 
-    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M, push=False, final=False, next_lora=None):
+    def _row_parallel(self, x, w_, a_, b_, t_buf, gate, h, ln_w, xn_out, M, push=False, final=False, next_lora=None,
+                      tap=None):
         """Row-parallel projection + residual + the RMSNorm that follows it.
 
         One GPU: the GEMM epilogue adds the residual in place and a norm kernel follows.  Tensor
         parallel: the GEMM writes this rank's partial result into symmetric memory and the fused
         NVLink kernel does all-reduce + residual + norm + broadcast; ``h`` stays row-sharded.
         ``next_lora = (A, t_buf)`` (one GPU, decode): fuse the LoRA-A product of the consumer of ``xn`` into the
-        norm launch."""
+        norm launch.  ``tap = (tap buffer, column)`` (push path): the owner kernel also broadcasts the updated
+        residual rows into that column of every rank's tap buffer."""
         cfg, tp = self.cfg, self.tp
         lora = a_ is not None and t_buf is not None
         if lora:
@@ -514,7 +534,7 @@ class TaHEngine:
             # the owners; the consumers of xn wait for the broadcast rows themselves (self._xn_wait)
             K.gemm(x, w_, tp_push=desc, **kw)
             self._xn_wait = None if final else tp.wait_desc
-            return tp.push_reduce_norm(M, h, ln_w, cfg.rms_norm_eps, add_residual=True, final_wait=final)
+            return tp.push_reduce_norm(M, h, ln_w, cfg.rms_norm_eps, add_residual=True, final_wait=final, tap=tap)
         self._xn_wait = None
         K.gemm(x, w_, out=tp.partial[:M], **kw)
         return tp.fused_reduce_norm(M, h, ln_w, cfg.rms_norm_eps, add_residual=True)
@@ -529,9 +549,11 @@ class TaHEngine:
         tl = self._tap_layers()
         H = cfg.hidden_size
         nL = len(w.layers)
-        off = os.environ.get("TAH_B200_NO_FUSE", "0")          # "1": both fusions off; "lora" / "qkv": that one off
-        fuse_norm_lora = off not in ("1", "lora") and lora and tp is None   # RMSNorm + LoRA-A of the gated rows in one launch
-        fuse_qkv = off not in ("1", "qkv") and hd == 128         # QK-norm + RoPE + KV write in the QKV GEMM epilogue
+        # Optional fusions of the decode chain.  Off by default: at 256 rows the chain of separate launches measured
+        # 1.7 % faster per tick than the fused kernels (whose extra work runs on four epilogue warps per CTA).
+        fuse = _fusions("")
+        fuse_norm_lora = "lora" in fuse and lora and tp is None  # RMSNorm + LoRA-A of the gated rows in one launch
+        fuse_qkv = "qkv" in fuse and hd == 128                   # QK-norm + RoPE + KV write in the QKV GEMM epilogue
         rope = dict(rope_cs=s.rope_cs, hd=hd, theta=cfg.rope_theta) if fuse_qkv else {}
         if tp is None:
             s.binding.tick_begin(w.embed, s.soft, s.h, **rope)   # the input embedding is the residual stream
@@ -546,10 +568,17 @@ class TaHEngine:
             xn = K.rms_norm(s.h, w.layers[0].ln1, cfg.rms_norm_eps, out=s.xn)
         self._xn_wait = None       # set by _row_parallel when xn is a tensor-parallel broadcast in flight
         push = tp is not None and os.environ.get("TAH_B200_TP_PULL", "0") != "1"
+        kernel_taps = (push and s.tap_buf is not None and tp.push_desc(B) is not None
+                       and os.environ.get("TAH_B200_TP_TAPS", "kernel") != "nccl")   # "nccl": all-gather form (baseline)
         for li, L in enumerate(w.layers):
-            if li in tl:
+            if li in tl and not (kernel_taps and li > 0):
                 j = tl.index(li)
-                s.taps[:, j * H:(j + 1) * H].copy_(s.h if tp is None else tp.gather_rows(s.h, B))
+                if tp is None:
+                    s.taps[:, j * H:(j + 1) * H].copy_(s.h)
+                elif li == 0:
+                    s.taps[:, j * H:(j + 1) * H].copy_(s.x_in)      # the embeddings: every rank has all rows
+                else:
+                    s.taps[:, j * H:(j + 1) * H].copy_(tp.gather_rows(s.h, B))
             if lora and not fuse_norm_lora:
                 K.lora_a_rows(xn, L.a_qkv, s.gate, out=s.t_qkv, tp_wait=self._xn_wait)
             kw = dict(x2=s.t_qkv, w2=L.b_qkv) if lora else {}
@@ -573,8 +602,10 @@ class TaHEngine:
                 K.gemm(xn, L.w_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
             next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
             nxt_lora = (w.layers[li + 1].a_qkv, s.t_qkv) if fuse_norm_lora and li + 1 < nL else None
+            # a tap of the next layer's input is this projection's updated residual stream
+            tap = (s.tap_buf, tl.index(li + 1) * H) if kernel_taps and li + 1 < nL and (li + 1) in tl else None
             xn = self._row_parallel(s.act, L.w_down, L.a_down if lora else None, L.b_down, s.t_down, s.gate, s.h,
-                                    next_ln, s.xn, B, push=push, final=li + 1 == nL, next_lora=nxt_lora)
+                                    next_ln, s.xn, B, push=push, final=li + 1 == nL, next_lora=nxt_lora, tap=tap)
         # xn is now the final-norm output of every row
         if cfg.num_hidden_layers in tl:
             j = tl.index(cfg.num_hidden_layers)

@@ -772,16 +772,19 @@ def fused_reduce_residual_norm(partial_ptrs, xout_ptrs, mc_partial: int, mc_xout
 
 def push_reduce_norm_bcast(slot, cnt, cnt_target, xout_ptrs, mc_xout: int, xflag_ptrs, xtarget, arrive, h, ln_w,
                            M: int, H: int, rank: int, world: int, rpr: int, eps: float, add_residual: bool,
-                           final_wait: bool, grid: int):
+                           final_wait: bool, grid: int, tap_ptrs=None, mc_tap: int = 0, tap_ld: int = 0):
     """Owner side of the push-based row-parallel epilogue: sum the slots that the peers' GEMMs
-    filled, residual add, RMSNorm, broadcast, flag (see ``push_reduce_norm_bcast_kernel``)."""
+    filled, residual add, RMSNorm, broadcast, flag (see ``push_reduce_norm_bcast_kernel``).  ``tap_ptrs``:
+    every rank's address of the tap column that also receives the updated residual rows (row pitch ``tap_ld``)."""
     n = len(xout_ptrs)
     arr = lambda ptrs: (c_void_p * n)(*ptrs)
     _rc(lib().tahb_push_reduce_norm_bcast(_p(slot), _p(cnt), _p(cnt_target), arr(xout_ptrs), c_void_p(mc_xout),
                                           arr(xflag_ptrs), _p(xtarget), _p(arrive), _p(h), _p(ln_w),
                                           _p(status_word(h.device)), c_int(M), c_int(H), c_int(rank), c_int(world),
                                           c_int(rpr), c_float(eps), c_int(1 if add_residual else 0),
-                                          c_int(1 if final_wait else 0), c_int(grid), _stream()),
+                                          c_int(1 if final_wait else 0), c_int(grid), _stream(),
+                                          arr(tap_ptrs) if tap_ptrs else None, c_void_p(mc_tap if tap_ptrs else 0),
+                                          c_ll(tap_ld if tap_ptrs else 0)),
         "tahb_push_reduce_norm_bcast")
 
 

@@ -183,13 +183,154 @@ def bench_rmsnorm(a):
     return {"op": "rms_norm", "M": M, "H": H}, t, 0.0, 2 * M * H * 2
 
 
+# ---------------------------------------------------------------------------------------------
+# multi-GPU cases: launch with  python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1
+#                               -m tah_b200.ops.microbench --op tp_chain | shard_gather
+# Device-timed with CUDA events, the launches of a batch replayed as one CUDA graph per rank where the
+# sequence is capturable, maximum over ranks; rank 0 prints one JSON line.
+# ---------------------------------------------------------------------------------------------
+def _dist_init():
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, dev, dist.get_rank(), dist.get_world_size()
+
+
+def _time_ranks(dist, dev, fn, iters, graph=True):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return round(float(t), 2)
+
+
+def bench_tp_chain(a):
+    """Row-parallel projection -> reduce + residual + RMSNorm -> column-parallel projection of a decode tick
+    (``--m`` rows, hidden ``--k``), as the push chain (GEMM epilogue stores into the owners' slots, owner kernel
+    broadcasts, the next GEMM's producer waits on landing flags), the pull chain (one fused all-reduce kernel
+    between two plain GEMMs) and NCCL's all-reduce alone; plus the vocabulary-parallel top-k merge kernel against
+    its all-gather + sort form.  Microseconds per iteration."""
+    from tah_b200.parallel.tp import TensorParallel
+    dist, dev, rank, world = _dist_init()
+    M, H, Fq = a.m, a.k, a.f
+    iters = a.iters if a.iters > 20 else 100
+    tp = TensorParallel(dist.group.WORLD, dev, H, M, use_multicast=not a.no_multicast)
+    h, ln = _rand(M, H).to(dev), torch.ones(H, device=dev, dtype=torch.bfloat16)
+    x, w = _rand(M, H // world).to(dev), _rand(H, H // world, scale=0.02).to(dev)
+    wq = _rand(Fq // world, H, scale=0.02).to(dev)
+    qkv = torch.empty(M, Fq // world, device=dev, dtype=torch.bfloat16)
+    desc = tp.push_desc(M)
+    tp.partial.normal_()
+    buf = _rand(M, H).to(dev)
+
+    def chain_push():
+        K.gemm(x, w, tp_push=desc)
+        xn = tp.push_reduce_norm(M, h, ln, 1e-6)
+        K.gemm(xn, wq, out=qkv, tp_wait=tp.wait_desc)
+
+    def chain_pull():
+        K.gemm(x, w, out=tp.partial[:M])
+        xn = tp.fused_reduce_norm(M, h, ln, 1e-6)
+        K.gemm(xn, wq, out=qkv)
+
+    res = {"op": "tp_chain", "world": world, "rows": M, "hidden": H, "multicast": bool(tp.mc_partial),
+           "us": {"chain_push": _time_ranks(dist, dev, chain_push, iters),
+                  "chain_pull": _time_ranks(dist, dev, chain_pull, iters),
+                  "fused_reduce_norm_alone": _time_ranks(dist, dev, lambda: tp.fused_reduce_norm(M, h, ln, 1e-6), iters),
+                  "row_gemm_alone": _time_ranks(dist, dev, lambda: K.gemm(x, w, out=tp.partial[:M]), iters),
+                  "col_gemm_alone": _time_ranks(dist, dev, lambda: K.gemm(tp.xout[:M], wq, out=qkv), iters),
+                  "nccl_all_reduce_alone": _time_ranks(dist, dev, lambda: dist.all_reduce(buf), iters)}}
+    k = a.topk
+    val = torch.sort(torch.randn(M, k, device=dev), dim=-1, descending=True).values.contiguous()
+    idx = torch.sort(torch.randint(0, 1 << 14, (M, k), device=dev, dtype=torch.int32), dim=-1).values.contiguous()
+    tp.prepare_merge(M)
+    lo = rank << 14
+    res["us"]["topk_merge_kernel"] = _time_ranks(dist, dev, lambda: tp.merge_topk(val, idx, lo, k), 20)
+    res["us"]["topk_merge_nccl_sort"] = _time_ranks(dist, dev, lambda: tp.merge_topk_nccl(val, idx, lo, k), 20)
+    # bytes that must cross NVLink per rank and chain: partial rows out to the owners + normalised rows out to the peers
+    byts = 2 * M * H * 2 * (world - 1) / world
+    res["nvlink_bytes_per_rank"] = int(byts)
+    res["nvlink_floor_us_at_770GBps"] = round(byts / 770e9 * 1e6, 2)
+    K.check_status()
+    return res, rank
+
+
+def bench_shard_gather(a):
+    """Parameter-sharded linears: the 4 x 7 matrices of seven 1.7B-model layers, every rank holding 1/world of each,
+    gathered by the push kernel one matrix ahead on a side stream while the tcgen05 GEMM of the previous matrix
+    (whose producer waits on the landing flags) runs.  Milliseconds for the 28 GEMMs at ``--m`` tokens."""
+    from tah_b200.parallel.fsdp import ShardedWeightStore
+    dist, dev, rank, world = _dist_init()
+    M = a.m if a.m > 256 else 8192
+    shapes = [(4096, 2048), (2048, 2048), (12288, 2048), (2048, 6144)] * 7
+    full = [_rand(F, Kd, scale=0.02).to(dev) for F, Kd in shapes]
+    xs = {Kd: _rand(M, Kd).to(dev) for Kd in (2048, 6144)}
+    us = lambda f: round(_time_ranks(dist, dev, f, 3, graph=False) / 1e3, 3)
+
+    def plain():
+        for w in full:
+            K.gemm(xs[w.shape[1]], w)
+
+    store = ShardedWeightStore(dist.group.WORLD, dev, full, n_buffers=2, use_multicast=not a.no_multicast)
+
+    def sharded():
+        store.prefetch(0)
+        for i in range(len(full)):
+            if i + 1 < len(full):
+                store.prefetch(i + 1)
+            store.linear(xs[shapes[i][1]], i)
+
+    def gather_only():
+        for i in range(len(full)):
+            store.prefetch(i)
+            store._where.pop(i)
+        torch.cuda.current_stream().wait_stream(store.side)
+
+    byts = sum(F * Kd * 2 for F, Kd in shapes)
+    t_plain, t_sh, t_g = us(plain), us(sharded), us(gather_only)
+    recv = byts * (world - 1) / world
+    res = {"op": "shard_gather", "world": world, "tokens": M, "multicast": bool(store.buf_mc[0]),
+           "ms": {"gemms_on_full_weights": t_plain, "gemms_on_sharded_weights_prefetch_one_ahead": t_sh, "gathers_alone": t_g},
+           "gathered_GB": round(byts / 1e9, 3), "received_GBps_per_rank": round(recv / (t_g * 1e-3) / 1e9, 1),
+           "hidden_fraction_of_gather": round(max(0.0, 1.0 - (t_sh - t_plain) / t_g), 3),
+           "nvlink_floor_ms_at_770GBps": round(recv / 770e9 * 1e3, 3)}
+    K.check_status()
+    return res, rank
+
+
+DIST_OPS = {"tp_chain": bench_tp_chain, "shard_gather": bench_shard_gather}
+
 OPS = {"attn_bwd": bench_attn_bwd, "gemm": bench_gemm, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn, "topk": bench_topk,
        "rmsnorm": bench_rmsnorm}
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--op", choices=sorted(OPS), required=True)
+    ap.add_argument("--op", choices=sorted(list(OPS) + list(DIST_OPS)), required=True)
+    ap.add_argument("--no-multicast", action="store_true", help="multi-GPU cases: plain peer stores instead of multimem")
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--f", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2048)
@@ -214,6 +355,13 @@ def main(argv=None):
     global USE_GRAPH
     USE_GRAPH = a.graph
     torch.manual_seed(0)
+    if a.op in DIST_OPS:
+        res, rank = DIST_OPS[a.op](a)
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        import torch.distributed as dist
+        dist.barrier()
+        os._exit(0)                       # symmetric-memory mappings are alive: skip the process-group teardown
     res, t, flops, byts = OPS[a.op](a)
     bw, fl, src = peaks()
     res.update({"graph": a.graph, "us": round(t * 1e6, 2), "GBps": round(byts / t / 1e9, 1), "TFLOPs": round(flops / t / 1e12, 1),

@@ -16,6 +16,7 @@ framework before each layer.  The trainer of this repository uses :class:`tah_b2
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -210,7 +211,11 @@ class FsdpState:
             del flat
         self.resident = {0: None, 1: None, 2: None}          # buffer -> unit index whose parameters it holds
         self.inflight = {}                                   # unit index -> use number of its pending gather
-        self.side = torch.cuda.Stream(device=device) if self.cuda else None
+        # TAH_B200_FSDP_SERIAL=1 puts the gathers and reduce-scatters on the compute stream (nothing overlaps): the
+        # reference point for the hidden-communication fraction that the training benchmark reports
+        self.serial = os.environ.get("TAH_B200_FSDP_SERIAL", "0") == "1"
+        self.side = None if not self.cuda else (torch.cuda.current_stream(device) if self.serial
+                                                else torch.cuda.Stream(device=device))
         self._hooks = []
         for i, layer in enumerate(layers):
             if i in self.layer_unit:

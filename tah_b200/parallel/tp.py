@@ -130,16 +130,44 @@ class TensorParallel:
         return (self.xflag_local, self.xtarget)
 
     def push_reduce_norm(self, M: int, h: torch.Tensor, ln_w: torch.Tensor, eps: float, add_residual: bool = True,
-                         final_wait: bool = False) -> torch.Tensor:
+                         final_wait: bool = False, tap=None) -> torch.Tensor:
         """Owner side after a ``tp_push`` GEMM on every rank.  The returned ``xout[:M]`` is complete
         on this rank only once the flags in :attr:`wait_desc` have reached their targets: consumers
-        either wait themselves (``tp_wait``) or ask for ``final_wait``."""
+        either wait themselves (``tp_wait``) or ask for ``final_wait``.  ``tap = (buffer from alloc_taps, column
+        offset in elements)``: that column block also receives the updated residual rows of all ranks, landed
+        under the same flags."""
         rpr = M // self.world_size
         grid = max(1, min(MAX_GRID, rpr))
+        kw = {}
+        if tap is not None:
+            tb, col = tap
+            kw = dict(tap_ptrs=[p + 2 * col for p in tb.ptrs], mc_tap=tb.mc + 2 * col if tb.mc else 0,
+                      tap_ld=tb.tensor.shape[1])
         K.push_reduce_norm_bcast(self._slot_flat, self._pushflags[0:1], self._pstate[0:1], self.xout_ptrs,
                                  self.mc_xout, self.xflag_ptrs, self.xtarget, self._pstate[1:2], h, ln_w, M,
-                                 self.hidden, self.rank, self.world_size, rpr, eps, add_residual, final_wait, grid)
+                                 self.hidden, self.rank, self.world_size, rpr, eps, add_residual, final_wait, grid,
+                                 **kw)
         return self.xout[:M]
+
+    def alloc_taps(self, rows: int, width: int):
+        """Symmetric ``[rows, width]`` bf16 buffer for hidden-state taps that the owner kernels fill on every rank
+        (collective: every rank calls it with the same shape; one buffer per shape).  Returns an object with
+        ``tensor`` (this rank's view), ``ptrs`` (every rank's address) and ``mc`` (multicast address or 0)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        from types import SimpleNamespace
+        cache = self.__dict__.setdefault("_tap_bufs", {})
+        if (rows, width) in cache:
+            return cache[(rows, width)]
+        flat = symm_mem.empty(rows * width, dtype=torch.bfloat16, device=self.device)
+        flat.zero_()
+        ht = symm_mem.rendezvous(flat, self.group)
+        mc = int(getattr(ht, "multicast_ptr", 0) or 0)
+        tb = SimpleNamespace(tensor=flat.view(rows, width), ptrs=[int(p) for p in ht.buffer_ptrs],
+                             mc=mc if self.use_multicast and self.mc_xout else 0, handle=ht)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        cache[(rows, width)] = tb
+        return tb
 
     # ---- cold paths: NCCL -----------------------------------------------------------------------
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:

@@ -205,16 +205,16 @@ def test_fast_forward_gives_valid_state_at_a_deeper_context():
         assert len(used) == len(set(used))
 
 
-def test_engine_with_head_dim_128_uses_fused_kernels_and_matches_unfused(monkeypatch):
-    """head_dim 128 takes the fused QKV epilogue (and the fused norm + LoRA-A launch); the unfused chain gives
-    the same tokens."""
+def test_engine_with_head_dim_128_fused_kernels_match_unfused(monkeypatch):
+    """With head_dim 128 the decode tick can take the fused QKV epilogue and the fused norm + LoRA-A launch
+    (``TAH_B200_FUSE=1``); the chain of separate launches gives the same tokens."""
     from tah_b200.engine import TaHEngine
     B, T, n_new = 4, 16, 20
     model = tiny_tah(max_iter=2, dtype=torch.bfloat16, head_dim=128, num_attention_heads=2, num_key_value_heads=1).cuda().eval()
     ids = torch.randint(0, 1024, (B, T), generator=torch.Generator().manual_seed(2)).cuda()
     outs = []
-    for no_fuse in ("0", "1"):
-        monkeypatch.setenv("TAH_B200_NO_FUSE", no_fuse)
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("TAH_B200_FUSE", fuse)
         eng = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, use_cuda_graph=True, deep_fraction=1.0)
         eng.hard_override = eng.make_bernoulli_override(B, (0.3,), seed=5)
         res = eng.generate(ids, None, max_new_tokens=n_new, do_sample=False)

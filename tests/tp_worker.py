@@ -241,6 +241,36 @@ def main():
     ok = ok and good
     if rank == 0:
         print(f"engine TP{world} vs 1 GPU: token agreement {agree:.2f}, first-4 agreement {first_tok:.2f} {'ok' if good else 'BAD'}")
+    # ---- learned decider under TP: hidden-state taps broadcast by the owner kernels == the all-gather form ----
+    H = 256
+    dkw = dict(topk=100, hidden_states_size=H, hidden_states_layer_nums=[0, 1, 3, 4], hidden_dims=[128, 128],
+               expansion_factor=2, dropout_rate=0.0, threshold=0.5)
+    mlp_model = tiny_tah(max_iter=2, dtype=torch.bfloat16, decider="MLPIterDecider", decider_kwargs=dkw, **over).to(dev).eval()
+    with torch.no_grad():
+        for n_, p_ in mlp_model.iter_decider.named_parameters():
+            if n_.endswith("bias"):
+                p_.normal_(std=0.2)
+    runs = []
+    for mode in ("kernel", "nccl"):
+        os.environ["TAH_B200_TP_TAPS"] = mode
+        e2 = TaHEngine(mlp_model, max_rows=B, max_seq_len=T + n_new + 2, deep_fraction=1.0, tp=tp)
+        calls = [0]
+        orig = tp.gather_rows
+        def counting(h, M, _orig=orig, _c=calls):
+            _c[0] += 1
+            return _orig(h, M)
+        tp.gather_rows = counting
+        r2 = e2.generate(ids, None, max_new_tokens=n_new, do_sample=False)
+        tp.gather_rows = orig
+        runs.append((torch.tensor(r2.tokens), torch.tensor(r2.iter_counts), calls[0]))
+    os.environ.pop("TAH_B200_TP_TAPS", None)
+    same_tok = bool((runs[0][0] == runs[1][0]).all())
+    hard = float(runs[0][1].mean()) - 1.0            # mean extra passes per emitted token
+    good = same_tok and runs[0][2] < runs[1][2] and bool((runs[0][1] == runs[1][1]).all())
+    ok = ok and good
+    if rank == 0:
+        print(f"MLP decider TP{world}: kernel taps == all-gather taps tokens {same_tok}; gather_rows calls {runs[0][2]} vs {runs[1][2]}; "
+              f"extra passes per token {hard:.2f} {'ok' if good else 'BAD'}")
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     passed = int(flag.item()) == 1
