@@ -72,128 +72,154 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const __nv_bfloat16* __res
 // RMSNorm fused with the LoRA-A product of the rows that are at depth >= 1 (decode tick):
 //   y[r] = w * bf16(x[r] * rstd)                     for every row
 //   T[r] = gate[r] ? y[r] A^T : 0                    (A: [R, H], T: [M, ldt])
-// Grid (rows, 1 + NS), 256 threads.  CTA (r, 0) normalises row r, stores y and, when the row is gated
-// off, clears T[r].  CTAs (r, 1 + s) exist for the LoRA-A product: for a gated row each of the NS
-// slices normalises the row again into shared memory (4 KB from L2) and its eight warps compute
-// R / NS of the outputs, three at a time with all loads of a step issued before the arithmetic, so
-// that the product is spread over NS x 8 warps instead of running in one CTA; for the other rows
-// they return at once.  Same summation order per output as lora_a_rows_kernel.  Saves the separate
-// LoRA-A launch in front of the QKV and gate/up projections.
+// One-dimensional grid of M + NORM_LORA_SLOTS * NORM_LORA_SLICES CTAs of 256 threads.  CTA b < M normalises
+// row b, stores y and, when the row is gated off, clears T[b].  The others exist for the LoRA-A product:
+// CTA (slot, slice) finds the slot-th gated row (then the (slot + SLOTS)-th, ...) by counting the gate vector
+// (M <= 1024), normalises that row again into shared memory and its eight warps compute outputs
+// slice * 8 + warp, + 8 * SLICES, ... with all loads of a dot product issued before the arithmetic.  The body
+// is kept small on purpose: a tick runs it once per CTA between other kernels, from a cold instruction cache.
+// Same summation order per output as lora_a_rows_kernel.
 // ---------------------------------------------------------------------------------------------
 constexpr int NORM_LORA_SLICES = 8;
+constexpr int NORM_LORA_SLOTS = 32;
 
 __global__ void __launch_bounds__(256) rmsnorm_lora_kernel(const __nv_bfloat16* __restrict__ x,
                                                            const __nv_bfloat16* __restrict__ w,
-                                                           __nv_bfloat16* __restrict__ y, int H, long long ldx,
+                                                           __nv_bfloat16* __restrict__ y, int M, int H, long long ldx,
                                                            long long ldy, float eps, const int* __restrict__ gate,
                                                            const __nv_bfloat16* __restrict__ A,
                                                            __nv_bfloat16* __restrict__ T, int R, long long ldt) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ uint4 srow[];            // H / 8 vectors: the normalised row (LoRA slices only)
+  extern __shared__ uint4 srow[];            // H / 8 vectors: the normalised row (LoRA CTAs only)
   __shared__ float red[8];
-  const int row = blockIdx.x;
-  const int slice = (int)blockIdx.y - 1;     // -1: the norm CTA
+  __shared__ int s_cnt[8];
+  __shared__ int s_row;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool gated = gate != nullptr && gate[row] != 0;
-  if (slice >= 0 && !gated) return;
+  const bool norm_cta = (int)blockIdx.x < M;
+  const int lid = (int)blockIdx.x - M;
+  const int slice = lid % NORM_LORA_SLICES;
+  int want = lid / NORM_LORA_SLICES;         // index of this CTA's gated row among the gated rows
   const int nvec = H / 8;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
-  constexpr int VPT = 4;                     // H <= 256 * 8 * 4 = 8192
-  uint4 v[VPT];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int idx = tid + i * 256;
-    if (idx < nvec) {
-      v[i] = xr[idx];
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(h[j]);
-        ss += f.x * f.x + f.y * f.y;
-      }
-    }
-  }
-  ss = warp_sum(ss);
-  if (lane == 0) red[warp] = ss;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) tot += red[k];   // fixed order: every CTA of a row gets the same rstd
-  const float rstd = rsqrtf(tot / (float)H + eps);
   const uint4* wr = reinterpret_cast<const uint4*>(w);
-  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+  for (;;) {
+    int row;
+    if (norm_cta) {
+      row = blockIdx.x;
+    } else {
+      // thread t looks at rows 4t .. 4t + 3; the want-th set gate picks the row
+      int g[4], cnt = 0;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int idx = tid + i * 256;
-    if (idx < nvec) {
-      uint4 wv = wr[idx];
-      uint4 o;
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
-      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
-      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(h[j]);
-        float2 g = __bfloat1622float2(wh[j]);
-        oh[j] = __floats2bfloat162_rn(g.x * bf16_round(f.x * rstd), g.y * bf16_round(f.y * rstd));
+      for (int i = 0; i < 4; ++i) {
+        const int r = tid * 4 + i;
+        g[i] = (r < M && gate[r] != 0) ? 1 : 0;
+        cnt += g[i];
       }
-      if (slice < 0) yr[idx] = o;
-      else srow[idx] = o;
+      int incl = cnt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (tid == 0) s_row = -1;
+      if (lane == 31) s_cnt[warp] = incl;
+      __syncthreads();
+      int base = 0;
+      for (int k = 0; k < warp; ++k) base += s_cnt[k];
+      int before = base + incl - cnt;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (g[i] && before == want) s_row = tid * 4 + i;
+        before += g[i];
+      }
+      __syncthreads();
+      row = s_row;
+      if (row < 0) return;
     }
-  }
-  __nv_bfloat16* out = T + (size_t)row * ldt;
-  if (slice < 0) {
-    if (!gated)
-      for (int j = tid; j < R; j += 256) out[j] = __float2bfloat16_rn(0.f);
-    return;
-  }
-  __syncthreads();
-  // outputs [j0, j1) of this slice, three per warp and step
-  const int per = (R + NORM_LORA_SLICES - 1) / NORM_LORA_SLICES;
-  const int j0 = slice * per, j1 = min(R, j0 + per);
-  for (int j = j0 + warp * 3; j < j1; j += 24) {
-    const int ja = j, jb = min(j + 1, j1 - 1), jc = min(j + 2, j1 - 1);
-    const uint4* a0 = reinterpret_cast<const uint4*>(A + (size_t)ja * H);
-    const uint4* a1 = reinterpret_cast<const uint4*>(A + (size_t)jb * H);
-    const uint4* a2 = reinterpret_cast<const uint4*>(A + (size_t)jc * H);
-    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
-    for (int i0 = lane; i0 < nvec; i0 += 128) {
-      uint4 av0[4], av1[4], av2[4];
+    // ---- normalise the row -------------------------------------------------------------
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+    constexpr int VPT = 4;                   // H <= 256 * 8 * 4 = 8192
+    uint4 v[VPT];
+    float ss = 0.f;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {          // 12 independent 16-byte loads before any arithmetic
-        const int i = i0 + u * 32;
-        if (i < nvec) { av0[u] = a0[i]; av1[u] = a1[i]; av2[u] = a2[i]; }
-      }
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = tid + i * 256;
+      if (idx < nvec) {
+        v[i] = xr[idx];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * 32;
-        if (i < nvec) {
-          const uint4 xv = srow[i];
-          const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
-          const __nv_bfloat162* ah0 = reinterpret_cast<const __nv_bfloat162*>(&av0[u]);
-          const __nv_bfloat162* ah1 = reinterpret_cast<const __nv_bfloat162*>(&av1[u]);
-          const __nv_bfloat162* ah2 = reinterpret_cast<const __nv_bfloat162*>(&av2[u]);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 a = __bfloat1622float2(xh[q]);
-            const float2 b0 = __bfloat1622float2(ah0[q]), b1 = __bfloat1622float2(ah1[q]), b2 = __bfloat1622float2(ah2[q]);
-            acc0 += a.x * b0.x + a.y * b0.y;
-            acc1 += a.x * b1.x + a.y * b1.y;
-            acc2 += a.x * b2.x + a.y * b2.y;
-          }
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(h[j]);
+          ss += f.x * f.x + f.y * f.y;
         }
       }
     }
-    acc0 = warp_sum(acc0);
-    acc1 = warp_sum(acc1);
-    acc2 = warp_sum(acc2);
-    if (lane == 0) {
-      out[ja] = __float2bfloat16_rn(acc0);
-      if (j + 1 < j1) out[jb] = __float2bfloat16_rn(acc1);
-      if (j + 2 < j1) out[jc] = __float2bfloat16_rn(acc2);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tot += red[k];   // fixed order: every CTA of a row gets the same rstd
+    const float rstd = rsqrtf(tot / (float)H + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = tid + i * 256;
+      if (idx < nvec) {
+        uint4 wv = wr[idx];
+        uint4 o;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(h[j]);
+          float2 g = __bfloat1622float2(wh[j]);
+          oh[j] = __floats2bfloat162_rn(g.x * bf16_round(f.x * rstd), g.y * bf16_round(f.y * rstd));
+        }
+        if (norm_cta) yr[idx] = o;
+        else srow[idx] = o;
+      }
     }
+    __nv_bfloat16* out = T + (size_t)row * ldt;
+    if (norm_cta) {
+      if (gate == nullptr || gate[row] == 0)
+        for (int j = tid; j < R; j += 256) out[j] = __float2bfloat16_rn(0.f);
+      return;
+    }
+    __syncthreads();
+    // ---- LoRA-A outputs of this slice: one per warp and step ---------------------------
+    for (int j = slice * 8 + warp; j < R; j += 8 * NORM_LORA_SLICES) {
+      const uint4* a0 = reinterpret_cast<const uint4*>(A + (size_t)j * H);
+      float acc = 0.f;
+      for (int i0 = lane; i0 < nvec; i0 += 256) {
+        uint4 av[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {          // eight independent 16-byte loads before any arithmetic
+          const int i = i0 + u * 32;
+          av[u] = i < nvec ? a0[i] : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * 32;
+          if (i < nvec) {
+            const uint4 xv = srow[i];
+            const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av[u]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 a = __bfloat1622float2(xh[q]);
+              const float2 b = __bfloat1622float2(ah[q]);
+              acc += a.x * b.x + a.y * b.y;
+            }
+          }
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) out[j] = __float2bfloat16_rn(acc);
+    }
+    want += NORM_LORA_SLOTS;                 // more gated rows than slots: take the next one
+    __syncthreads();
   }
 }
 
@@ -679,10 +705,11 @@ extern "C" int tahb_rmsnorm_lora(const void* x, const void* w, void* y, int M, i
                                  float eps, const int* gate, const void* A, void* T, int R, long long ldt,
                                  cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (H % 8 || H > 8192 || R <= 0) return -1;
-  cudaError_t e = launch_chain(rmsnorm_lora_kernel, dim3(M, 1 + NORM_LORA_SLICES), dim3(256), (size_t)H * 2, stream,
+  if (H % 8 || H > 8192 || R <= 0 || M > 1024) return -1;
+  const int lora_ctas = gate != nullptr ? NORM_LORA_SLOTS * NORM_LORA_SLICES : 0;
+  cudaError_t e = launch_chain(rmsnorm_lora_kernel, dim3(M + lora_ctas), dim3(256), (size_t)H * 2, stream,
                                reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
-                               reinterpret_cast<__nv_bfloat16*>(y), H, ldx, ldy, eps, gate,
+                               reinterpret_cast<__nv_bfloat16*>(y), M, H, ldx, ldy, eps, gate,
                                reinterpret_cast<const __nv_bfloat16*>(A), reinterpret_cast<__nv_bfloat16*>(T), R, ldt);
   return e == cudaSuccess ? 0 : -3;
 }

@@ -46,9 +46,6 @@ struct GemmParams {
   int kb_ext;   // R / 64
   int splits;   // cluster size along z (1 = no split-K)
   int tma_out;  // 1: stage the output tile in shared memory and write it with a TMA store
-  int pair;     // DUAL kernels only. 0: SwiGLU of the two accumulators.  1: the accumulators are two plain
-                // output tiles (features f0.. and up_off + f0..) that share the CTA's activation tile, which
-                // halves the activation bytes a CTA pulls per unit of work (requires the staged/TMA output path)
   int act;      // epilogue activation on the (non-dual) output: 0 none, 1 GELU (erf form) of the bf16-rounded value
   // Operand majors (backward GEMMs read their operands transposed, straight from the row-major tensors):
   //   a_mn: the 128-row operand is stored [reduction, feature] (feature contiguous): dgrad reads W[F, K] as
@@ -122,8 +119,7 @@ __device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, flo
     y = bf16_round(silu(bf16_round(a))) * bf16_round(u);
   } else {
     y = a;
-    if (p.act == 1) y = gelu_erf(bf16_round(a));
-    if (p.residual != nullptr) y = bf16_round(y) + __bfloat162float(p.residual[(size_t)t * p.ld_res + f]);
+    if (p.residual != nullptr) y = bf16_round(a) + __bfloat162float(p.residual[(size_t)t * p.ld_res + f]);
   }
   p.out[(size_t)t * p.ld_out + f] = __float2bfloat16_rn(y);
 }
@@ -131,22 +127,33 @@ __device__ __forceinline__ void store_one(const GemmParams& p, int t, int f, flo
 // Epilogue value into the shared staging tile; with `add_res` the slot already holds the residual
 // element (brought in by a TMA load).
 template <bool DUAL>
-__device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u, bool add_res, int act = 0) {
+__device__ __forceinline__ void stage_one(__nv_bfloat16* slot, float a, float u, bool add_res) {
   float y;
   if constexpr (DUAL) {
     y = bf16_round(silu(bf16_round(a))) * bf16_round(u);
   } else {
     y = a;
-    if (act == 1) y = gelu_erf(bf16_round(a));
-    if (add_res) y = bf16_round(y) + __bfloat162float(*slot);
+    if (add_res) y = bf16_round(a) + __bfloat162float(*slot);
   }
   *slot = __float2bfloat16_rn(y);
+}
+
+// Activation pass over a staged tile (n_tok x 128 bf16 in shared memory), run by the 128 epilogue threads after
+// they have all staged their rows: GELU (erf form) of the bf16-rounded outputs.  Kept out of the staging loops,
+// whose unrolled bodies every GEMM executes.
+__device__ __noinline__ void gelu_tile(__nv_bfloat16* stg, int n_tok) {
+  const int e = threadIdx.x - 64;
+  __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(stg);
+  for (int i = e; i < n_tok * 64; i += 128) {
+    const float2 f = __bfloat1622float2(v[i]);
+    v[i] = __floats2bfloat162_rn(gelu_erf(f.x), gelu_erf(f.y));
+  }
 }
 
 // Copy `n_tok` staged rows ([token][128 features] bf16 in shared memory, tokens ta..ta+n_tok) into the
 // owners' slot buffers with 16-byte peer stores (128 epilogue threads: 16 lanes per 256-byte row),
 // then fence and advance each touched owner's arrival counter by the rows it received.
-__device__ __forceinline__ void push_rows(const GemmParams& p, const __nv_bfloat16* stg, int ta, int n_tok, int f0) {
+__device__ __noinline__ void push_rows(const GemmParams& p, const __nv_bfloat16* stg, int ta, int n_tok, int f0) {
   const int e = threadIdx.x - 64;                 // 0..127
   const int sub = e & 15, r0 = e >> 4;            // 16-byte piece of the row, first row of this thread
   const int H = p.push_ld;
@@ -175,7 +182,11 @@ __device__ __forceinline__ void push_rows(const GemmParams& p, const __nv_bfloat
 // one per token); then the four warps take the tokens round robin; a lane owns four consecutive dims of the
 // head, so the head's sum of squares is one warp reduction and the rotate-half partner (dim +- 64) sits in
 // lane +- 16.  Same arithmetic and rounding as qk_norm_rope_kv_kernel.  `aux` needs n_tok * 264 bytes.
-__device__ __forceinline__ void qkv_epilogue(const GemmParams& p, const __nv_bfloat16* stg, uint8_t* aux, int ta,
+#ifndef TAHB_QKV_U
+#define TAHB_QKV_U 1      // tokens per warp and step: 1 measured fastest inside a tick (4 unrolled chains are faster in isolation
+                          // but four times the straight-line code, fetched cold by every CTA)
+#endif
+__device__ __noinline__ void qkv_epilogue(const GemmParams& p, const __nv_bfloat16* stg, uint8_t* aux, int ta,
                                              int n_tok, int f0) {
   const int e = threadIdx.x - 64;                 // 0..127
   const int w4 = e >> 5, lane = e & 31;
@@ -224,7 +235,7 @@ __device__ __forceinline__ void qkv_epilogue(const GemmParams& p, const __nv_bfl
   const __nv_bfloat162 sgn = upper ? __floats2bfloat162_rn(1.f, 1.f) : __floats2bfloat162_rn(-1.f, -1.f);
   // Four tokens per warp and step, written phase by phase: the latency of a token's dependent chain (reduction,
   // shuffles) is hidden by the other three tokens' chains.
-  constexpr int U = 4;
+  constexpr int U = TAHB_QKV_U;
   for (int r0 = w4; r0 < n_tok; r0 += 4 * U) {
     int rr[U];
     bool live[U];
@@ -327,7 +338,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_x2,
                const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
-               const GemmParams p) {
+               const __grid_constant__ GemmParams p) {
   using C = GemmCfg<BN, DUAL>;
   pdl_launch_dependents();      // the next kernel of the chain may be scheduled behind this one
   extern __shared__ uint8_t smem_raw[];
@@ -412,6 +423,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(128, BN) | (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
+      const uint32_t a_step = (p.a_mn ? 2048u : 32u) >> 4, b_step = (p.b_mn ? 2048u : 32u) >> 4;
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % C::NS;
         const uint32_t ph = (i / C::NS) & 1;
@@ -419,12 +431,15 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
         const uint32_t b_addr = a_addr + C::W_BYTES;
+        // K-major: 16 reduction elements = 32 bytes along the swizzled row; MN-major: 16 reduction rows of
+        // 128 bytes = 2048 bytes, the next 64 features / columns 8192 bytes further.  The start address sits in
+        // the low bits of the descriptor in 16-byte units, so a k step is an addition.
+        const uint64_t da0 = p.a_mn ? umma_desc_mn_sw128(a_addr, 8192) : umma_desc_sw128(a_addr);
+        const uint64_t db0 = p.b_mn ? umma_desc_mn_sw128(b_addr, 8192) : umma_desc_sw128(b_addr);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          // K-major: 16 reduction elements = 32 bytes along the swizzled row; MN-major: 16 reduction rows of
-          // 128 bytes = 2048 bytes, the next 64 features / columns 8192 bytes further
-          const uint64_t db = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, 8192) : umma_desc_sw128(b_addr + k * 32);
-          const uint64_t da = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, 8192) : umma_desc_sw128(a_addr + k * 32);
+          const uint64_t da = da0 + (uint64_t)(k * a_step);
+          const uint64_t db = db0 + (uint64_t)(k * b_step);
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
           umma_bf16(tmem_base, da, db, idesc, acc);
           if constexpr (DUAL) umma_bf16(tmem_base + BN, umma_desc_sw128(a_addr + C::W_TILE + k * 32), db, idesc, acc);
@@ -444,14 +459,11 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     tc_fence_after();
     if (S == 1) {
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [BN tokens][128 features]
-      __nv_bfloat16* stg1 = stg + BN * 128;                            // second tile of a pair
-      const bool pair = DUAL && p.pair != 0;
       const bool res_tma = p.tma_out && p.residual != nullptr;
       if (res_tma) {
         if (threadIdx.x == 64) {
-          mbar_expect_tx(res_bar, BN * 256 * (pair ? 2 : 1));
+          mbar_expect_tx(res_bar, BN * 256);
           tma_load_2d(stg, &tm_res, f0, t0, res_bar);
-          if (pair) tma_load_2d(stg1, &tm_res, p.up_off + f0, t0, res_bar);
         }
         mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       }
@@ -462,16 +474,10 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tmem_ld_chunk<C::CHUNK>(trow + c0, a);
         if constexpr (DUAL) tmem_ld_chunk<C::CHUNK>(trow + BN + c0, u);
         tmem_ld_wait();
-        if (pair) {
-#pragma unroll
-          for (int j = 0; j < C::CHUNK; ++j) {
-            stage_one<false>(stg + (c0 + j) * 128 + row, a[j], 0.f, res_tma);
-            stage_one<false>(stg1 + (c0 + j) * 128 + row, DUAL ? u[j] : 0.f, 0.f, res_tma);
-          }
-        } else if (p.tma_out) {
+        if (p.tma_out) {
 #pragma unroll
           for (int j = 0; j < C::CHUNK; ++j)
-            stage_one<DUAL>(stg + (c0 + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma, p.act);
+            stage_one<DUAL>(stg + (c0 + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
         } else if (f < p.F) {
 #pragma unroll
           for (int j = 0; j < C::CHUNK; ++j) {
@@ -486,13 +492,15 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       } else if (p.push_world > 0) {
         named_bar_sync(1, 128);
         push_rows(p, stg, t0, BN, f0);
-        if (pair) push_rows(p, stg1, t0, BN, p.up_off + f0);
       } else if (p.tma_out) {
+        if (p.act == 1) {
+          named_bar_sync(1, 128);
+          gelu_tile(stg, BN);
+        }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
           tma_store_2d(&tm_out, stg, f0, t0);
-          if (pair) tma_store_2d(&tm_out, stg1, p.up_off + f0, t0);
           tma_store_commit();
           tma_store_wait_read();
         }
@@ -550,14 +558,11 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const float* red = reinterpret_cast<const float*>(smem);
       // output staging tile [per tokens][128 features] lives behind the received blocks
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + split_stage_offset(S, C::NACC * per));
-      __nv_bfloat16* stg1 = stg + per * 128;
-      const bool pair = DUAL && p.pair != 0;
       const bool res_tma = p.tma_out && p.residual != nullptr;
       if (res_tma) {
         if (threadIdx.x == 64) {
-          mbar_expect_tx(res_bar, per * 256 * (pair ? 2 : 1));
+          mbar_expect_tx(res_bar, per * 256);
           tma_load_2d(stg, &tm_res, f0, t0 + rank * per, res_bar);
-          if (pair) tma_load_2d(stg1, &tm_res, p.up_off + f0, t0 + rank * per, res_bar);
         }
         mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       }
@@ -578,15 +583,9 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             for (int j = 0; j < 16; ++j) u[j] += src[(per + j) * 128];
           }
         }
-        if (pair) {
+        if (p.tma_out) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            stage_one<false>(stg + (c + j) * 128 + row, a[j], 0.f, res_tma);
-            stage_one<false>(stg1 + (c + j) * 128 + row, DUAL ? u[j] : 0.f, 0.f, res_tma);
-          }
-        } else if (p.tma_out) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) stage_one<DUAL>(stg + (c + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma, p.act);
+          for (int j = 0; j < 16; ++j) stage_one<DUAL>(stg + (c + j) * 128 + row, a[j], DUAL ? u[j] : 0.f, res_tma);
         } else if (f < p.F) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -601,13 +600,15 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       } else if (p.push_world > 0) {
         named_bar_sync(1, 128);
         push_rows(p, stg, t0 + rank * per, per, f0);
-        if (pair) push_rows(p, stg1, t0 + rank * per, per, p.up_off + f0);
       } else if (p.tma_out) {
+        if (p.act == 1) {
+          named_bar_sync(1, 128);
+          gelu_tile(stg, per);
+        }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
           tma_store_2d(&tm_out, stg, f0, t0 + rank * per);
-          if (pair) tma_store_2d(&tm_out, stg1, p.up_off + f0, t0 + rank * per);
           tma_store_commit();
           tma_store_wait_read();
         }
@@ -688,7 +689,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
   }
   if (p.splits > 1) {
     const int per = BN / p.splits;
-    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 * (p.pair ? 2 : 1) +
+    if (per % 16 || (size_t)split_stage_offset(p.splits, C::NACC * per) + (size_t)per * 256 +
                             (p.qkv_on ? (size_t)per * 264 : 0) >
                         (size_t)C::NS * C::STAGE_BYTES)
       return -11;
@@ -754,23 +755,17 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
                      int a_mn = 0, int b_mn = 0, int k_rows = 0) {
   if (M <= 0 || F <= 0) return 0;
   // transposed operands: W is then [K, F] (ldw = its row pitch), X is [K, M]; no LoRA extension, no dual
-  if ((a_mn || b_mn) && (dual == 1 || dual == 2 || R > 0 || qkv != nullptr || tp.push_world > 0)) return -27;
+  if ((a_mn || b_mn) && (dual == 1 || R > 0 || qkv != nullptr || tp.push_world > 0)) return -27;
   if (a_mn && F % 128) return -27;
   const bool push = tp.push_world > 0;
   if (qkv != nullptr && (dual != 0 || residual != nullptr || push || F != (qkv->nq + 2 * qkv->nkv) * 128 ||
                          qkv->n_caches > 4 || qkv->q_out == nullptr || qkv->pos == nullptr))
     return -26;
-  // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 2 = pair: two plain
-  // output tiles per CTA (features f and F/2 + f) sharing the activation tile, 3 = one accumulator + GELU
-  const bool pair = dual == 2;
-  const int act = dual == 3 ? 1 : 0;          // dual == 3: one accumulator with a GELU epilogue
+  // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 3 = one accumulator + GELU
+  if (dual == 2) return -24;
+  const int act = dual == 3 ? 1 : 0;
   if (dual == 3) dual = 0;
   const int F_full = F;
-  if (pair) {
-    if (F % 256) return -24;
-    F = F / 2;
-    up_off = F;
-  }
   if (push && (dual == 1 || residual != nullptr || F_full % 128 || tp.push_world > GEMM_MAX_RANKS || tp.push_rpr <= 0))
     return -23;
   if (K % 64 || R % 64 || K <= 0) return -20;
@@ -797,7 +792,7 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   CUtensorMap mo, mr;
   int tma_out = !push && qkv == nullptr && make_map(&mo, out, M, F_full, ldo, bn / splits, false) == 0;
   if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F_full, ldr, bn / splits, false) == 0;
-  if (pair && !tma_out && !push) return -25;     // the pair epilogue only exists on the staged path
+  if (act && (!tma_out || residual != nullptr)) return -28;   // the GELU pass runs on the staged tile, before no residual
   if (!tma_out) mo = mw;
   if (!tma_out || residual == nullptr) mr = mo;
   GemmParams p;
@@ -824,7 +819,6 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
     p.cache_sel = p.slot = p.pos = nullptr;
     p.rope_cs = nullptr;
   }
-  p.pair = pair ? 1 : 0;
   p.act = act;
   p.a_mn = a_mn;
   p.b_mn = b_mn;

@@ -16,7 +16,9 @@ from typing import List, Optional, Sequence
 import torch
 
 _LIB = None
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libtahb200.so")
+# TAH_B200_LIB: load another build of the library (A/B timing of kernel changes)
+_LIB_PATH = os.environ.get("TAH_B200_LIB") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                                           "lib", "libtahb200.so")
 
 c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
@@ -96,7 +98,7 @@ def _check_bf16_2d(t: torch.Tensor, name: str):
 SM_COUNT = 148
 
 
-def _fits(bn: int, s: int, nacc: int, pair: bool = False) -> bool:
+def _fits(bn: int, s: int, nacc: int) -> bool:
     stage = 16384 * nacc + bn * 128
     ns = min(8, (196 * 1024) // stage)
     if s == 1:
@@ -105,10 +107,10 @@ def _fits(bn: int, s: int, nacc: int, pair: bool = False) -> bool:
     if bn % s or per % 16:
         return False
     red = ((s - 1) * 128 * nacc * per * 4 + 1023) // 1024 * 1024
-    return red + per * 256 * (2 if pair else 1) <= ns * stage
+    return red + per * 256 <= ns * stage
 
 
-def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False, pair: bool = False):
+def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
     """Pick the token-tile width and the split-K cluster size with a small cost model.
 
     Measured on B200: a k-block (64 of K) costs about 0.3 us of load latency per CTA unless the
@@ -122,7 +124,7 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False, pair: bool
     best = None
     for bn in cands:
         for s in (1, 2, 4):
-            if s > 1 and (kb // s < 2 or not _fits(bn, s, nacc, pair)):
+            if s > 1 and (kb // s < 2 or not _fits(bn, s, nacc)):
                 continue
             ctas = ((F + 127) // 128) * ((M + bn - 1) // bn) * s
             waves = (ctas + SM_COUNT - 1) // SM_COUNT
@@ -136,11 +138,6 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False, pair: bool
             if best is None or t < best[0] - 1e-9:
                 best = (t, bn, s)
     return best[1], best[2]
-
-
-# measured on B200 at 256 rows: pairing halves the CTA count and loses more than the saved activation
-# traffic gains (e.g. 4096x2048: 14.1 us paired vs 12.1 us), so it is opt-in
-PAIR_AUTO = os.environ.get("TAH_B200_GEMM_PAIR", "0") == "1"
 
 
 def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
@@ -183,15 +180,11 @@ def wait_flags(flags: torch.Tensor, targets: torch.Tensor) -> None:
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
-         bn: int = 0, tp_push=None, tp_wait=None, pair: Optional[bool] = None, gelu: bool = False) -> torch.Tensor:
+         bn: int = 0, tp_push=None, tp_wait=None, gelu: bool = False) -> torch.Tensor:
     """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
     weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
 
-    ``gelu``: the epilogue applies the erf GELU to the bf16-rounded output (before an optional residual add).
-
-    ``pair``: every CTA computes two 128-feature output tiles (features ``f`` and ``F/2 + f``) from one
-    activation tile, which cuts the activation bytes pulled per output (off unless asked for: it was not
-    faster at decode sizes on B200).
+    ``gelu``: the epilogue applies the erf GELU to the bf16-rounded output (not together with ``residual``).
 
     Tensor parallel (see :class:`tah_b200.parallel.tp.TensorParallel`): ``tp_push =
     (slot_ptrs, cnt_ptrs, rank, rows_per_rank)`` replaces the output by peer stores of the tile
@@ -219,18 +212,15 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         _check_bf16_2d(out, "out")
     if residual is not None:
         _check_bf16_2d(residual, "residual")
-    if pair is None:
-        pair = PAIR_AUTO and not swiglu and M <= 256 and F % 256 == 0 and F >= 1024 and F <= 16384
-    pair = bool(pair) and not swiglu and F % 256 == 0
     if splits is None and bn == 0:
-        bn, splits = plan_gemm(M, F // 2, K, R, True, pair=True) if pair else plan_gemm(M, F, K, R, swiglu)
+        bn, splits = plan_gemm(M, F, K, R, swiglu)
     elif splits is None:
         splits = 1
     args = (_p(w), _p(x), _p(out), _p(residual), _p(w2), _p(x2), c_int(M), c_int(F), c_int(K), c_int(R),
             c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
             c_ll(residual.stride(0) if residual is not None else 0),
             c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
-            c_int(1 if swiglu else 2 if pair else 3 if gelu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+            c_int(1 if swiglu else 3 if gelu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
             _p(status_word(x.device)), _stream())
     if tp_push is None and tp_wait is None:
         rc = lib().tahb_gemm(*args)

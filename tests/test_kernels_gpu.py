@@ -28,15 +28,15 @@ GEMM_SHAPES = [(64, 256, 256), (16, 128, 64), (1, 128, 128), (100, 384, 512), (2
 @pytest.mark.parametrize("M,F,K,R", [(256, 4096, 2048, 192), (64, 2048, 6144, 64), (100, 512, 256, 0), (256, 2048, 1024, 64)])
 @pytest.mark.parametrize("bn,splits", [(0, None), (128, 1), (128, 2), (64, 4)])
 @pytest.mark.parametrize("residual", [False, True])
-def test_gemm_pair_mode(M, F, K, R, bn, splits, residual):
-    """Two output tiles per CTA (pair mode) with LoRA K-extension, residual and split-K against fp32."""
+def test_gemm_forced_plans(M, F, K, R, bn, splits, residual):
+    """Forced token-tile widths and split-K cluster sizes with LoRA K-extension and residual against fp32."""
     Kc = _cuda()
     x, w = _rand(M, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
     x2 = _rand(M, R, seed=3) if R else None
     w2 = _rand(F, R, scale=0.05, seed=4) if R else None
     res = _rand(M, F, seed=5) if residual else None
     kw = dict(bn=bn, splits=splits) if bn else {}
-    out = Kc.gemm(x, w, x2=x2, w2=w2, residual=res, pair=True, **kw)
+    out = Kc.gemm(x, w, x2=x2, w2=w2, residual=res, **kw)
     Kc.check_status()
     ref = x.float() @ w.float().t()
     if R:
