@@ -569,10 +569,11 @@ __global__ void __launch_bounds__(256) shard_gather_push_kernel(const ShardGathe
 // Every rank holds, per row, a sorted (value desc, index asc) list of k candidates over its
 // vocabulary shard.  One launch per rank, one CTA per row:
 //   1. CTA r stores its row's k (value, global index) pairs into slot [epoch parity][rank][r] of every
-//      rank's symmetric exchange buffer (plain peer stores over NVLink), fences, and adds 1 to word r of
-//      every rank's arrival array;
-//   2. it waits (bounded) until its own arrival word r has reached world * epoch, i.e. CTA r of every rank
-//      has delivered this call's candidates;
+//      rank's symmetric exchange buffer (plain peer stores over NVLink), fences, and writes this call's epoch
+//      into word [r][its own rank] of every rank's arrival array (one word per row and source: a count shared
+//      by the sources could be completed by a fast peer's next call while a slow peer's delivery is missing);
+//   2. it waits (bounded) until all `world` words of its own arrival row r have reached the epoch, i.e. CTA r
+//      of every rank has delivered this call's candidates;
 //   3. it merges the `world` sorted lists: each candidate's global rank is its own index plus, for every
 //      other list, the number of entries that precede it (binary search), and the first k go to the output.
 // The epoch is a per-row counter in local memory that the kernel advances itself, so the launch can be
@@ -584,7 +585,7 @@ constexpr int MERGE_MAX_K = 128;
 struct TopkMergeParams {
   float* xval[COMM_MAX_RANKS];        // every rank's exchange buffer: values [2][world][rows][MERGE_MAX_K]
   int* xidx[COMM_MAX_RANKS];          // indices, same layout
-  uint32_t* arrive[COMM_MAX_RANKS];   // every rank's arrival words [rows]
+  uint32_t* arrive[COMM_MAX_RANKS];   // every rank's arrival words [rows][COMM_MAX_RANKS] (indexed by source rank)
   uint32_t* epoch;                    // local [rows]
   const float* val;                   // local candidates [rows, ldv]
   const int* idx;
@@ -619,17 +620,19 @@ __global__ void __launch_bounds__(256) tp_topk_merge_kernel(const TopkMergeParam
   __syncthreads();
   if (tid < W) {
     __threadfence_system();
-    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.arrive[tid] + r), "r"(1u) : "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.arrive[tid] + (size_t)r * COMM_MAX_RANKS + p.rank), "r"(ep)
+                 : "memory");
   }
   // 2. wait for every rank's delivery of this call
   if (tid == 0) {
-    const uint32_t want = ep * (uint32_t)W;
-    const uint32_t* mine = p.arrive[p.rank] + r;
+    const uint32_t* mine = p.arrive[p.rank] + (size_t)r * COMM_MAX_RANKS;
     const unsigned long long limit = p.wait_limit_ns ? p.wait_limit_ns : WAIT_TIMEOUT_NS;
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     int ok = 1;
-    while ((int32_t)(ld_acquire_sys(mine) - want) < 0) {
+    int src = 0;                       // sources 0 .. src - 1 have delivered
+    while (src < W) {
+      if ((int32_t)(ld_acquire_sys(mine + src) - ep) >= 0) { ++src; continue; }
       if ((++spins & 0xff) == 0) {
         const unsigned long long now = globaltimer_ns();
         if (t0 == 0) t0 = now;

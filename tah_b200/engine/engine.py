@@ -246,18 +246,22 @@ class TaHEngine:
         if tensor_core_attn:
             tile_q0, tile_qn = K.attn_tiles(seq_counts)
         rope_cs = K.rope_table(pos, hd, cfg.rope_theta) if fuse_qkv else None     # once per pass, shared by the layers
+        # tensor parallel: token counts that deal out in 16-row blocks take the push path (reduce-scatter in the
+        # GEMM epilogue, consumers wait on landing flags), the others the pull kernel
+        push = (tp is not None and os.environ.get("TAH_B200_TP_PULL", "0") != "1" and tp.push_desc(n) is not None)
+        self._xn_wait = None
         xn = K.rms_norm(h, w.layers[0].ln1, cfg.rms_norm_eps, out=xn_buf)
         for li, L in enumerate(w.layers):
             if taps_out is not None and li in tap_layers:
                 taps_out[li] = h.clone() if tp is None else tp.gather_rows(h, n)
-            kw = dict(x2=K.gemm(xn, L.a_qkv), w2=L.b_qkv) if lora else {}
+            kw = dict(x2=K.gemm(xn, L.a_qkv, tp_wait=self._xn_wait), w2=L.b_qkv) if lora else {}
             kd, vd = bf(n, nkv * hd), bf(n, nkv * hd)
             if fuse_qkv:
                 q = K.gemm_qkv(xn, L.w_qkv, L.q_norm, L.k_norm, pos, nq, nkv, cfg.rms_norm_eps, cfg.rope_theta,
                                k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
-                               page_size=self.page_size, rope_cs=rope_cs, **kw)
+                               page_size=self.page_size, rope_cs=rope_cs, tp_wait=self._xn_wait, **kw)
             else:
-                qkv = K.gemm(xn, L.w_qkv, **kw)
+                qkv = K.gemm(xn, L.w_qkv, tp_wait=self._xn_wait, **kw)
                 q = K.qk_norm_rope_kv(qkv, L.q_norm, L.k_norm, pos, nq, nkv, hd, cfg.rms_norm_eps, cfg.rope_theta,
                                       k_dense=kd, v_dense=vd, caches=[self.kv.layer_pool(depth, li)], slot=slots,
                                       page_size=self.page_size)
@@ -268,15 +272,15 @@ class TaHEngine:
                 o = K.prefill_attn(q, ks, vs, seg_base, seg_count, tile_q0, tile_qn, nq, nkv, hd, scale)
             else:
                 o = K.varlen_attn_naive(q, ks, vs, seg_base, seg_count, nq, nkv, hd, scale)
-            xn = self._row_parallel(o, L.w_o, L.a_o if lora else None, L.b_o, t_o, None, h, L.ln2, xn_buf, n)
+            xn = self._row_parallel(o, L.w_o, L.a_o if lora else None, L.b_o, t_o, None, h, L.ln2, xn_buf, n, push=push)
             if lora:
-                t = K.gemm(xn, L.a_gu)
-                act = K.gemm(xn, L.w_gu, x2=t, w2=L.b_gu, swiglu=True)
+                t = K.gemm(xn, L.a_gu, tp_wait=self._xn_wait)
+                act = K.gemm(xn, L.w_gu, x2=t, w2=L.b_gu, swiglu=True, tp_wait=self._xn_wait)
             else:
-                act = K.gemm(xn, L.w_gu, swiglu=True)
+                act = K.gemm(xn, L.w_gu, swiglu=True, tp_wait=self._xn_wait)
             next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
             xn = self._row_parallel(act, L.w_down, L.a_down if lora else None, L.b_down, t_down, None, h, next_ln,
-                                    xn_buf, n)
+                                    xn_buf, n, push=push, final=li + 1 == nL)
         hn = xn.clone()
         if taps_out is not None and cfg.num_hidden_layers in tap_layers:
             taps_out[cfg.num_hidden_layers] = hn

@@ -192,7 +192,7 @@ class TensorParallel:
     # ---- vocabulary-parallel arg-max / top-k merge: candidates exchanged by peer stores, merged locally -----
     def _merge_buffers(self, rows: int):
         """Symmetric exchange buffers for :meth:`merge_topk` (values / indices ``[2][world][rows][128]``, one
-        arrival word per row) and the local per-row epoch counters."""
+        arrival word per row and source rank) and the local per-row epoch counters."""
         cache = self.__dict__.setdefault("_merge", {})         # one set of buffers per row count
         st = cache.get(rows)
         if st is not None:
@@ -201,7 +201,7 @@ class TensorParallel:
         n = 2 * self.world_size * rows * 128
         xv = symm_mem.empty(n, dtype=torch.float32, device=self.device)
         xi = symm_mem.empty(n, dtype=torch.int32, device=self.device)
-        ar = symm_mem.empty(rows, dtype=torch.int32, device=self.device)
+        ar = symm_mem.empty(rows * 8, dtype=torch.int32, device=self.device)      # [rows][8 sources]
         ar.zero_()
         hv, hi, ha = (symm_mem.rendezvous(t, self.group) for t in (xv, xi, ar))
         st = dict(rows=rows, keep=(xv, xi, ar, hv, hi, ha), xval=[int(p) for p in hv.buffer_ptrs],

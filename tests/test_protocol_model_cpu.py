@@ -2,9 +2,11 @@
 symmetric buffers are shared Python lists, peer stores / flag updates are ordinary writes under the GIL.
 
 * exchange protocol of ``tp_topk_merge_kernel`` (``csrc/comm.cu``): deliver to every peer's slot ``[epoch
-  parity][source]``, add 1 to the peer's arrival word, wait until the own word reaches ``world * epoch``, read.
-  The model checks that with two slots a reader never sees data of another call although peers run up to one
-  call ahead, and that the wait is bounded: a rank that never delivers makes the others give up with a status
+  parity][source]``, write the call's epoch into the peer's arrival word of this source, wait until all own
+  words have reached the epoch, read.  (One counted word per rank is not enough: a fast peer's next call can
+  complete the count while a slow peer's delivery is missing; an earlier form of the kernel had that race and
+  this model showed it.)  The model checks that with two slots a reader never sees data of another call
+  although peers run up to one call ahead, and that the wait is bounded: a rank that never delivers makes the others give up with a status
   instead of spinning forever.
 * landing-flag protocol of the push all-gather (``shard_gather_push_kernel`` + the consumer's ``wait_peer_rows``):
   the consumer's target grows by the push grid size per use; a consumer never reads a buffer before all sources
@@ -26,8 +28,7 @@ def _spin(cond, limit_s):
 
 def _run_exchange(world, calls, absent=None, limit_s=5.0, seed=0):
     slots = [[[None] * world for _ in range(2)] for _ in range(world)]      # slots[rank][parity][source]
-    arrive = [0] * world
-    lock = threading.Lock()                                                # the atomic add on the arrival word
+    arrive = [[0] * world for _ in range(world)]                           # arrive[rank][source] = epoch delivered
     status, bad = [0] * world, []
 
     def rank_main(r):
@@ -39,9 +40,8 @@ def _run_exchange(world, calls, absent=None, limit_s=5.0, seed=0):
             for q in range(world):
                 time.sleep(rng.random() * 1e-4)
                 slots[q][par][r] = (ep, r)
-                with lock:
-                    arrive[q] += 1
-            if not _spin(lambda: arrive[r] >= ep * world, limit_s):
+                arrive[q][r] = ep                                          # release store, one word per source
+            if not _spin(lambda: all(a >= ep for a in arrive[r]), limit_s):
                 status[r] = 4                                              # STATUS_TIMEOUT_PEER_FLAG, then return
                 return
             got = [slots[r][par][q] for q in range(world)]
