@@ -43,6 +43,9 @@ def add_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--decider", default="oracle-mlp", choices=["oracle-mlp", "label", "mlp"])
     ap.add_argument("--lora-rank", type=int, default=64)
     ap.add_argument("--strategy", default="zero2", choices=["zero2", "zero3"])
+    ap.add_argument("--kernel-table", default=None,
+                    help="after the timed steps, run one more step under the PyTorch profiler and write the kernels' "
+                         "device-time table to this file (rank 0)")
     ap.add_argument("--checkpoint", action="store_true",
                     help="recompute the dense stages of every layer in backward (needed for longer sequences / larger models)")
 
@@ -127,6 +130,9 @@ def run(a, steps: int, warmup: int) -> dict:
     if world > 1:
         dist.barrier()
     torch.cuda.reset_peak_memory_stats()
+    from bench_clocks import ClockSampler
+    sampler = ClockSampler(local)
+    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
@@ -135,18 +141,27 @@ def run(a, steps: int, warmup: int) -> dict:
     e1.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    if getattr(a, "kernel_table", None):
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(a.kernel_table, "w") as fh:
+                fh.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
     ms = torch.tensor([e0.elapsed_time(e1), wall * 1e3], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms, wall_ms = float(ms[0]), float(ms[1])
     toks = steps * a.accum * a.seq * world
     rec = {
-        "metric": "TaH-plus-1.7B SFT training tokens/s", "value": round(toks / (ms / 1e3), 1), "unit": "tokens/s",
+        "metric": ("TaH-plus-1.7B" if a.train_model == "tah-plus-1.7b" else a.train_model) + " SFT training tokens/s", "value": round(toks / (ms / 1e3), 1), "unit": "tokens/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / max(1, steps), 1),
         "e2e": {"value": round(toks / (wall_ms / 1e3), 1), "unit": "tokens/s",
                 "includes": "pinned-host batch H2D every micro-batch, forward, backward, optimizer, loss D2H",
                 "h2d_bytes_per_step": h2d * a.accum, "d2h_bytes_per_step": 4 * a.accum},
-        "loss": round(loss, 4), "dtype": "bf16 (fp32 master weights)",
+        "loss": round(loss, 4), "dtype": "bf16 (fp32 master weights)", "clocks": clocks,
         "data": "synthetic", "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         "config": {"model": a.train_model, "seq_len": a.seq, "micro_batches_per_step": a.accum,
                    "global_batch": a.accum * world, "hard_rate": hard_rate, "decider": a.decider,
