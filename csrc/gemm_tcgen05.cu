@@ -16,6 +16,10 @@
 //   residual   out = residual[t, f] + bf16(acc)
 //   DUAL       two accumulators per CTA, gate = rows f and up = rows up_off + f of W:
 //              out = bf16(silu(bf16(gate))) * bf16(up)             (SwiGLU)
+//   interleaved SwiGLU (act 2)   one accumulator; the rows of W alternate gate_i, up_i, so a 128-row tile
+//              holds 64 output features and the partner of a value sits in the neighbouring TMEM lane:
+//              out[t, f / 2] = bf16(silu(bf16(gate))) * bf16(up).  One 256-token MMA per k step instead of two
+//              128-token ones: the faster form at every token count (19 vs 29 us at 256 x 12288 x 2048).
 //
 // Split-K: a thread-block cluster of S CTAs along z splits the k-blocks; the partial accumulators
 // of columns owned by other ranks go to the CTA's own shared memory, and every CTA adds to its own
@@ -46,7 +50,8 @@ struct GemmParams {
   int kb_ext;   // R / 64
   int splits;   // cluster size along z (1 = no split-K)
   int tma_out;  // 1: stage the output tile in shared memory and write it with a TMA store
-  int act;      // epilogue activation on the (non-dual) output: 0 none, 1 GELU (erf form) of the bf16-rounded value
+  int act;      // epilogue activation on the (non-dual) output: 0 none, 1 GELU (erf form) of the bf16-rounded value,
+                // 2 SwiGLU of interleaved gate / up rows (out has F / 2 features)
   // Operand majors (backward GEMMs read their operands transposed, straight from the row-major tensors):
   //   a_mn: the 128-row operand is stored [reduction, feature] (feature contiguous): dgrad reads W[F, K] as
   //         W^T, wgrad reads X[T, K] as X^T;   b_mn: the column operand is stored [reduction, column]
@@ -147,6 +152,28 @@ __device__ __noinline__ void gelu_tile(__nv_bfloat16* stg, int n_tok) {
   for (int i = e; i < n_tok * 64; i += 128) {
     const float2 f = __bfloat1622float2(v[i]);
     v[i] = __floats2bfloat162_rn(gelu_erf(f.x), gelu_erf(f.y));
+  }
+}
+
+// Interleaved-SwiGLU epilogue of one accumulator tile (S == 1 path): lanes 2i / 2i + 1 of the tile hold gate_i / up_i.
+// Per token pair the even lane sends its gate of the odd token and receives the up value of the even token (one
+// shuffle), so each lane evaluates one SiLU per two tokens; results go to a [BN tokens][64 features] staging tile.
+template <int BN, int CHUNK>
+__device__ __noinline__ void swiglu_interleaved_tile(uint32_t trow, __nv_bfloat16* stg, int row) {
+  const bool odd = row & 1;
+  const int fo = row >> 1;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+    float a[CHUNK];
+    tmem_ld_chunk<CHUNK>(trow + c0, a);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < CHUNK; j += 2) {
+      const float recv = __shfl_xor_sync(0xffffffffu, odd ? a[j] : a[j + 1], 1);
+      const float g = odd ? recv : a[j];            // even lane: token j, odd lane: token j + 1
+      const float u = odd ? a[j + 1] : recv;
+      stg[(c0 + j + (odd ? 1 : 0)) * 64 + fo] = __float2bfloat16_rn(bf16_round(silu(bf16_round(g))) * bf16_round(u));
+    }
   }
 }
 
@@ -467,8 +494,12 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
         mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
       }
+      const bool swiglu_il = !DUAL && p.act == 2;
+      if (swiglu_il) {
+        if constexpr (!DUAL) swiglu_interleaved_tile<BN, C::CHUNK>(trow, stg, row);
+      }
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += C::CHUNK) {
+      for (int c0 = swiglu_il ? BN : 0; c0 < BN; c0 += C::CHUNK) {
         float a[C::CHUNK];
         float u[DUAL ? C::CHUNK : 1];
         tmem_ld_chunk<C::CHUNK>(trow + c0, a);
@@ -500,7 +531,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
-          tma_store_2d(&tm_out, stg, f0, t0);
+          tma_store_2d(&tm_out, stg, swiglu_il ? f0 / 2 : f0, t0);
           tma_store_commit();
           tma_store_wait_read();
         }
@@ -647,13 +678,13 @@ static EncodeTiledFn get_encode_fn() {
 // 2D bf16 row-major [rows, cols] with leading dimension ld (elements).  Operand maps use a
 // {64, box_rows} box with the 128-byte swizzle; output/residual maps a {128, box_rows} box, unswizzled.
 static int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows,
-                    bool operand) {
+                    bool operand, unsigned out_box_cols = 128u) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {operand ? 64u : 128u, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {operand ? 64u : out_box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -761,10 +792,12 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   if (qkv != nullptr && (dual != 0 || residual != nullptr || push || F != (qkv->nq + 2 * qkv->nkv) * 128 ||
                          qkv->n_caches > 4 || qkv->q_out == nullptr || qkv->pos == nullptr))
     return -26;
-  // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 3 = one accumulator + GELU
+  // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 3 = one accumulator + GELU,
+  // 4 = one accumulator, SwiGLU of interleaved gate / up rows (F weight rows -> F / 2 output features)
   if (dual == 2) return -24;
-  const int act = dual == 3 ? 1 : 0;
-  if (dual == 3) dual = 0;
+  const int act = dual == 3 ? 1 : dual == 4 ? 2 : 0;
+  if (dual == 3 || dual == 4) dual = 0;
+  if (act == 2 && (F % 2 || splits > 1 || push || residual != nullptr || qkv != nullptr || a_mn || b_mn)) return -29;
   const int F_full = F;
   if (push && (dual == 1 || residual != nullptr || F_full % 128 || tp.push_world > GEMM_MAX_RANKS || tp.push_rpr <= 0))
     return -23;
@@ -790,9 +823,10 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   }
   // output (and residual) through TMA when their layout allows it, else element-wise stores
   CUtensorMap mo, mr;
-  int tma_out = !push && qkv == nullptr && make_map(&mo, out, M, F_full, ldo, bn / splits, false) == 0;
+  int tma_out = !push && qkv == nullptr &&
+                make_map(&mo, out, M, act == 2 ? F_full / 2 : F_full, ldo, bn / splits, false, act == 2 ? 64u : 128u) == 0;
   if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F_full, ldr, bn / splits, false) == 0;
-  if (act && (!tma_out || residual != nullptr)) return -28;   // the GELU pass runs on the staged tile, before no residual
+  if (act && (!tma_out || residual != nullptr)) return -28;   // the activation passes work on the staged tile, without a residual
   if (!tma_out) mo = mw;
   if (!tma_out || residual == nullptr) mr = mo;
   GemmParams p;

@@ -273,11 +273,12 @@ class TaHEngine:
             else:
                 o = K.varlen_attn_naive(q, ks, vs, seg_base, seg_count, nq, nkv, hd, scale)
             xn = self._row_parallel(o, L.w_o, L.a_o if lora else None, L.b_o, t_o, None, h, L.ln2, xn_buf, n, push=push)
+            sw = dict(swiglu_interleaved=True) if w.gu_interleaved else dict(swiglu=True)
             if lora:
                 t = K.gemm(xn, L.a_gu, tp_wait=self._xn_wait)
-                act = K.gemm(xn, L.w_gu, x2=t, w2=L.b_gu, swiglu=True, tp_wait=self._xn_wait)
+                act = K.gemm(xn, L.w_gu, x2=t, w2=L.b_gu, tp_wait=self._xn_wait, **sw)
             else:
-                act = K.gemm(xn, L.w_gu, swiglu=True, tp_wait=self._xn_wait)
+                act = K.gemm(xn, L.w_gu, tp_wait=self._xn_wait, **sw)
             next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
             xn = self._row_parallel(act, L.w_down, L.a_down if lora else None, L.b_down, t_down, None, h, next_ln,
                                     xn_buf, n, push=push, final=li + 1 == nL)
@@ -600,10 +601,11 @@ class TaHEngine:
                                     push=push, next_lora=(L.a_gu, s.t_gu) if fuse_norm_lora else None)
             if lora and not fuse_norm_lora:
                 K.lora_a_rows(xn, L.a_gu, s.gate, out=s.t_gu, tp_wait=self._xn_wait)
+            sw = dict(swiglu_interleaved=True) if w.gu_interleaved else dict(swiglu=True)
             if lora:
-                K.gemm(xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
+                K.gemm(xn, L.w_gu, x2=s.t_gu, w2=L.b_gu, out=s.act, tp_wait=self._xn_wait, **sw)
             else:
-                K.gemm(xn, L.w_gu, swiglu=True, out=s.act, tp_wait=self._xn_wait)
+                K.gemm(xn, L.w_gu, out=s.act, tp_wait=self._xn_wait, **sw)
             next_ln = w.layers[li + 1].ln1 if li + 1 < nL else w.final_norm
             nxt_lora = (w.layers[li + 1].a_qkv, s.t_qkv) if fuse_norm_lora and li + 1 < nL else None
             # a tap of the next layer's input is this projection's updated residual stream

@@ -12,7 +12,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional
 
+import os
+
 import torch
+
+from tah_b200.ops import cuda as K
 
 
 def _pad64(n: int) -> int:
@@ -75,6 +79,8 @@ class EngineWeights:
         self.r = base.lora.r
         dev = base.device
         bf = lambda t: t.detach().to(torch.bfloat16).contiguous()
+        # TAH_B200_SWIGLU=dual keeps the stacked [gate; up] layout and the two-accumulator SwiGLU GEMM
+        self.gu_interleaved = os.environ.get("TAH_B200_SWIGLU", "interleaved") != "dual"
         self.embed = bf(base.model.embed_tokens.weight)
         head = base.lm_head_weight
         V = head.shape[0]
@@ -119,6 +125,11 @@ class EngineWeights:
             lw.a_qkv, lw.b_qkv = _lora_pair(at.qkv_proj, rows=qkv_rows)
             lw.a_o, lw.b_o = _lora_pair(at.o_proj, cols=o_cols)
             lw.a_gu, lw.b_gu = _lora_pair(mlp.gate_up_proj, rows=gu_rows)
+            if self.gu_interleaved:
+                # rows gate_0, up_0, gate_1, ...: the GEMM's interleaved SwiGLU epilogue (one accumulator)
+                lw.w_gu = K.interleave_gate_up(lw.w_gu)
+                if lw.b_gu is not None:
+                    lw.b_gu = K.interleave_gate_up(lw.b_gu)
             lw.a_down, lw.b_down = _lora_pair(mlp.down_proj, cols=d_cols)
             self.layers.append(lw)
         l0 = self.layers[0]

@@ -140,6 +140,13 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
     return best[1], best[2]
 
 
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """``[2I, K]`` gate rows then up rows -> ``[2I, K]`` with rows ``gate_0, up_0, gate_1, up_1, ...`` (the layout
+    :func:`gemm` wants for ``swiglu_interleaved``; apply it to the LoRA-B extension of the projection as well)."""
+    half = w.shape[0] // 2
+    return torch.stack((w[:half], w[half:]), dim=1).reshape(w.shape).contiguous()
+
+
 def pick_splits(M: int, F: int, K: int, R: int = 0, dual: bool = False) -> int:
     return plan_gemm(M, F, K, R, dual)[1]
 
@@ -180,11 +187,14 @@ def wait_flags(flags: torch.Tensor, targets: torch.Tensor) -> None:
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
-         bn: int = 0, tp_push=None, tp_wait=None, gelu: bool = False) -> torch.Tensor:
+         bn: int = 0, tp_push=None, tp_wait=None, gelu: bool = False, swiglu_interleaved: bool = False) -> torch.Tensor:
     """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
     weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
 
     ``gelu``: the epilogue applies the erf GELU to the bf16-rounded output (not together with ``residual``).
+
+    ``swiglu_interleaved``: the rows of ``w`` (and ``w2``) alternate ``gate_i, up_i`` (see :func:`interleave_gate_up`)
+    and ``out[M, F/2] = silu(gate) * up``: one accumulator and one wide MMA per k step, the faster SwiGLU form.
 
     Tensor parallel (see :class:`tah_b200.parallel.tp.TensorParallel`): ``tp_push =
     (slot_ptrs, cnt_ptrs, rank, rows_per_rank)`` replaces the output by peer stores of the tile
@@ -195,6 +205,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     tp_wait = _take_pending_wait(tp_wait)
     M, K = x.shape
     F = w.shape[0] // 2 if swiglu else w.shape[0]
+    F_out = F // 2 if swiglu_interleaved else F
+    if swiglu_interleaved and (swiglu or gelu or residual is not None or tp_push is not None or F % 2):
+        raise ValueError("swiglu_interleaved excludes swiglu / gelu / residual / tp_push")
     if w.shape[1] != K:
         raise ValueError(f"K mismatch: x {tuple(x.shape)} w {tuple(w.shape)}")
     R = 0
@@ -207,12 +220,16 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     if tp_push is not None:
         out = x.new_empty(0, F) if out is None else out
     elif out is None:
-        out = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(M, F_out, dtype=torch.bfloat16, device=x.device)
     else:
         _check_bf16_2d(out, "out")
     if residual is not None:
         _check_bf16_2d(residual, "residual")
-    if splits is None and bn == 0:
+    if swiglu_interleaved:
+        splits = 1                       # the interleaved epilogue exists for unsplit tiles
+        if bn == 0:
+            bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+    elif splits is None and bn == 0:
         bn, splits = plan_gemm(M, F, K, R, swiglu)
     elif splits is None:
         splits = 1
@@ -220,7 +237,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
             c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
             c_ll(residual.stride(0) if residual is not None else 0),
             c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
-            c_int(1 if swiglu else 3 if gelu else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+            c_int(1 if swiglu else 3 if gelu else 4 if swiglu_interleaved else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
             _p(status_word(x.device)), _stream())
     if tp_push is None and tp_wait is None:
         rc = lib().tahb_gemm(*args)

@@ -82,6 +82,30 @@ def test_gemm_swiglu(M, I, K, splits):
     _close(out, ref, atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("M,I,K,R", [(64, 768, 256, 0), (16, 6144, 2048, 64), (200, 1536, 512, 64), (256, 6144, 2048, 64),
+                                     (130, 1216, 2048, 0), (700, 768, 512, 64), (1, 128, 128, 0)])
+def test_gemm_swiglu_interleaved(M, I, K, R):
+    """SwiGLU on interleaved gate / up rows (one accumulator, partner value in the neighbouring TMEM lane) equals the
+    stacked-layout reference, with and without the LoRA K-extension, for token counts on and off the tile sizes."""
+    Kc = _cuda()
+    x, w = _rand(M, K, seed=1), _rand(2 * I, K, scale=K ** -0.5, seed=2)
+    x2 = _rand(M, R, seed=3) if R else None
+    w2 = _rand(2 * I, R, scale=0.05, seed=4) if R else None
+    out = Kc.gemm(x, Kc.interleave_gate_up(w), x2=x2, w2=None if w2 is None else Kc.interleave_gate_up(w2),
+                  swiglu_interleaved=True)
+    Kc.check_status()
+    assert out.shape == (M, I)
+    acc = x.float() @ w.float().t()
+    if R:
+        acc = acc + x2.float() @ w2.float().t()
+    gu = acc.to(torch.bfloat16).float()
+    ref = torch.nn.functional.silu(gu[:, :I]).to(torch.bfloat16).float() * gu[:, I:]
+    _close(out, ref, atol=3e-2, rtol=3e-2)
+    # same values as the two-accumulator form (unsplit: the same summation order over K)
+    dual = Kc.gemm(x, w, x2=x2, w2=w2, swiglu=True, splits=1)
+    assert torch.equal(out, dual)
+
+
 def test_gemm_strided_views():
     Kc = _cuda()
     big = _rand(64, 1024, seed=7)
