@@ -360,7 +360,7 @@ __host__ __device__ constexpr int split_stage_offset(int S, int cols_per_rank) {
   return (((S - 1) * 128 * cols_per_rank * 4) + 1023) & ~1023;
 }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool PAIR = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_x2,
@@ -435,7 +435,14 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         } else {
           tma_load_2d(st, mw, x, f0, &full_bar[s]);
         }
-        if constexpr (DUAL) tma_load_2d(st + C::W_TILE, mw, x, p.up_off + f0, &full_bar[s]);
+        if constexpr (DUAL) {               // second feature tile: the "up" rows (SwiGLU) or features up_off + f0 (pair)
+          if (p.a_mn) {
+            tma_load_2d(st + C::W_TILE, mw, p.up_off + f0, x, &full_bar[s]);
+            tma_load_2d(st + C::W_TILE + 8192, mw, p.up_off + f0 + 64, x, &full_bar[s]);
+          } else {
+            tma_load_2d(st + C::W_TILE, mw, x, p.up_off + f0, &full_bar[s]);
+          }
+        }
         if (p.b_mn) {
 #pragma unroll
           for (int j = 0; j < (BN >= 64 ? BN / 64 : 1); ++j)
@@ -463,13 +470,14 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         // the low bits of the descriptor in 16-byte units, so a k step is an addition.
         const uint64_t da0 = p.a_mn ? umma_desc_mn_sw128(a_addr, 8192) : umma_desc_sw128(a_addr);
         const uint64_t db0 = p.b_mn ? umma_desc_mn_sw128(b_addr, 8192) : umma_desc_sw128(b_addr);
+        const uint64_t da1 = p.a_mn ? umma_desc_mn_sw128(a_addr + C::W_TILE, 8192) : umma_desc_sw128(a_addr + C::W_TILE);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint64_t da = da0 + (uint64_t)(k * a_step);
           const uint64_t db = db0 + (uint64_t)(k * b_step);
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
           umma_bf16(tmem_base, da, db, idesc, acc);
-          if constexpr (DUAL) umma_bf16(tmem_base + BN, umma_desc_sw128(a_addr + C::W_TILE + k * 32), db, idesc, acc);
+          if constexpr (DUAL) umma_bf16(tmem_base + BN, da1 + (uint64_t)(k * a_step), db, idesc, acc);
         }
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
       }
@@ -487,6 +495,51 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (S == 1) {
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [BN tokens][128 features]
       const bool res_tma = p.tma_out && p.residual != nullptr;
+      if constexpr (PAIR) {
+        // Two plain output tiles (features f0.. and up_off + f0..) that shared the CTA's activation tile: per unit
+        // of work a CTA pulls half the activation bytes, which is what bounds the GEMM at large token counts.
+        __nv_bfloat16* stg1 = stg + BN * 128;
+        const bool il = p.act == 2;
+        if (res_tma) {
+          if (threadIdx.x == 64) {
+            mbar_expect_tx(res_bar, BN * 256 * 2);
+            tma_load_2d(stg, &tm_res, f0, t0, res_bar);
+            tma_load_2d(stg1, &tm_res, p.up_off + f0, t0, res_bar);
+          }
+          mbar_wait(res_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA_FULL);
+        }
+        if (il) {
+          swiglu_interleaved_tile<BN, C::CHUNK>(trow, stg, row);
+          swiglu_interleaved_tile<BN, C::CHUNK>(trow + BN, stg1, row);
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += C::CHUNK) {
+            float a[C::CHUNK], u[C::CHUNK];
+            tmem_ld_chunk<C::CHUNK>(trow + c0, a);
+            tmem_ld_chunk<C::CHUNK>(trow + BN + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < C::CHUNK; ++j) {
+              stage_one<false>(stg + (c0 + j) * 128 + row, a[j], 0.f, res_tma);
+              stage_one<false>(stg1 + (c0 + j) * 128 + row, u[j], 0.f, res_tma);
+            }
+          }
+        }
+        if (p.push_world > 0) {
+          named_bar_sync(1, 128);
+          push_rows(p, stg, t0, BN, f0);
+          push_rows(p, stg1, t0, BN, p.up_off + f0);
+        } else {
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (threadIdx.x == 64) {
+            tma_store_2d(&tm_out, stg, il ? f0 / 2 : f0, t0);
+            tma_store_2d(&tm_out, stg1, il ? (p.up_off + f0) / 2 : p.up_off + f0, t0);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+        }
+      } else {
       if (res_tma) {
         if (threadIdx.x == 64) {
           mbar_expect_tx(res_bar, BN * 256);
@@ -535,6 +588,7 @@ gemm_fl_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           tma_store_commit();
           tma_store_wait_read();
         }
+      }
       }
     }
     tc_fence_before();
@@ -708,12 +762,12 @@ static int make_map_mn(CUtensorMap* m, const void* base, long long red_rows, lon
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool PAIR = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mw2, const CUtensorMap& mx2,
                   const CUtensorMap& mo, const CUtensorMap& mr, const GemmParams& p, cudaStream_t stream) {
   using C = GemmCfg<BN, DUAL>;
   static bool configured = false;
-  auto kern = gemm_fl_kernel<BN, DUAL>;
+  auto kern = gemm_fl_kernel<BN, DUAL, PAIR>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -10;
     configured = true;
@@ -786,19 +840,31 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
                      int a_mn = 0, int b_mn = 0, int k_rows = 0) {
   if (M <= 0 || F <= 0) return 0;
   // transposed operands: W is then [K, F] (ldw = its row pitch), X is [K, M]; no LoRA extension, no dual
-  if ((a_mn || b_mn) && (dual == 1 || R > 0 || qkv != nullptr || tp.push_world > 0)) return -27;
+  if ((a_mn || b_mn) && (dual == 1 || dual == 6 || R > 0 || qkv != nullptr || tp.push_world > 0)) return -27;
   if (a_mn && F % 128) return -27;
   const bool push = tp.push_world > 0;
   if (qkv != nullptr && (dual != 0 || residual != nullptr || push || F != (qkv->nq + 2 * qkv->nkv) * 128 ||
                          qkv->n_caches > 4 || qkv->q_out == nullptr || qkv->pos == nullptr))
     return -26;
   // dual: 0 = one accumulator, 1 = SwiGLU of W rows [0, F) and [up_off, up_off + F), 3 = one accumulator + GELU,
-  // 4 = one accumulator, SwiGLU of interleaved gate / up rows (F weight rows -> F / 2 output features)
-  if (dual == 2) return -24;
-  const int act = dual == 3 ? 1 : dual == 4 ? 2 : 0;
+  // 4 = one accumulator, SwiGLU of interleaved gate / up rows (F weight rows -> F / 2 output features),
+  // 2 = pair: two plain 128-feature tiles per CTA (features f and F / 2 + f) that share a 256-token activation
+  //     tile, unsplit; 6 = pair + interleaved SwiGLU.  The pair forms halve the activation bytes per unit of work
+  //     and are the fast ones at large token counts (1350-1400 vs 915-1100 TFLOP/s at 8192+ tokens).
+  const bool pair = dual == 2 || dual == 6;
+  const int act = dual == 3 ? 1 : (dual == 4 || dual == 6) ? 2 : 0;
   if (dual == 3 || dual == 4) dual = 0;
   if (act == 2 && (F % 2 || splits > 1 || push || residual != nullptr || qkv != nullptr || a_mn || b_mn)) return -29;
   const int F_full = F;
+  if (pair) {
+    if (F % 256 || qkv != nullptr || R % 64) return -24;
+    dual = 2;
+    F = F / 2;
+    up_off = F;
+    bn = 256;
+    splits = 1;
+  }
+  if (pair && b_mn && M % 64) return -24;
   if (push && (dual == 1 || residual != nullptr || F_full % 128 || tp.push_world > GEMM_MAX_RANKS || tp.push_rpr <= 0))
     return -23;
   if (K % 64 || R % 64 || K <= 0) return -20;
@@ -812,7 +878,7 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   int rc;
   // k_rows: true reduction length of MN-major operands (K is rounded up to whole k-blocks; TMA zero-fills the rest)
   const long long kr = k_rows > 0 ? k_rows : K;
-  if ((rc = a_mn ? make_map_mn(&mw, W, kr, F, ldw) : make_map(&mw, W, w_rows, K, ldw, 128, true))) return rc;
+  if ((rc = a_mn ? make_map_mn(&mw, W, kr, w_rows, ldw) : make_map(&mw, W, w_rows, K, ldw, 128, true))) return rc;
   if ((rc = b_mn ? make_map_mn(&mx, X, kr, M, ldx) : make_map(&mx, X, M, K, ldx, bn, true))) return rc;
   if (R > 0) {
     if ((rc = make_map(&mw2, W2, w_rows, R, ldw2, 128, true))) return rc;
@@ -826,6 +892,7 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
   int tma_out = !push && qkv == nullptr &&
                 make_map(&mo, out, M, act == 2 ? F_full / 2 : F_full, ldo, bn / splits, false, act == 2 ? 64u : 128u) == 0;
   if (tma_out && residual != nullptr) tma_out = make_map(&mr, residual, M, F_full, ldr, bn / splits, false) == 0;
+  if (pair && !tma_out && !push) return -25;     // the pair epilogue only exists on the staged paths
   if (act && (!tma_out || residual != nullptr)) return -28;   // the activation passes work on the staged tile, without a residual
   if (!tma_out) mo = mw;
   if (!tma_out || residual == nullptr) mr = mo;
@@ -881,6 +948,7 @@ static int gemm_impl(const void* W, const void* X, void* out, const void* residu
 #define TAHB_LAUNCH(BN_)                                                              \
   case BN_:                                                                           \
     return dual ? launch<BN_, true>(mw, mx, mw2, mx2, mo, mr, p, stream) : launch<BN_, false>(mw, mx, mw2, mx2, mo, mr, p, stream);
+  if (pair) return launch<256, true, true>(mw, mx, mw2, mx2, mo, mr, p, stream);
   switch (bn) {
     TAHB_LAUNCH(16)
     TAHB_LAUNCH(32)
@@ -935,11 +1003,12 @@ extern "C" int tahb_gemm_qkv(const void* W, const void* X, const void* W2, const
 //   a_mn: W is stored [K, F] row-major (row pitch ldw) instead of [F, K];
 //   b_mn: X is stored [K, M] row-major (row pitch ldx) instead of [M, K].
 // K (the reduction length) may be any multiple of 8; rows past it read as zeros.  F % 128 == 0 with a_mn.
+// pair != 0: two feature tiles per CTA sharing a 256-column tile (F % 256 == 0; with b_mn also M % 64 == 0), unsplit.
 extern "C" int tahb_gemm_t(const void* W, const void* X, void* out, const void* residual, int M, int F, int K,
                            long long ldw, long long ldx, long long ldo, long long ldr, int a_mn, int b_mn, int splits,
-                           int bn, int* status, cudaStream_t stream) {
+                           int bn, int* status, cudaStream_t stream, int pair) {
   const int Kp = (K + 63) / 64 * 64;          // the tail k-block of MN-major operands is zero-filled by TMA
   if (Kp != K && !(a_mn && b_mn)) return -20; // a K-major operand needs whole k-blocks
-  return gemm_impl(W, X, out, residual, nullptr, nullptr, M, F, Kp, 0, ldw, ldx, ldo, ldr, 0, 0, 0, 0, splits, bn,
-                   status, stream, GemmTpArgs(), nullptr, a_mn, b_mn, K);
+  return gemm_impl(W, X, out, residual, nullptr, nullptr, M, F, Kp, 0, ldw, ldx, ldo, ldr, 0, 0, pair ? 2 : 0, 0, splits,
+                   bn, status, stream, GemmTpArgs(), nullptr, a_mn, b_mn, K);
 }

@@ -49,7 +49,7 @@ class GenerationResult:
 def _fusions(default: str):
     """Kernel fusions selected by ``TAH_B200_FUSE``: "1" = all, "0" = none, or a comma list of "qkv" (QK-norm, RoPE
     and the K/V write in the QKV GEMM's epilogue) and "lora" (LoRA-A of the gated rows inside the RMSNorm launch);
-    unset = ``default`` (the packed prefill pass fuses "qkv", the decode tick nothing)."""
+    unset = ``default`` (nothing: the chains of separate launches measured faster in decode and in prefill)."""
     v = os.environ.get("TAH_B200_FUSE", default)
     if v == "1":
         return {"qkv", "lora"}
@@ -242,7 +242,9 @@ class TaHEngine:
         t_down = bf(n, w.r_down) if lora else None
         tap_layers = self._tap_layers()
         tensor_core_attn = hd in (64, 128) and os.environ.get("TAH_B200_NAIVE_PREFILL", "0") != "1"
-        fuse_qkv = hd == 128 and "qkv" in _fusions("qkv")
+        # off by default here as well: at thousands of tokens per tile column the epilogue's QK-norm / RoPE arithmetic
+        # on four warps costs as much as the tile's main loop (prefill 272 ms fused, 254 ms with the separate kernel)
+        fuse_qkv = hd == 128 and "qkv" in _fusions("")
         if tensor_core_attn:
             tile_q0, tile_qn = K.attn_tiles(seq_counts)
         rope_cs = K.rope_table(pos, hd, cfg.rope_theta) if fuse_qkv else None     # once per pass, shared by the layers

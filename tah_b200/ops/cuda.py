@@ -140,6 +140,11 @@ def plan_gemm(M: int, F: int, K: int, R: int = 0, dual: bool = False):
     return best[1], best[2]
 
 
+# token count from which the two-tile ("pair") GEMM is the default; TAH_B200_GEMM_PAIR=0 turns it off
+PAIR_AUTO = os.environ.get("TAH_B200_GEMM_PAIR", "1") != "0"
+PAIR_MIN_TOKENS = 1024
+
+
 def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
     """``[2I, K]`` gate rows then up rows -> ``[2I, K]`` with rows ``gate_0, up_0, gate_1, up_1, ...`` (the layout
     :func:`gemm` wants for ``swiglu_interleaved``; apply it to the LoRA-B extension of the projection as well)."""
@@ -187,11 +192,17 @@ def wait_flags(flags: torch.Tensor, targets: torch.Tensor) -> None:
 def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, x2: Optional[torch.Tensor] = None,
          w2: Optional[torch.Tensor] = None, swiglu: bool = False, splits: Optional[int] = None,
-         bn: int = 0, tp_push=None, tp_wait=None, gelu: bool = False, swiglu_interleaved: bool = False) -> torch.Tensor:
+         bn: int = 0, tp_push=None, tp_wait=None, gelu: bool = False, swiglu_interleaved: bool = False,
+         pair: Optional[bool] = None) -> torch.Tensor:
     """``out[M,F] = x[M,K] @ w[F,K]^T (+ x2[M,R] @ w2[F,R]^T) (+ residual)``; with ``swiglu`` the
     weight is ``[2F, K]`` (gate rows then up rows) and ``out = silu(gate) * up``.
 
     ``gelu``: the epilogue applies the erf GELU to the bf16-rounded output (not together with ``residual``).
+
+    ``pair``: every CTA computes two 128-feature output tiles (features ``f`` and ``F/2 + f``) from one 256-token
+    activation tile, unsplit.  It halves the activation bytes a CTA pulls per unit of work, which is what bounds
+    the kernel at large token counts (1350-1400 vs 915-1100 TFLOP/s at 8192+ tokens); default: on from
+    ``PAIR_MIN_TOKENS`` tokens when the shape allows it (also with ``swiglu_interleaved``).
 
     ``swiglu_interleaved``: the rows of ``w`` (and ``w2``) alternate ``gate_i, up_i`` (see :func:`interleave_gate_up`)
     and ``out[M, F/2] = silu(gate) * up``: one accumulator and one wide MMA per k step, the faster SwiGLU form.
@@ -225,7 +236,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
         _check_bf16_2d(out, "out")
     if residual is not None:
         _check_bf16_2d(residual, "residual")
-    if swiglu_interleaved:
+    if pair is None:
+        pair = (PAIR_AUTO and M >= PAIR_MIN_TOKENS and bn == 0 and splits is None and not swiglu and not gelu
+                and w.shape[0] % 256 == 0)
+    pair = bool(pair) and not swiglu and not gelu and w.shape[0] % 256 == 0
+    if pair:
+        bn, splits = 256, 1
+    elif swiglu_interleaved:
         splits = 1                       # the interleaved epilogue exists for unsplit tiles
         if bn == 0:
             bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
@@ -237,7 +254,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
             c_ll(w.stride(0)), c_ll(x.stride(0)), c_ll(out.stride(0)),
             c_ll(residual.stride(0) if residual is not None else 0),
             c_ll(w2.stride(0) if w2 is not None else 0), c_ll(x2.stride(0) if x2 is not None else 0),
-            c_int(1 if swiglu else 3 if gelu else 4 if swiglu_interleaved else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
+            c_int(1 if swiglu else 3 if gelu else (6 if pair else 4) if swiglu_interleaved else 2 if pair else 0), c_int(F if swiglu else 0), c_int(splits), c_int(bn),
             _p(status_word(x.device)), _stream())
     if tp_push is None and tp_wait is None:
         rc = lib().tahb_gemm(*args)
@@ -259,7 +276,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
 
 
 def gemm_t(x: torch.Tensor, w: torch.Tensor, *, x_t: bool = False, w_t: bool = False, out: Optional[torch.Tensor] = None,
-           residual: Optional[torch.Tensor] = None, splits: Optional[int] = None, bn: int = 0) -> torch.Tensor:
+           residual: Optional[torch.Tensor] = None, splits: Optional[int] = None, bn: int = 0,
+           pair: Optional[bool] = None) -> torch.Tensor:
     """GEMM with operands read transposed straight from their row-major storage (the backward GEMMs):
 
     * ``w_t``: ``w`` is ``[K, F]`` (instead of ``[F, K]``); * ``x_t``: ``x`` is ``[K, M]`` (instead of ``[M, K]``);
@@ -280,12 +298,17 @@ def gemm_t(x: torch.Tensor, w: torch.Tensor, *, x_t: bool = False, w_t: bool = F
     if Kx != Kw:
         raise ValueError(f"reduction mismatch: x {tuple(x.shape)} (x_t={x_t}) w {tuple(w.shape)} (w_t={w_t})")
     if not (x_t or w_t):
-        return gemm(x, w, out=out, residual=residual, splits=splits, bn=bn)
+        return gemm(x, w, out=out, residual=residual, splits=splits, bn=bn, pair=pair)
     if out is None:
         out = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
     if residual is not None:
         _check_bf16_2d(residual, "residual")
-    if splits is None and bn == 0:
+    if pair is None:
+        pair = PAIR_AUTO and M >= PAIR_MIN_TOKENS and bn == 0 and splits is None
+    pair = bool(pair) and F % 256 == 0 and (not x_t or M % 64 == 0)
+    if pair:
+        bn, splits = 256, 1
+    elif splits is None and bn == 0:
         bn, splits = plan_gemm(M, F, (Kx + 63) // 64 * 64, 0, False)
         if x_t:
             bn = max(bn, 64)
@@ -294,7 +317,7 @@ def gemm_t(x: torch.Tensor, w: torch.Tensor, *, x_t: bool = False, w_t: bool = F
     _rc(lib().tahb_gemm_t(_p(w), _p(x), _p(out), _p(residual), c_int(M), c_int(F), c_int(Kx), c_ll(w.stride(0)),
                           c_ll(x.stride(0)), c_ll(out.stride(0)), c_ll(residual.stride(0) if residual is not None else 0),
                           c_int(1 if w_t else 0), c_int(1 if x_t else 0), c_int(splits), c_int(bn),
-                          _p(status_word(x.device)), _stream()), "tahb_gemm_t")
+                          _p(status_word(x.device)), _stream(), c_int(1 if pair else 0)), "tahb_gemm_t")
     return out
 
 

@@ -34,12 +34,16 @@ def main():
         hard = (torch.rand(world, 2, 64, generator=g) < 0.3).long() + 1
         batches.append((ids.to(dev), hard.to(dev)))
     ok = True
-    for use_mc in (False, True):
+    # (multimem stores?, gradient checkpointing?): the checkpointed layers recompute their forward inside the backward
+    # pass, after the backward hook has made the unit resident again
+    for use_mc, ckpt in ((False, False), (True, False), (True, True)):
         losses, params, mem = {}, {}, {}
         for mode in ("zero2", "zero3"):
             torch.cuda.synchronize()
             model = tiny_tah(seed=0, dtype=torch.bfloat16).to(dev)
             model.train()
+            if ckpt:
+                model.gradient_checkpointing_enable()
             if mode == "zero3":
                 st = shard_model(model, dist.group.WORLD, dev, min_shard_numel=1 << 12, use_multicast=use_mc)
                 opt = FsdpAdamW(model, lr=1e-3, weight_decay=0.01, max_grad_norm=1.0, use_multicast=use_mc)
@@ -71,7 +75,7 @@ def main():
         good = perr < 2e-2 and lerr < 5e-2 and mem["zero3"] * world == full and stats["prefetched"] > 0
         ok = ok and good
         if rank == 0:
-            print(f"fsdp world={world} multicast={use_mc}: param err {perr:.2e}, loss err {lerr:.2e}, local shard "
+            print(f"fsdp world={world} multicast={use_mc} checkpointing={ckpt}: param err {perr:.2e}, loss err {lerr:.2e}, local shard "
                   f"{mem['zero3']} of {full} bytes, stats {stats} {'ok' if good else 'BAD'}")
         dist.barrier()
     flag = torch.tensor([1 if ok else 0], device=dev)

@@ -106,6 +106,51 @@ def test_gemm_swiglu_interleaved(M, I, K, R):
     assert torch.equal(out, dual)
 
 
+@pytest.mark.parametrize("M,F,K,R", [(256, 4096, 2048, 64), (1000, 512, 256, 0), (2048, 2048, 1024, 64), (77, 256, 128, 0)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_gemm_pair_mode(M, F, K, R, residual):
+    """Two output tiles per CTA sharing a 256-token activation tile (the large-token-count form), with the LoRA
+    K-extension and a residual, against fp32; bitwise equal to the one-tile form (same summation order)."""
+    Kc = _cuda()
+    x, w = _rand(M, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    x2 = _rand(M, R, seed=3) if R else None
+    w2 = _rand(F, R, scale=0.05, seed=4) if R else None
+    res = _rand(M, F, seed=5) if residual else None
+    out = Kc.gemm(x, w, x2=x2, w2=w2, residual=res, pair=True)
+    Kc.check_status()
+    ref = x.float() @ w.float().t()
+    if R:
+        ref = ref + x2.float() @ w2.float().t()
+    if residual:
+        ref = ref.to(torch.bfloat16).float() + res.float()
+    _close(out, ref, atol=3e-2, rtol=3e-2)
+    assert torch.equal(out, Kc.gemm(x, w, x2=x2, w2=w2, residual=res, pair=False, bn=256, splits=1))
+
+
+@pytest.mark.parametrize("M,I,K,R", [(2048, 1536, 512, 64), (300, 768, 256, 0)])
+def test_gemm_pair_mode_with_interleaved_swiglu(M, I, K, R):
+    Kc = _cuda()
+    x, w = _rand(M, K, seed=1), Kc.interleave_gate_up(_rand(2 * I, K, scale=K ** -0.5, seed=2))
+    x2 = _rand(M, R, seed=3) if R else None
+    w2 = Kc.interleave_gate_up(_rand(2 * I, R, scale=0.05, seed=4)) if R else None
+    a = Kc.gemm(x, w, x2=x2, w2=w2, swiglu_interleaved=True, pair=True)
+    b = Kc.gemm(x, w, x2=x2, w2=w2, swiglu_interleaved=True, pair=False)
+    Kc.check_status()
+    assert a.shape == (M, I) and torch.equal(a, b)
+
+
+@pytest.mark.parametrize("T,F,K", [(2048, 1024, 512), (4096, 2048, 2048)])
+def test_backward_gemms_pair_mode_equals_one_tile_form(T, F, K):
+    """The transposed-operand GEMMs (data and weight gradient) in pair mode give the same bits as the one-tile form."""
+    Kc = _cuda()
+    x, w = _rand(T, K, seed=1), _rand(F, K, scale=K ** -0.5, seed=2)
+    gy = _rand(T, F, seed=3, scale=F ** -0.5)
+    assert torch.equal(Kc.gemm_t(gy, w, w_t=True, pair=True), Kc.gemm_t(gy, w, w_t=True, pair=False, bn=256, splits=1))
+    assert torch.equal(Kc.gemm_t(gy, x, x_t=True, w_t=True, pair=True),
+                       Kc.gemm_t(gy, x, x_t=True, w_t=True, pair=False, bn=256, splits=1))
+    Kc.check_status()
+
+
 def test_gemm_strided_views():
     Kc = _cuda()
     big = _rand(64, 1024, seed=7)
