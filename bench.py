@@ -185,7 +185,7 @@ def run_ours(args):
             elif kind == "start":
                 barrier()
                 if i == 0:
-                    sampler.start()
+                    win[0]["wall0"] = time.time()
                 win[i]["tok0"] = int(s.tokens_done.item())
                 win[i]["e0"] = torch.cuda.Event(enable_timing=True)
                 win[i]["e1"] = torch.cuda.Event(enable_timing=True)
@@ -195,8 +195,9 @@ def run_ours(args):
                 barrier()
                 win[i]["tok1"] = int(s.tokens_done.item())
                 if i + 1 == len(win):
-                    win[i]["clocks"] = sampler.stop()
+                    win[i]["clocks"] = sampler.stop(win[0]["wall0"], time.time())
 
+    sampler.start()                                     # ahead of the call: nvidia-smi takes a while to deliver samples
     ids = prompts_host.to(dev, non_blocking=True)
     res = eng.generate(ids, None, max_new_tokens=NEW_TOKENS + slack, do_sample=False, max_ticks=total_ticks,
                        sync_every=1 << 30, on_tick=on_tick)

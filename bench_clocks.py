@@ -4,6 +4,7 @@ from __future__ import annotations
 import statistics
 import subprocess
 import threading
+import time
 
 
 class ClockSampler:
@@ -21,16 +22,20 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))       # arrival time of the sample on this host
 
-    def stop(self) -> dict:
+    def stop(self, t0: float = None, t1: float = None) -> dict:
+        """Summary of the samples; with ``t0`` / ``t1`` (``time.time()`` values) only of those that arrived inside
+        that window (widened by one sampling period), falling back to all samples of the run when the window is
+        shorter than a period.  nvidia-smi needs a few hundred milliseconds to deliver its first sample, so the
+        sampler is started ahead of a short timed region and the window selects the samples under load."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -40,7 +45,13 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        lines = list(self.lines)
+        scope = "all samples of the run"
+        if t0 is not None and t1 is not None:
+            inside = [(ts, ln) for ts, ln in lines if t0 - 0.1 <= ts <= t1 + 0.1]
+            if inside:
+                lines, scope = inside, "samples inside the timed windows"
+        for _, ln in lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -53,4 +64,4 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "scope": scope}

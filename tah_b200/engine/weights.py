@@ -69,7 +69,10 @@ class EngineWeights:
         self.tp = tp
         ws = 1 if tp is None else tp.world_size
         rk = 0 if tp is None else tp.rank
-        if cfg.num_key_value_heads % ws or cfg.intermediate_size % (ws * 128) and ws > 1:
+        # MLP channels per rank: whole 64-wide k-blocks for the down projection; the interleaved gate / up layout then
+        # has 2 * 64 rows per pair of k-blocks, i.e. whole 128-row tiles (the stacked layout needs 128 channels)
+        chan = 64 if os.environ.get("TAH_B200_SWIGLU", "interleaved") != "dual" else 128
+        if ws > 1 and (cfg.num_key_value_heads % ws or cfg.num_attention_heads % ws or cfg.intermediate_size % (ws * chan)):
             raise ValueError(f"tensor-parallel size {ws} does not divide the model's heads/channels")
         self.nq = cfg.num_attention_heads // ws
         self.nkv = cfg.num_key_value_heads // ws

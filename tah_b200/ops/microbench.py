@@ -70,7 +70,8 @@ def _copies(bytes_per_copy, want):
 
 def bench_gemm(a):
     M, F, Kd, R = a.m, a.f, a.k, a.r
-    wrows = 2 * F if a.swiglu else F
+    il = a.swiglu_interleaved
+    wrows = 2 * F if (a.swiglu or il) else F
     n = _copies(wrows * Kd * 2 + M * Kd * 2, a.copies)
     ws = [_rand(wrows, Kd, scale=Kd ** -0.5) for _ in range(n)]
     xs = [_rand(M, Kd) for _ in range(n)]
@@ -78,11 +79,22 @@ def bench_gemm(a):
     x2 = _rand(M, R) if R else None
     out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
     plan = dict(bn=a.bn, splits=a.splits) if a.bn else {}
-    fn = lambda i: K.gemm(xs[i % n], ws[i % n], out=out, x2=x2, w2=w2, swiglu=a.swiglu, **plan)
+    if a.pair is not None:
+        plan["pair"] = bool(a.pair)
+    if a.transposed == "dgrad":          # dx[M, F] = dy[M, Kd] w[Kd, F]: the weight is read transposed in place
+        fn = lambda i: K.gemm_t(xs[i % n], ws[i % n].view(Kd, wrows), w_t=True, out=out, **plan)
+    elif a.transposed == "wgrad":        # dw[M, F] = dy[Kd, M]^T x[Kd, F]: both operands transposed (reduction over Kd tokens)
+        gy = [_rand(Kd, M) for _ in range(n)]
+        fn = lambda i: K.gemm_t(gy[i % n], ws[i % n].view(Kd, wrows), x_t=True, w_t=True, out=out, **plan)
+    else:
+        fn = lambda i: K.gemm(xs[i % n], ws[i % n], out=out, x2=x2, w2=w2, swiglu=a.swiglu, swiglu_interleaved=il, **plan)
     t = _time(fn, a.iters, a.warmup)
     flops = 2.0 * M * wrows * (Kd + R)
     byts = (wrows * (Kd + R) + M * (Kd + R) + M * F) * 2
-    res = {"op": "gemm", "M": M, "F": F, "K": Kd, "R": R, "swiglu": a.swiglu, "plan_bn_splits": [a.bn, a.splits] if a.bn else K.plan_gemm(M, F, Kd, R, a.swiglu)}
+    auto_pair = K.PAIR_AUTO and M >= K.PAIR_MIN_TOKENS and not a.bn and wrows % 256 == 0 and not a.swiglu
+    res = {"op": "gemm", "M": M, "F": F, "K": Kd, "R": R, "swiglu": a.swiglu, "swiglu_interleaved": il,
+           "transposed": a.transposed, "pair": bool(a.pair) if a.pair is not None else auto_pair,
+           "plan_bn_splits": [a.bn, a.splits] if a.bn else K.plan_gemm(M, F, Kd, R, a.swiglu)}
     if a.cublas:
         ref = lambda i: torch.matmul(xs[i % n], ws[i % n].t())
         res["cublas_us"] = round(_time(ref, a.iters, a.warmup) * 1e6, 2)
@@ -336,6 +348,10 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--r", type=int, default=0, help="LoRA K-extension width")
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--swiglu-interleaved", action="store_true", help="SwiGLU on interleaved gate / up rows (one accumulator)")
+    ap.add_argument("--pair", type=int, default=None, help="1 / 0: force the two-tile (pair) form on / off (default: automatic)")
+    ap.add_argument("--transposed", default="", choices=["", "dgrad", "wgrad"],
+                    help="time the transposed-operand forms used by the backward pass (reduction length = --k)")
     ap.add_argument("--bn", type=int, default=0, help="force the token-tile width (with --splits) instead of the planner")
     ap.add_argument("--splits", type=int, default=1, help="split-K cluster size used with --bn")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on the same operands")
