@@ -579,6 +579,28 @@ __global__ void __launch_bounds__(256) lora_a_rows_kernel(const __nv_bfloat16* _
 // ---------------------------------------------------------------------------------------------
 // SwiGLU on a materialised [M, 2I] gate|up tensor (used where the GEMM epilogue fusion is off).
 // ---------------------------------------------------------------------------------------------
+// Vector form: 8 columns (16 bytes of gate, 16 of up) per thread; needs I, the row pitches and the bases aligned to 8.
+__global__ void swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int M, int I,
+                                  long long ld_in, long long ld_out) {
+  const int vpr = I / 8;
+  const long long n = (long long)M * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vpr), c = (int)(i % vpr) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gu + (size_t)r * ld_in + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gu + (size_t)r * ld_in + I + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      o2[j] = __floats2bfloat162_rn(bf16_round(silu(g.x)) * u.x, bf16_round(silu(g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * ld_out + c) = ov;
+  }
+}
+
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int M, int I,
                               long long ld_in, long long ld_out) {
   const long long n = (long long)M * I;
@@ -809,11 +831,17 @@ extern "C" int tahb_lora_a_rows_tp(const void* x, const void* A, void* T, const 
 extern "C" int tahb_swiglu(const void* gu, void* out, int M, int I, long long ld_in, long long ld_out,
                            cudaStream_t stream) {
   if (M <= 0) return 0;
-  const long long n = (long long)M * I;
+  const bool vec = I % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const long long n = vec ? (long long)M * (I / 8) : (long long)M * I;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  swiglu_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
-                                            reinterpret_cast<__nv_bfloat16*>(out), M, I, ld_in, ld_out);
+  if (vec)
+    swiglu_vec_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
+                                                  reinterpret_cast<__nv_bfloat16*>(out), M, I, ld_in, ld_out);
+  else
+    swiglu_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(gu),
+                                              reinterpret_cast<__nv_bfloat16*>(out), M, I, ld_in, ld_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -223,24 +223,30 @@ def main():
     # MLP channels divide by the group size
     over = {} if world <= 2 else dict(num_attention_heads=world, num_key_value_heads=world, head_dim=64,
                                       intermediate_size=128 * world)
-    model = tiny_tah(max_iter=2, dtype=torch.bfloat16, **over).to(dev).eval()
     gen = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 1024, (B, T), generator=gen).to(dev)
     tp = TensorParallel(dist.group.WORLD, dev, use_multicast=os.environ.get("TAH_B200_NVLS", "1") != "0")
-    eng = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, deep_fraction=1.0, tp=tp)
-    eng.hard_override = eng.make_bernoulli_override(B, (0.3,), seed=5)
-    out_tp = eng.generate(ids, None, max_new_tokens=n_new, do_sample=False)
-    solo = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, deep_fraction=1.0)
-    solo.hard_override = eng.hard_override
-    out_1 = solo.generate(ids, None, max_new_tokens=n_new, do_sample=False)
-    a, b = torch.tensor(out_tp.tokens), torch.tensor(out_1.tokens)
-    # identical until the first bf16-rounding flip of a row; compare the agreeing prefix length
-    agree = (a == b).float().mean().item()
-    first_tok = (a[:, :4] == b[:, :4]).float().mean().item()
-    good = first_tok >= 0.9 and agree >= 0.6
-    ok = ok and good
-    if rank == 0:
-        print(f"engine TP{world} vs 1 GPU: token agreement {agree:.2f}, first-4 agreement {first_tok:.2f} {'ok' if good else 'BAD'}")
+    # second variant: MLP channels per rank that are whole 64-wide k-blocks but not whole 128-row tiles (the
+    # Qwen3-4B shapes at eight ranks: 9728 / 8 = 1216)
+    variants = [over, dict(over, intermediate_size=192 * world)]
+    for vi, ov in enumerate(variants):
+        model = tiny_tah(max_iter=2, dtype=torch.bfloat16, **ov).to(dev).eval()
+        eng = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, deep_fraction=1.0, tp=tp)
+        eng.hard_override = eng.make_bernoulli_override(B, (0.3,), seed=5)
+        out_tp = eng.generate(ids, None, max_new_tokens=n_new, do_sample=False)
+        solo = TaHEngine(model, max_rows=B, max_seq_len=T + n_new + 2, deep_fraction=1.0)
+        solo.hard_override = eng.hard_override
+        out_1 = solo.generate(ids, None, max_new_tokens=n_new, do_sample=False)
+        a, b = torch.tensor(out_tp.tokens), torch.tensor(out_1.tokens)
+        # identical until the first bf16-rounding flip of a row; compare the agreeing prefix length
+        agree = (a == b).float().mean().item()
+        first_tok = (a[:, :4] == b[:, :4]).float().mean().item()
+        good = first_tok >= 0.9 and agree >= 0.6
+        ok = ok and good
+        if rank == 0:
+            print(f"engine TP{world} vs 1 GPU (MLP channels per rank {model.config.intermediate_size // world}): token agreement "
+                  f"{agree:.2f}, first-4 agreement {first_tok:.2f} {'ok' if good else 'BAD'}")
+        del eng, solo
     # ---- learned decider under TP: hidden-state taps broadcast by the owner kernels == the all-gather form ----
     H = 256
     dkw = dict(topk=100, hidden_states_size=H, hidden_states_layer_nums=[0, 1, 3, 4], hidden_dims=[128, 128],
