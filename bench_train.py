@@ -43,6 +43,7 @@ def add_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--decider", default="oracle-mlp", choices=["oracle-mlp", "label", "mlp"])
     ap.add_argument("--lora-rank", type=int, default=64)
     ap.add_argument("--strategy", default="zero2", choices=["zero2", "zero3"])
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (layers sharded over groups of adjacent ranks)")
     ap.add_argument("--kernel-table", default=None,
                     help="after the timed steps, run one more step under the PyTorch profiler and write the kernels' "
                          "device-time table to this file (rank 0)")
@@ -93,7 +94,16 @@ def run(a, steps: int, warmup: int) -> dict:
     dev = torch.device("cuda", local)
     hard_rate = a.hard_rate if a.hard_rate is not None else (1.0 if a.decider == "label" else 0.06)
     model, cfg = build_train_model(a, dev)
-    if a.strategy == "zero3" and world > 1:
+    tp_size = int(getattr(a, "tp", 1) or 1)
+    dp_world, dp_rank = world, rank
+    if tp_size > 1:
+        from tah_b200.parallel.tp_train import TPOptimizer, shard_model_tp, tp_dp_groups
+        from tah_b200.parallel.zero import ZeroAdamW
+        tp_group, dp_group, _, dp_rank = tp_dp_groups(tp_size)
+        dp_world = world // tp_size
+        st = shard_model_tp(model, tp_group)
+        opt = TPOptimizer(ZeroAdamW(model.parameters(), group=dp_group, lr=2e-5, weight_decay=0.01, max_grad_norm=1.0), st)
+    elif a.strategy == "zero3" and world > 1:
         from tah_b200.parallel.fsdp import FsdpAdamW, shard_model
         shard_model(model, dist.group.WORLD, dev)
         opt = FsdpAdamW(model, lr=2e-5, weight_decay=0.01, max_grad_norm=1.0)
@@ -101,7 +111,7 @@ def run(a, steps: int, warmup: int) -> dict:
         from tah_b200.parallel.zero import ZeroAdamW
         opt = ZeroAdamW(model.parameters(), lr=2e-5, weight_decay=0.01, max_grad_norm=1.0)
 
-    g = torch.Generator().manual_seed(100 + rank)
+    g = torch.Generator().manual_seed(100 + dp_rank)          # ranks of one tensor-parallel group see the same batch
     V = cfg.vocab_size
     h2d = 0
 
@@ -154,7 +164,7 @@ def run(a, steps: int, warmup: int) -> dict:
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms, wall_ms = float(ms[0]), float(ms[1])
-    toks = steps * a.accum * a.seq * world
+    toks = steps * a.accum * a.seq * dp_world
     rec = {
         "metric": ("TaH-plus-1.7B" if a.train_model == "tah-plus-1.7b" else a.train_model) + " SFT training tokens/s", "value": round(toks / (ms / 1e3), 1), "unit": "tokens/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / max(1, steps), 1),
@@ -164,12 +174,13 @@ def run(a, steps: int, warmup: int) -> dict:
         "loss": round(loss, 4), "dtype": "bf16 (fp32 master weights)", "clocks": clocks,
         "data": "synthetic", "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         "config": {"model": a.train_model, "seq_len": a.seq, "micro_batches_per_step": a.accum,
-                   "global_batch": a.accum * world, "hard_rate": hard_rate, "decider": a.decider,
+                   "global_batch": a.accum * dp_world, "hard_rate": hard_rate, "decider": a.decider,
                    "loss": "CE" if a.decider == "label" else "CE + decider BCE",
                    "second_iteration_on": "labelled tokens" if a.decider == "label" else
                                           ("every token" if a.decider == "oracle-mlp" else "tokens the decider picks"),
                    "lora_rank": a.lora_rank, "max_iter": 2,
-                   "parallelism": (f"fsdp{world} (zero3: sharded parameters, gradients, optimizer state)"
+                   "parallelism": (f"tp{tp_size} x dp{dp_world} (layers sharded over the tensor-parallel group, zero2 over the data-parallel group)"
+                                   if tp_size > 1 else f"fsdp{world} (zero3: sharded parameters, gradients, optimizer state)"
                                    if a.strategy == "zero3" and world > 1 else f"dp{world} + sharded AdamW (zero2)"),
                    "grad_checkpointing": bool(a.checkpoint)}}
     del opt, model

@@ -132,7 +132,8 @@ def _synthetic(n: int, device, max_iter: int):
 def _parallel_config(path):
     """Launch-topology file (``script/recipes/parallel_configs/zero{2,3}.yaml``; the reference's accelerate /
     DeepSpeed files, ``script/recipes/accelerate_configs/zero2.yaml:3-16``, play this role there).  Keys read:
-    ``strategy`` (zero2 | zero3), ``nvls`` (use NVLS multimem in the fused collectives)."""
+    ``strategy`` (zero2 | zero3), ``tp_size`` (tensor-parallel group size, layers sharded over adjacent ranks),
+    ``nvls`` (use NVLS multimem in the fused collectives)."""
     if not path:
         return {}
     with open(path, encoding="utf-8") as fh:
@@ -176,6 +177,8 @@ def main(config_path: str, synthetic: int = 0, max_steps: int = -1, parallel_con
     pc = _parallel_config(parallel_config or tc.pop("parallel_config", None))
     if pc.get("strategy") and "strategy" not in tc:
         tc["strategy"] = pc["strategy"]
+    if pc.get("tp_size") and "tp_size" not in tc:
+        tc["tp_size"] = int(pc["tp_size"])
     args = TaHTrainingArguments.from_dict(dict(tc, output_dir=out_dir))
     if max_steps > 0:
         args.max_steps = max_steps

@@ -136,12 +136,14 @@ class ZeroAdamW:
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0, lr: Optional[float] = None,
-             extra_norm_sq: Optional[torch.Tensor] = None) -> torch.Tensor:
+             extra_norm_sq: Optional[torch.Tensor] = None, norm_hook=None) -> torch.Tensor:
         """One update.  ``grad_scale`` multiplies the rank-averaged gradient (e.g. 1 for losses already
         normalised over the accumulation window).  ``extra_norm_sq`` (optional device scalar): this rank's
         share of the squared gradient norm of parameters managed elsewhere (parameter-sharded units); it joins
-        the all-reduce, so clipping uses the norm over both sets.  Returns the global gradient norm (device
-        tensor); ``self.norm_sq`` holds its square."""
+        the all-reduce, so clipping uses the norm over both sets.  ``norm_hook(self)`` (optional) is called once
+        the rank-averaged, scaled gradient shard is in ``self.gshard`` (flat elements ``[self.lo, self.hi)``) and
+        returns a further share of the squared norm (tensor-parallel training adds the other ranks' shards there).
+        Returns the global gradient norm (device tensor); ``self.norm_sq`` holds its square."""
         self._collect_stray_grads()
         self.step_count += 1
         lr = self.lr if lr is None else lr
@@ -149,11 +151,11 @@ class ZeroAdamW:
         bc1, bc2 = 1.0 - b1 ** self.step_count, 1.0 - b2 ** self.step_count
         scale = grad_scale / self.world
         if self.cuda:
-            return self._step_cuda(scale, lr, b1, b2, bc1, bc2, extra_norm_sq)
-        return self._step_torch(scale, lr, b1, b2, bc1, bc2, extra_norm_sq)
+            return self._step_cuda(scale, lr, b1, b2, bc1, bc2, extra_norm_sq, norm_hook)
+        return self._step_torch(scale, lr, b1, b2, bc1, bc2, extra_norm_sq, norm_hook)
 
     # ---- CUDA: fused kernels over peer memory -------------------------------------------------
-    def _step_cuda(self, scale, lr, b1, b2, bc1, bc2, extra_norm_sq=None):
+    def _step_cuda(self, scale, lr, b1, b2, bc1, bc2, extra_norm_sq=None, norm_hook=None):
         import ctypes
         from tah_b200.ops import cuda as K
         lib = K.lib()
@@ -180,6 +182,8 @@ class ZeroAdamW:
         launch(0)
         if extra_norm_sq is not None:
             self.norm_sq += extra_norm_sq.to(self.norm_sq.dtype)
+        if norm_hook is not None:
+            self.norm_sq += norm_hook(self).to(self.norm_sq.dtype).reshape(1)
         if self.world > 1:
             dist.all_reduce(self.norm_sq, group=self.group)
         launch(1)
@@ -187,7 +191,7 @@ class ZeroAdamW:
         return self.last_grad_norm
 
     # ---- CPU / generic: PyTorch statement of the same algorithm --------------------------------
-    def _step_torch(self, scale, lr, b1, b2, bc1, bc2, extra_norm_sq=None):
+    def _step_torch(self, scale, lr, b1, b2, bc1, bc2, extra_norm_sq=None, norm_hook=None):
         g_full = self.flat_grad.float()
         if self.world > 1:
             dist.all_reduce(g_full, group=self.group)
@@ -195,6 +199,9 @@ class ZeroAdamW:
         nsq = (g * g).sum().reshape(1)
         if extra_norm_sq is not None:
             nsq = nsq + extra_norm_sq.to(nsq.dtype).reshape(1)
+        if norm_hook is not None:
+            self.gshard = g
+            nsq = nsq + norm_hook(self).to(nsq.dtype).reshape(1)
         if self.world > 1:
             dist.all_reduce(nsq, group=self.group)
         self.norm_sq = nsq

@@ -71,6 +71,9 @@ class TaHTrainingArguments:
     remove_unused_columns: bool = False
     # parallel strategy: "zero2" (replicated bf16 parameters, sharded fp32 state) or "zero3" (parameters sharded too)
     strategy: str = "zero2"
+    # tensor-parallel size: the decoder layers are sharded over groups of tp_size adjacent ranks
+    # (tah_b200.parallel.tp_train), the remaining world / tp_size ranks are data parallel (zero2 over that group)
+    tp_size: int = 1
     # failure detection (multi-rank jobs): every rank bumps a heartbeat counter in the rendezvous store; before each
     # optimizer step the peers' counters are checked and a rank whose counter stood still for heartbeat_timeout_s is
     # reported as a RankFailure; a step that runs longer than step_timeout_s (> 0) raises StepTimeout
@@ -134,6 +137,7 @@ class CustomTaHTrainer:
         self.dist_on = dist.is_available() and dist.is_initialized()
         self.rank = dist.get_rank() if self.dist_on else 0
         self.world = dist.get_world_size() if self.dist_on else 1
+        self.dp_rank, self.dp_world = self.rank, self.world      # data-parallel coordinates (differ under TP)
         self.optimizer: Optional[ZeroAdamW] = None
         self._log_file = None
         self._wandb = None
@@ -172,9 +176,10 @@ class CustomTaHTrainer:
             order = torch.randperm(n, generator=g).tolist()
         else:
             order = list(range(n))
-        per_rank = math.ceil(n / self.world) if not self.args.dataloader_drop_last else n // self.world
-        order = (order + order[: per_rank * self.world - n])[: per_rank * self.world] if per_rank * self.world > n else order
-        mine = order[self.rank::self.world]
+        dw = self.dp_world
+        per_rank = math.ceil(n / dw) if not self.args.dataloader_drop_last else n // dw
+        order = (order + order[: per_rank * dw - n])[: per_rank * dw] if per_rank * dw > n else order
+        mine = order[self.dp_rank::dw]
         for i in range(0, len(mine), batch_size):
             idx = mine[i:i + batch_size]
             if len(idx) < batch_size and self.args.dataloader_drop_last:
@@ -187,7 +192,7 @@ class CustomTaHTrainer:
         return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
 
     def steps_per_epoch(self) -> int:
-        per_rank = math.ceil(len(self.train_dataset) / self.world)
+        per_rank = math.ceil(len(self.train_dataset) / self.dp_world)
         micro = math.ceil(per_rank / self.args.per_device_train_batch_size)
         return max(1, micro // self.args.gradient_accumulation_steps)
 
@@ -195,13 +200,27 @@ class CustomTaHTrainer:
     def create_optimizer(self):
         """``strategy: zero2`` - replicated bf16 parameters, sharded fp32 state (:class:`ZeroAdamW`);
         ``strategy: zero3`` - parameters sharded as well: the model is cut into units whose weights are gathered
-        layer by layer (:mod:`tah_b200.parallel.fsdp`).  One process falls back to the first form."""
+        layer by layer (:mod:`tah_b200.parallel.fsdp`).  One process falls back to the first form.
+        ``tp_size > 1``: the layers are sharded over tensor-parallel groups first (:mod:`tah_b200.parallel.tp_train`)
+        and the optimizer runs zero2 over the data-parallel group of the rank."""
         a = self.args
         kw = dict(lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                   weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm or 0.0)
         no_decay = [p for n, p in self.model.named_parameters()
                     if p.dim() < 2 or n.endswith("bias") or "norm" in n.lower() or n.endswith("threshold")]
-        if str(a.strategy).lower() in ("zero3", "fsdp") and self.dist_on and self.world > 1:
+        if int(getattr(a, "tp_size", 1) or 1) > 1:
+            if not self.dist_on or self.world % int(a.tp_size):
+                raise ValueError(f"tp_size {a.tp_size} needs a world size that is a multiple of it")
+            if str(a.strategy).lower() in ("zero3", "fsdp"):
+                raise NotImplementedError("tp_size > 1 runs with strategy zero2 (parameter sharding is not combined)")
+            from tah_b200.parallel.tp_train import TPOptimizer, shard_model_tp, tp_dp_groups
+            tp_group, dp_group, _, self.dp_rank = tp_dp_groups(int(a.tp_size))
+            self.dp_world = self.world // int(a.tp_size)
+            st = getattr(self.model, "_tp_train", None) or shard_model_tp(self.model, tp_group)
+            no_decay = [p for n, p in self.model.named_parameters()
+                        if p.dim() < 2 or n.endswith("bias") or "norm" in n.lower() or n.endswith("threshold")]
+            self.optimizer = TPOptimizer(ZeroAdamW(self.model.parameters(), group=dp_group, no_decay=no_decay, **kw), st)
+        elif str(a.strategy).lower() in ("zero3", "fsdp") and self.dist_on and self.world > 1:
             from tah_b200.parallel.fsdp import FsdpAdamW, shard_model
             if getattr(self.model, "_fsdp", None) is None:
                 shard_model(self.model, dist.group.WORLD, self.model.device)
@@ -220,11 +239,11 @@ class CustomTaHTrainer:
     # ---- train ----------------------------------------------------------------------------------
     def train(self, resume_from_checkpoint: Optional[str] = None):
         a = self.args
-        torch.manual_seed(a.seed + self.rank)
         if a.gradient_checkpointing and hasattr(self.model, "gradient_checkpointing_enable"):
             self.model.gradient_checkpointing_enable()
         if self.optimizer is None:
             self.create_optimizer()
+        torch.manual_seed(a.seed + self.dp_rank)        # ranks of one tensor-parallel group draw the same dropout masks
         spe = self.steps_per_epoch()
         self.state.max_steps = a.max_steps if a.max_steps and a.max_steps > 0 else int(math.ceil(spe * a.num_train_epochs))
         if resume_from_checkpoint:
@@ -308,7 +327,7 @@ class CustomTaHTrainer:
                     self._check_device_status()
                 if self.metrics is not None:
                     dt = time.perf_counter() - t_step
-                    rec = {"step_s": round(dt, 4), "tokens": n_tok, "tokens_per_s": round(n_tok * self.world / max(dt, 1e-9), 1),
+                    rec = {"step_s": round(dt, 4), "tokens": n_tok, "tokens_per_s": round(n_tok * self.dp_world / max(dt, 1e-9), 1),
                            "loss": step_loss}
                     if self.model.device.type == "cuda":
                         rec["peak_mem_gb"] = round(torch.cuda.max_memory_allocated(self.model.device) / 2 ** 30, 2)
@@ -363,7 +382,7 @@ class CustomTaHTrainer:
     def _save(self, output_dir: Optional[str] = None, state_dict=None):
         output_dir = output_dir or self.args.output_dir
         os.makedirs(output_dir, exist_ok=True)
-        fsdp = getattr(self.model, "_fsdp", None)
+        fsdp = getattr(self.model, "_fsdp", None) or getattr(self.model, "_tp_train", None)
         if fsdp is not None:
             # parameter-sharded model: every rank takes part in gathering the full 16-bit weights, rank 0 writes
             with fsdp.materialized():

@@ -54,12 +54,24 @@ def case_trainer(out):
         hard = [1] * 24
         hard[7] = 2
         rows.append(dict(input_ids=ids, attention_mask=[1] * 24, labels=[-100] * 3 + ids[3:], iter_count_labels=hard))
+    tp = int(os.environ.get("TAH_TEST_TP", "1"))          # tensor-parallel size: world / tp data-parallel replicas
+    dp = world // tp
     args = TaHTrainingArguments(output_dir=os.environ["TAH_TEST_OUT"], per_device_train_batch_size=1,
-                                gradient_accumulation_steps=4 // world if world <= 4 else 1, learning_rate=1e-3,
-                                max_grad_norm=1.0, num_train_epochs=1, logging_steps=1, save_strategy="no", seed=0)
+                                gradient_accumulation_steps=4 // dp if dp <= 4 else 1, learning_rate=1e-3,
+                                max_grad_norm=1.0, num_train_epochs=1, logging_steps=1, save_strategy="no", seed=0,
+                                tp_size=tp)
     tr = CustomTaHTrainer(model, args, rows, None, data_collator=CustomTaHDataCollator(None, pad_token_id=0))
     tr.train()
     out.update(losses=[h["loss"] for h in tr.state.log_history if "loss" in h], steps=tr.state.global_step)
+    if tp > 1:
+        # saving gathers the shards: the written checkpoint has the full shapes again
+        tr.save_model(os.path.join(os.environ["TAH_TEST_OUT"], "final"))
+        dist.barrier()
+        if rank == 0:
+            from safetensors import safe_open
+            with safe_open(os.path.join(os.environ["TAH_TEST_OUT"], "final", "model.safetensors"), "pt") as fh:
+                out.update(saved_q_rows=int(fh.get_tensor("model.layers.0.self_attn.q_proj.weight").shape[0]),
+                           saved_down_cols=int(fh.get_tensor("model.layers.0.mlp.down_proj.weight").shape[1]))
 
 
 def case_fsdp(out):
@@ -106,6 +118,63 @@ def case_fsdp(out):
     dl = max(abs(a - b) for a, b in zip(losses["zero2"], losses["zero3"]))
     out.update(param_err=err, loss_err=dl, losses=losses["zero3"])
     assert err < 2e-5 and dl < 1e-4, (err, dl)
+
+
+def case_tp_train(out):
+    """Tensor-parallel training (heads / MLP channels of every layer sharded over the group) == the same steps on
+    the full model: losses, clipped gradient norm and final (gathered) parameters.  World 2: pure TP; world 4: two
+    data-parallel replicas of a TP pair, the same global batch as two unsharded ranks."""
+    from tah_b200.parallel.tp_train import TPOptimizer, shard_model_tp, tp_dp_groups
+    from tah_b200.parallel.zero import ZeroAdamW
+    from tests.helpers import tiny_tah
+    rank, world = dist.get_rank(), dist.get_world_size()
+    tp_group, dp_group, tp_rank, dp_rank = tp_dp_groups(2)
+    dp = world // 2
+    g = torch.Generator().manual_seed(5)
+    batches = []
+    for _ in range(3):
+        ids = torch.randint(0, 1024, (dp, 2, 24), generator=g)
+        hard = (torch.rand(dp, 2, 24, generator=g) < 0.3).long() + 1
+        batches.append((ids, hard))
+    losses, params, norms = {}, {}, {}
+    for mode in ("full", "tp"):
+        model = tiny_tah(seed=0, max_iter=2)
+        model.train()
+        if mode == "tp":
+            st = shard_model_tp(model, tp_group)
+            opt = TPOptimizer(ZeroAdamW(model.parameters(), group=dp_group, lr=1e-3, weight_decay=0.01, max_grad_norm=0.3), st)
+            out.update(sharded=len(st.sharded), partial=len(st.partial_grad),
+                       local_fraction=sum(p.numel() for p, _, _ in st.sharded) / max(1, sum(
+                           st.gather_full(p, how, sp).numel() for p, how, sp in st.sharded)))
+        else:
+            opt = ZeroAdamW(model.parameters(), group=dp_group, lr=1e-3, weight_decay=0.01, max_grad_norm=0.3)
+        ls, ns = [], []
+        for ids, hard in batches:
+            for micro in range(2):
+                o = model(ids[dp_rank, micro:micro + 1], labels=ids[dp_rank, micro:micro + 1],
+                          iter_count_labels=hard[dp_rank, micro:micro + 1])
+                (o.loss / 2).backward()
+                ls.append(float(o.loss))
+            ns.append(float(opt.step()))
+            opt.zero_grad()
+        losses[mode], norms[mode] = ls, ns
+        if mode == "tp":
+            with st.materialized():
+                params[mode] = {n: p.detach().clone() for n, p in model.named_parameters()}
+                # the gathered model is a valid full model again: one forward must run
+                model.eval()
+                with torch.no_grad():
+                    for h in st.hooks:
+                        h.remove()
+                    full_loss = float(model(batches[0][0][0, :1], labels=batches[0][0][0, :1]).loss)
+            out.update(full_loss_after=full_loss)
+        else:
+            params[mode] = {n: p.detach().clone() for n, p in model.named_parameters()}
+    err = max(float((params["full"][n] - params["tp"][n]).abs().max()) for n in params["full"])
+    dl = max(abs(a - b) for a, b in zip(losses["full"], losses["tp"]))
+    dn = max(abs(a - b) / max(a, 1e-6) for a, b in zip(norms["full"], norms["tp"]))
+    out.update(param_err=err, loss_err=dl, norm_err=dn, norms=norms["tp"], losses=losses["tp"])
+    assert err < 5e-5 and dl < 1e-4 and dn < 1e-4, (err, dl, dn)
 
 
 def case_heartbeat(out):

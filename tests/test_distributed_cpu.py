@@ -61,3 +61,29 @@ def test_heartbeat_detects_a_rank_that_left(tmp_path):
 def test_short_group_timeout_ends_a_collective_with_an_error(tmp_path):
     res, ranks = _run("collective_timeout", 2, tmp_path, 29715, timeout=120)
     assert ranks[0]["raised"] is True and ranks[0]["seconds"] < 30
+
+
+@pytest.mark.parametrize("world,port", [(2, 29721), (4, 29722)])
+def test_tensor_parallel_training_matches_unsharded(tmp_path, world, port):
+    """Layers sharded over a TP pair (world 2: pure TP, world 4: TP x DP) train like the unsharded model."""
+    res, ranks = _run("tp_train", world, tmp_path, port, timeout=400)
+    assert res.returncode == 0, res.stderr[-3000:]
+    r0 = ranks[0]
+    assert r0["param_err"] < 5e-5 and r0["loss_err"] < 1e-4 and r0["norm_err"] < 1e-4
+    assert r0["sharded"] > 0 and r0["partial"] > 0 and abs(r0["local_fraction"] - 0.5) < 1e-6
+    assert min(r0["norms"]) > 0.3                      # clipping was active, so the norm correction mattered
+
+
+def test_trainer_with_tensor_parallel_pairs_follows_the_same_loss_curve(tmp_path):
+    """``tp_size: 2`` in the trainer (world 2 = one TP pair, world 4 = two pairs, data parallel) against one process;
+    the saved checkpoint holds the gathered full tensors."""
+    res1, r1 = _run("trainer", 1, tmp_path, 29731)
+    res2, r2 = _run("trainer", 2, tmp_path, 29732, env={"TAH_TEST_TP": "2"})
+    res4, r4 = _run("trainer", 4, tmp_path, 29733, env={"TAH_TEST_TP": "2"}, timeout=400)
+    for res in (res1, res2, res4):
+        assert res.returncode == 0, res.stderr[-3000:]
+    a, b, c = r1[0]["losses"], r2[0]["losses"], r4[0]["losses"]
+    assert len(a) == len(b) == len(c) == 2
+    assert abs(a[0] - b[0]) < 1e-4 and abs(a[1] - b[1]) < 5e-3
+    assert abs(a[0] - c[0]) < 1e-4 and abs(a[1] - c[1]) < 5e-3
+    assert r2[0]["saved_q_rows"] == 256 and r2[0]["saved_down_cols"] == 768

@@ -1,4 +1,5 @@
-"""Parameter-sharded training (ZeRO-3) on 2 and 4 GPUs against the replicated ZeRO-2 optimizer."""
+"""Parameter-sharded training (ZeRO-3) and tensor-parallel training on 2 and 4 GPUs against the replicated ZeRO-2
+optimizer."""
 import os
 import subprocess
 import sys
@@ -20,3 +21,15 @@ def test_fsdp_step_matches_zero2(world):
     sys.stdout.write(res.stdout[-4000:])
     sys.stderr.write(res.stderr[-4000:])
     assert res.returncode == 0 and "FSDP_WORKER_PASS" in res.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_training_matches_unsharded(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29660 + world), os.path.join(ROOT, "tests", "tp_train_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    sys.stdout.write(res.stdout[-4000:])
+    sys.stderr.write(res.stderr[-4000:])
+    assert res.returncode == 0 and "TP_TRAIN_WORKER_PASS" in res.stdout
