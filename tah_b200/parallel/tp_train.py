@@ -277,5 +277,9 @@ class TPOptimizer:
     def zero_grad(self, *a, **k):
         return self.inner.zero_grad(*a, **k)
 
+    def accumulate(self):
+        if hasattr(self.inner, "accumulate"):
+            self.inner.accumulate()
+
     def __getattr__(self, name):
         return getattr(self.inner, name)

@@ -319,6 +319,8 @@ class CustomTaHTrainer:
                             out = self.model(**b, num_items_in_batch=n_items)
                         with nvtx_range("train/backward"):
                             out.loss.backward()
+                        if accum > 1 and hasattr(self.optimizer, "accumulate"):
+                            self.optimizer.accumulate()          # fp32 sum over the window, one rounding at the step
                         step_loss += float(out.loss.detach())
                     lr = self._lr_at(self.state.global_step)
                     with nvtx_range("train/optimizer"):

@@ -362,3 +362,29 @@ def test_zero_adamw_no_decay_group_matches_torch_param_groups():
         ropt.zero_grad()
     for (n, a), b in zip(net.named_parameters(), ref.parameters()):
         torch.testing.assert_close(a, b, atol=1e-6, rtol=1e-5, msg=n)
+
+
+def test_zero_adamw_accumulates_micro_batch_gradients_in_fp32():
+    """``accumulate()`` after every backward: the window's gradient is summed in fp32 and rounded to bf16 once, so
+    sixteen micro-batches whose gradients differ by orders of magnitude keep their small terms."""
+    from tah_b200.parallel.zero import ZeroAdamW
+    torch.manual_seed(0)
+    n = 4096
+    grads = [torch.randn(n) * (1.0 if i == 0 else 2e-3) for i in range(16)]
+    exact = torch.stack(grads).sum(0)
+
+    def run(use_acc):
+        p = torch.nn.Parameter(torch.zeros(n, dtype=torch.bfloat16))
+        opt = ZeroAdamW([p], lr=1e-3, weight_decay=0.0, max_grad_norm=0.0)
+        for g in grads:
+            p.grad.add_(g.to(torch.bfloat16))            # what autograd does: accumulate into the 16-bit buffer
+            if use_acc:
+                opt.accumulate()
+        opt._collect_stray_grads()
+        opt._flush_accumulator()
+        return opt.flat_grad[:n].float().clone()
+
+    err_plain = (run(False) - exact).abs().mean()
+    err_acc = (run(True) - exact).abs().mean()
+    assert err_acc < 0.5 * err_plain                      # one rounding instead of sixteen
+    assert err_acc < 2.5e-3                                # bf16 rounding of values of order one
