@@ -13,6 +13,7 @@ per-sample time is the batch time divided by the batch size.
 from __future__ import annotations
 
 import gc
+import os
 import time
 from typing import Callable, Dict, List, Tuple
 
@@ -101,6 +102,22 @@ def setup_tah(config: Dict, model_path: str, tokenizer, tp_size: int = 1):
         (_, texts), secs = time_inference(TaHForCasualLM_generate, model, tokenizer, inputs, **gen_kw)
         return [(t, secs / max(1, len(prompts))) for t in texts]
 
+    def serve_all(prompts: List[str], rows: int) -> List[Tuple[str, float]]:
+        """All prompts of a job through the engine's continuous batching: ``rows`` requests decode at a time and a
+        request that finishes hands its row (and KV pages) to the next queued one, instead of whole batches waiting
+        for their longest answer (reasoning benchmarks have answers of 100 to 4096 tokens).  CUDA only."""
+        from tah_b200.engine import get_engine
+        eng = get_engine(model, max_rows=max(int(rows), 1))
+        ids = [torch.tensor(tokenizer.encode(p), dtype=torch.long) for p in prompts]
+        kw = {k: gen_kw[k] for k in ("max_new_tokens", "do_sample", "temperature", "top_p", "top_k", "min_p")}
+        (tokens, stats), secs = time_inference(eng.serve, ids, rows=int(rows),
+                                               eos_token_id=getattr(tokenizer, "eos_token_id", None), **kw)
+        per = secs / max(1, len(prompts))
+        return [(tokenizer.decode(t) if t else "", per) for t in tokens]
+
+    if model.device.type == "cuda" and os.environ.get("TAH_B200_FORCE_TORCH", "0") != "1" \
+            and bool(config.get("continuous_batching", True)):
+        infer.serve_all = serve_all
     return model, infer
 
 

@@ -179,9 +179,12 @@ def run_single_job(*, config: Dict, combined_dataset_name: str, output_dir: str,
     with open(results_file, "w", newline="", encoding="utf-8") as fh:
         csv.DictWriter(fh, fieldnames=_CSV_FIELDS).writeheader()
     rows: List[dict] = []
+    # a backend with continuous batching takes the whole job at once (batch_size = rows decoding at a time)
+    serve_all = getattr(infer, "serve_all", None)
+    all_outputs = serve_all(prompts, bs) if serve_all is not None and len(prompts) > bs else None
     for b in range(math.ceil(len(prompts) / bs)):
         lo, hi = b * bs, min(len(prompts), (b + 1) * bs)
-        outputs = infer(prompts[lo:hi])
+        outputs = all_outputs[lo:hi] if all_outputs is not None else infer(prompts[lo:hi])
         with open(results_file, "a", newline="", encoding="utf-8") as fh:
             writer = csv.DictWriter(fh, fieldnames=_CSV_FIELDS)
             for j, (text, secs) in enumerate(outputs):

@@ -287,3 +287,49 @@ def test_serve_admits_requests_into_freed_rows_and_matches_generate():
     assert solo.bucket_rows(3) == 4 and len(a.tokens) == 3 and a.tokens == b.tokens
     assert solo.graph_captures == caps                     # the 3- and the 4-request calls share one captured graph
     assert c.tokens[:3] == a.tokens
+
+
+class _WordTok:
+    """Minimal tokenizer: whitespace-separated integers are the token ids."""
+    eos_token_id = 1023
+    pad_token_id = 0
+    padding_side = "left"
+
+    def encode(self, text):
+        return [int(w) for w in text.split()]
+
+    def decode(self, ids, **_):
+        return " ".join(str(int(i)) for i in ids)
+
+    def __call__(self, prompts, return_tensors="pt", padding=True):
+        rows = [self.encode(p) for p in prompts]
+        T = max(len(r) for r in rows)
+        ids = torch.zeros(len(rows), T, dtype=torch.long)
+        mask = torch.zeros(len(rows), T, dtype=torch.long)
+        for i, r in enumerate(rows):
+            ids[i, T - len(r):] = torch.tensor(r)
+            mask[i, T - len(r):] = 1
+        return {"input_ids": ids, "attention_mask": mask}
+
+
+def test_tah_eval_backend_continuous_batching_matches_static_batches(tmp_path):
+    """The ``tah`` eval backend on a saved checkpoint: ``serve_all`` (continuous batching over the whole job) gives
+    the texts of the static-batch ``infer`` path."""
+    from tah_b200.evaluate.backends import setup_tah
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16)
+    model.save_pretrained(str(tmp_path / "ckpt"))
+    tok = _WordTok()
+    cfg = {"max_new_tokens": 10, "temperature": 0.0, "dtype": "bfloat16"}
+    m, infer = setup_tah(cfg, str(tmp_path / "ckpt"), tok)
+    assert m.device.type == "cuda" and hasattr(infer, "serve_all")
+    g = torch.Generator().manual_seed(7)
+    prompts = [" ".join(str(int(x)) for x in torch.randint(2, 1000, (n,), generator=g)) for n in (7, 19, 12, 25, 5)]
+    served = infer.serve_all(prompts, rows=2)
+    static = infer(prompts[:2]) + infer(prompts[2:4]) + infer(prompts[4:])
+    assert len(served) == len(static) == 5
+    same = 0
+    for (a, _), (b, _) in zip(served, static):
+        ta, tb = a.split(), b.split()
+        assert 0 < len(ta) <= 10
+        same += sum(x == y for x, y in zip(ta, tb)) >= min(len(ta), len(tb)) - 2
+    assert same >= 4

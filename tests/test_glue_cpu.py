@@ -174,6 +174,43 @@ def test_run_single_job_and_combine(tmp_path, monkeypatch):
     assert "Total Accuracy" in open(base / "evaluation_stats.csv").read()
 
 
+def test_run_single_job_hands_the_whole_job_to_a_continuous_batching_backend(tmp_path, monkeypatch):
+    """A backend whose ``infer`` carries ``serve_all`` gets all prompts of the job in one call (rows = batch_size);
+    results land on their problems and repeats in order."""
+    import csv
+    from tah_b200.evaluate import jobs, matheval
+    from tah_b200.evaluate.jobs import run_single_job
+
+    class Grader:
+        def rule_judge(self, out, gold):
+            ans = out.strip().split()[-1] if out.strip() else ""
+            return (ans == gold, ans or "No extracted answer")
+    monkeypatch.setitem(matheval.evaluator_map, "toy", Grader())
+    calls = []
+
+    def factory(backend, config, model_path, tokenizer, tp_size=1):
+        def infer(prompts):
+            raise AssertionError("static batches must not be used when serve_all exists and the job is larger than a batch")
+
+        def serve_all(prompts, rows):
+            calls.append((len(prompts), rows))
+            return [(f"the answer is {len(p.split())}", 0.25) for p in prompts]
+        infer.serve_all = serve_all
+        return object(), infer
+
+    mapping = {"id_field": "id", "question_field": "question", "answer_field": "answer", "answer_type": "boxed"}
+    probs = [{"id": f"toy_{i}", "question": " ".join("w" * (i + 1)), "answer": str(i + 1)} for i in range(5)]
+    monkeypatch.setattr(jobs, "_make_prompt", lambda text, tok, is_code: text)
+    run_single_job(config={"batch_size": 2, "repeat_size": 2}, combined_dataset_name="toy", output_dir=str(tmp_path),
+                   timestamp="ts", model_path="", job_id=0, job_nums=1, start_idx=0, end_idx=5, tp_size=1,
+                   backend="tah", data_range=None, problems_data=probs, field_mapping=mapping,
+                   unified_code_solutions_file=None, tokenizer=_FakeTok(), backend_factory=factory)
+    assert calls == [(10, 2)]
+    rows = list(csv.DictReader(open(tmp_path / "toy_tah" / "ts" / "job_0" / "detailed_results.csv")))
+    assert len(rows) == 10 and all(r["is_correct"] == "True" for r in rows)
+    assert [r["problem_id"] for r in rows[:4]] == ["toy_0", "toy_0", "toy_1", "toy_1"]
+
+
 def test_code_sanitize_and_evaluate(tmp_path):
     text = "Here you go:\n```python\nimport math\n\ndef helper(x):\n    return x + 1\n\ndef unused():\n    return 0\n\ndef add1(x):\n    return helper(x)\n```\nthanks"
     code = codeeval.sanitize(text, "add1")
