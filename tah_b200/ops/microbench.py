@@ -101,6 +101,42 @@ def bench_gemm(a):
     return res, t, flops, byts
 
 
+def bench_gemm_qkv(a):
+    """QKV projection of a decode tick (``--m`` rows, 16 q / 8 KV heads of 128, LoRA extension ``--r``): the plain
+    GEMM followed by the QK-norm + RoPE + paged-KV-write kernel, against the GEMM with that work in its epilogue."""
+    M, H, nq, nkv, hd, R = a.m, a.k, a.nq, a.nkv, 128, a.r
+    F = (nq + 2 * nkv) * hd
+    n = _copies(F * H * 2, a.copies)
+    ws = [_rand(F, H, scale=H ** -0.5) for _ in range(n)]
+    b = _rand(F, R, scale=0.05) if R else None
+    x, t = _rand(M, H), (_rand(M, R) if R else None)
+    qw, kw = torch.ones(hd, device="cuda", dtype=torch.bfloat16), torch.ones(hd, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 2000, (M,), device="cuda", dtype=torch.int32)
+    pages = (M + 15) // 16 + 4
+    caches = [torch.zeros(pages, 2, nkv, 16, hd, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    slot = torch.randperm(pages * 16, device="cuda")[:M].to(torch.int32)
+    sel = torch.zeros(M, dtype=torch.int32, device="cuda")
+    q = torch.empty(M, nq * hd, dtype=torch.bfloat16, device="cuda")
+    qkv = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    table = K.rope_table(pos, hd, 1e6)
+    ext = dict(x2=t, w2=b) if R else {}
+
+    def separate(i):
+        K.gemm(x, ws[i % n], out=qkv, **ext)
+        K.qk_norm_rope_kv(qkv, qw, kw, pos, nq, nkv, hd, 1e-6, 1e6, q_out=q, caches=caches, cache_sel=sel, slot=slot,
+                          page_size=16)
+
+    def fused(i):
+        K.gemm_qkv(x, ws[i % n], qw, kw, pos, nq, nkv, 1e-6, 1e6, q_out=q, caches=caches, cache_sel=sel, slot=slot,
+                   page_size=16, rope_cs=table, **ext)
+
+    t_sep = _time(separate, a.iters, a.warmup)
+    t_fused = _time(fused, a.iters, a.warmup)
+    res = {"op": "gemm_qkv", "M": M, "F": F, "K": H, "R": R, "separate_us": round(t_sep * 1e6, 2),
+           "fused_us": round(t_fused * 1e6, 2)}
+    return res, t_fused, 2.0 * M * F * (H + R), (F * (H + R) + M * (H + R) + M * F) * 2
+
+
 def bench_decode_attn(a):
     nq, nkv, hd, page = a.nq, a.nkv, a.hd, 16
     rows, ctx = a.rows, a.ctx
@@ -335,7 +371,7 @@ def bench_shard_gather(a):
 
 DIST_OPS = {"tp_chain": bench_tp_chain, "shard_gather": bench_shard_gather}
 
-OPS = {"attn_bwd": bench_attn_bwd, "gemm": bench_gemm, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn, "topk": bench_topk,
+OPS = {"gemm_qkv": bench_gemm_qkv, "attn_bwd": bench_attn_bwd, "gemm": bench_gemm, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn, "topk": bench_topk,
        "rmsnorm": bench_rmsnorm}
 
 
