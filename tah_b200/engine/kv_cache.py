@@ -15,6 +15,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List
 
+import os
+
 import torch
 
 
@@ -24,6 +26,9 @@ class CacheGeometry:
     n_kv_heads: int
     head_dim: int
     page_size: int = 16
+
+
+GUARD_PATTERN = 0x5A5A          # int16 view of the bf16 guard pages
 
 
 class PagedKVCache:
@@ -39,15 +44,27 @@ class PagedKVCache:
         self.len: List[torch.Tensor] = []
         self.free_stack: List[torch.Tensor] = []
         self.free_count: List[torch.Tensor] = []
+        # TAH_B200_CANARY=G: G guard pages behind every layer's pool, filled with a bit pattern that no kernel may
+        # touch (pages are only ever handed out from the free stack); check_guards() verifies them on the host
+        self.guard_pages = int(os.environ.get("TAH_B200_CANARY", "0") or 0)
         for d in range(n_depths):
             pages = rows * ppr if d == 0 else max(rows * 2, int(rows * ppr * deep_fraction))
             self.n_pages.append(pages)
-            self.pool.append(torch.zeros(geo.n_layers, pages, 2, geo.n_kv_heads, geo.page_size, geo.head_dim,
-                                         dtype=dtype, device=device))
+            pool = torch.zeros(geo.n_layers, pages + self.guard_pages, 2, geo.n_kv_heads, geo.page_size, geo.head_dim,
+                               dtype=dtype, device=device)
+            if self.guard_pages:
+                pool[:, pages:].view(torch.int16).fill_(GUARD_PATTERN)
+            self.pool.append(pool)
             self.page_table.append(torch.zeros(rows, ppr, dtype=torch.int32, device=device))
             self.len.append(torch.zeros(rows, dtype=torch.int32, device=device))
             self.free_stack.append(torch.arange(pages, dtype=torch.int32, device=device))
             self.free_count.append(torch.full((1,), pages, dtype=torch.int32, device=device))
+
+    def check_guards(self) -> bool:
+        """True when every guard page still holds the pattern (always true without ``TAH_B200_CANARY``)."""
+        if not self.guard_pages:
+            return True
+        return all(bool((p[:, n:].view(torch.int16) == GUARD_PATTERN).all()) for p, n in zip(self.pool, self.n_pages))
 
     def bytes(self) -> int:
         return sum(p.numel() * p.element_size() for p in self.pool)

@@ -244,10 +244,15 @@ class CustomTaHTrainer:
         if self.optimizer is None:
             self.create_optimizer()
         torch.manual_seed(a.seed + self.dp_rank)        # ranks of one tensor-parallel group draw the same dropout masks
+        self._resume_rng = None
         spe = self.steps_per_epoch()
         self.state.max_steps = a.max_steps if a.max_steps and a.max_steps > 0 else int(math.ceil(spe * a.num_train_epochs))
         if resume_from_checkpoint:
             self._load_training_state(resume_from_checkpoint)
+            if self._resume_rng is not None:
+                torch.set_rng_state(self._resume_rng["cpu"])
+                if self._resume_rng.get("cuda") is not None and self.model.device.type == "cuda":
+                    torch.cuda.set_rng_state(self._resume_rng["cuda"], self.model.device)
         if a.report_to in ("wandb", ["wandb"]) and self.rank == 0:
             try:
                 import wandb
@@ -406,7 +411,11 @@ class CustomTaHTrainer:
         self._save(ckpt)
         if not a.save_only_model and self.optimizer is not None:
             os.makedirs(os.path.join(ckpt, "optim"), exist_ok=True)
-            torch.save(self.optimizer.state_dict(), os.path.join(ckpt, "optim", f"rank{self.rank}.pt"))
+            sd = self.optimizer.state_dict()
+            # random-number state of this rank (dropout masks, forced continuations): an exact resume continues it
+            sd["rng"] = {"cpu": torch.get_rng_state(),
+                         "cuda": torch.cuda.get_rng_state(self.model.device) if self.model.device.type == "cuda" else None}
+            torch.save(sd, os.path.join(ckpt, "optim", f"rank{self.rank}.pt"))
         if self.rank == 0:
             with open(os.path.join(ckpt, "trainer_state.json"), "w") as fh:
                 json.dump({"global_step": self.state.global_step, "epoch": self.state.epoch,
@@ -427,4 +436,8 @@ class CustomTaHTrainer:
             self.state.global_step, self.state.epoch = int(d["global_step"]), float(d["epoch"])
         opt = os.path.join(ckpt, "optim", f"rank{self.rank}.pt")
         if os.path.exists(opt) and self.optimizer is not None:
-            self.optimizer.load_state_dict(torch.load(opt, map_location="cpu", weights_only=False))
+            sd = torch.load(opt, map_location="cpu", weights_only=False)
+            rng = sd.pop("rng", None)
+            self.optimizer.load_state_dict(sd)
+            if rng is not None:
+                self._resume_rng = rng                       # applied after train() has seeded the generators

@@ -333,3 +333,20 @@ def test_tah_eval_backend_continuous_batching_matches_static_batches(tmp_path):
         assert 0 < len(ta) <= 10
         same += sum(x == y for x, y in zip(ta, tb)) >= min(len(ta), len(tb)) - 2
     assert same >= 4
+
+
+def test_kv_guard_pages_stay_untouched(monkeypatch):
+    """``TAH_B200_CANARY``: guard pages behind every layer's KV pool keep their pattern through prefill, decode
+    ticks at both depths, page allocation on the device and the serving loop's page recycling."""
+    from tah_b200.engine import TaHEngine
+    monkeypatch.setenv("TAH_B200_CANARY", "2")
+    model = tiny_tah(max_iter=2, dtype=torch.bfloat16).cuda().eval()
+    eng = TaHEngine(model, max_rows=4, max_seq_len=80, use_cuda_graph=True, deep_fraction=1.0)
+    eng.hard_override = eng.make_bernoulli_override(4, (0.4,), seed=3)
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, 1024, (4, 23), generator=g).cuda()
+    eng.generate(ids, None, max_new_tokens=40, do_sample=False)
+    assert eng.kv.guard_pages == 2 and eng.kv.check_guards()
+    prompts = [torch.randint(0, 1024, (n,), generator=g) for n in (9, 30, 14, 5, 21)]
+    eng.serve(prompts, max_new_tokens=12, rows=2, check_every=4)
+    assert eng.kv.check_guards()

@@ -309,3 +309,50 @@ def test_prune_reads_calibration_from_a_saved_dataset(tmp_path):
         prune.read_calibration_texts(str(tmp_path / "ds"), "text", 2)
     (tmp_path / "c.txt").write_text("one\n\ntwo\n")
     assert prune.read_calibration_texts(str(tmp_path / "c.txt")) == ["one", "two"]
+
+
+def test_trainer_resume_is_exact_with_optimizer_and_rng_state(tmp_path):
+    """Train four steps with a checkpoint after two; a second trainer resumed from that checkpoint reaches the same
+    parameters: model weights, sharded optimizer state, data position and the random-number state (LoRA dropout is
+    on, so the masks of steps 3 and 4 must continue the first run's stream)."""
+    from tah_b200 import TaHForCausalLM
+    from tah_b200.train import CustomTaHDataCollator, CustomTaHTrainer, TaHTrainingArguments
+    from tests.helpers import tiny_tah
+
+    def rows():
+        g = torch.Generator().manual_seed(11)
+        out = []
+        for _ in range(8):
+            ids = torch.randint(0, 1024, (20,), generator=g).tolist()
+            hard = [1] * 20
+            hard[5] = 2
+            out.append(dict(input_ids=ids, attention_mask=[1] * 20, labels=[-100] * 2 + ids[2:], iter_count_labels=hard))
+        return out
+
+    def args(out_dir, **kw):
+        return TaHTrainingArguments(output_dir=str(out_dir), per_device_train_batch_size=1, gradient_accumulation_steps=2,
+                                    learning_rate=1e-3, max_grad_norm=1.0, num_train_epochs=1, logging_steps=1, seed=0,
+                                    save_strategy="steps", save_steps=2, save_only_model=False, **kw)
+
+    def build():
+        m = tiny_tah(seed=0)
+        for mod in m.modules():
+            if hasattr(mod, "lora") and getattr(mod.lora, "r", 0) > 0:
+                mod.lora.lora_dropout = 0.25
+        return m
+
+    m1 = build()
+    t1 = CustomTaHTrainer(m1, args(tmp_path / "a"), rows(), None, data_collator=CustomTaHDataCollator(None, pad_token_id=0))
+    t1.train()
+    assert t1.state.global_step == 4 and (tmp_path / "a" / "checkpoint-2" / "optim" / "rank0.pt").exists()
+    final = {n: p.detach().clone() for n, p in m1.named_parameters()}
+
+    m2 = TaHForCausalLM.from_pretrained(str(tmp_path / "a" / "checkpoint-2"))
+    for mod in m2.modules():
+        if hasattr(mod, "lora") and getattr(mod.lora, "r", 0) > 0:
+            mod.lora.lora_dropout = 0.25
+    t2 = CustomTaHTrainer(m2, args(tmp_path / "b"), rows(), None, data_collator=CustomTaHDataCollator(None, pad_token_id=0))
+    t2.train(resume_from_checkpoint=str(tmp_path / "a" / "checkpoint-2"))
+    assert t2.state.global_step == 4
+    err = max(float((final[n] - p.detach()).abs().max()) for n, p in m2.named_parameters())
+    assert err < 1e-6, err

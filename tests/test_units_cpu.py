@@ -388,3 +388,16 @@ def test_zero_adamw_accumulates_micro_batch_gradients_in_fp32():
     err_acc = (run(True) - exact).abs().mean()
     assert err_acc < 0.5 * err_plain                      # one rounding instead of sixteen
     assert err_acc < 2.5e-3                                # bf16 rounding of values of order one
+
+
+def test_kv_cache_guard_pages(monkeypatch):
+    from tah_b200.engine.kv_cache import CacheGeometry, PagedKVCache
+    monkeypatch.setenv("TAH_B200_CANARY", "2")
+    kv = PagedKVCache(CacheGeometry(2, 2, 64, 16), 3, 40, 2, device="cpu")
+    assert kv.pool[0].shape[1] == kv.n_pages[0] + 2 and kv.check_guards()
+    slots = kv.assign_prefill(0, torch.tensor([5, 17, 33]))
+    assert int(slots.max()) < kv.n_pages[0] * 16            # slots never reach into the guard pages
+    kv.pool[1][0, kv.n_pages[1], 0, 0, 0, 0] = 1.0
+    assert not kv.check_guards()
+    monkeypatch.delenv("TAH_B200_CANARY")
+    assert PagedKVCache(CacheGeometry(2, 2, 64, 16), 3, 40, 2, device="cpu").check_guards()
