@@ -305,6 +305,11 @@ class CustomTaHTrainer:
     def _train_loop(self, a, spe, accum, loss_window, t0, start_epoch):
         for epoch in range(start_epoch, int(math.ceil(a.num_train_epochs)) if a.max_steps <= 0 else 10 ** 9):
             micro = list(self._loader(self.train_dataset, a.per_device_train_batch_size, True, epoch))
+            if not micro:
+                raise RuntimeError("the training set is empty on this rank")
+            # an epoch with fewer micro-batches than the accumulation window is one (shorter) window, so that every
+            # epoch makes at least the one step that steps_per_epoch() promises
+            accum = min(accum, len(micro))
             skip = (self.state.global_step - epoch * spe) * accum if epoch == start_epoch else 0
             for w in range(skip, len(micro) - accum + 1, accum):
                 window = micro[w:w + accum]

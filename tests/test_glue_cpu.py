@@ -356,3 +356,20 @@ def test_trainer_resume_is_exact_with_optimizer_and_rng_state(tmp_path):
     assert t2.state.global_step == 4
     err = max(float((final[n] - p.detach()).abs().max()) for n, p in m2.named_parameters())
     assert err < 1e-6, err
+
+
+def test_trainer_with_fewer_micro_batches_than_the_accumulation_window_still_steps(tmp_path):
+    """Three rows against ``gradient_accumulation_steps=8`` and ``max_steps=2``: each epoch is one shorter window (the
+    loop used to spin over epochs without ever taking a step)."""
+    from tah_b200.train import CustomTaHDataCollator, CustomTaHTrainer, TaHTrainingArguments
+    from tests.helpers import tiny_tah
+    g = torch.Generator().manual_seed(2)
+    rows = []
+    for _ in range(3):
+        ids = torch.randint(0, 1024, (16,), generator=g).tolist()
+        rows.append(dict(input_ids=ids, attention_mask=[1] * 16, labels=ids, iter_count_labels=[1] * 15 + [2]))
+    args = TaHTrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=1, gradient_accumulation_steps=8,
+                                learning_rate=1e-3, max_steps=2, logging_steps=1, save_strategy="no", seed=0)
+    tr = CustomTaHTrainer(tiny_tah(seed=0), args, rows, None, data_collator=CustomTaHDataCollator(None, pad_token_id=0))
+    tr.train()
+    assert tr.state.global_step == 2
