@@ -373,3 +373,25 @@ def test_trainer_with_fewer_micro_batches_than_the_accumulation_window_still_ste
     tr = CustomTaHTrainer(tiny_tah(seed=0), args, rows, None, data_collator=CustomTaHDataCollator(None, pad_token_id=0))
     tr.train()
     assert tr.state.global_step == 2
+
+
+def test_sft_script_runs_a_shipped_recipe_on_synthetic_data(tmp_path):
+    """``script/train/SFT_TaH.py --synthetic`` with the shipped step-1 recipe (16 accumulation steps, more than the
+    eight synthetic rows): two optimizer steps, evaluation, final checkpoint in the reference layout."""
+    import subprocess
+    import sys
+    import yaml
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = yaml.safe_load(open(os.path.join(root, "script", "recipes", "qwen3_1.7", "sft_tah_step1.yaml")))
+    cfg["data"]["output_dir"] = str(tmp_path / "run")
+    cfg["training"]["save_strategy"] = "no"
+    cfg["training"]["report_to"] = "none"
+    path = tmp_path / "cfg.yaml"
+    yaml.safe_dump(cfg, open(path, "w"))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run([sys.executable, os.path.join(root, "script", "train", "SFT_TaH.py"), "--config", str(path),
+                          "--synthetic", "8", "--max_steps", "2"], capture_output=True, text=True, timeout=400, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "Saved final model" in res.stdout
+    finals = [os.path.join(dp, "final_model") for dp, dn, _ in os.walk(tmp_path / "run") if "final_model" in dn]
+    assert finals and {"model.safetensors", "tah_config.json", "iter_decider.bin"} <= set(os.listdir(finals[0]))
